@@ -1,0 +1,230 @@
+/*
+ * splash_b200 — C ABI of the B200 (sm_100a) splash-attention path.
+ *
+ * The reference (primatrix/tokamax) has no C ABI: its splash attention is reached through two
+ * Python interfaces (tokamax/_src/ops/experimental/tpu/splash_attention/splash_attention_kernel.py
+ * and tokamax/_src/ops/attention/api.py).  Each entry point below names the reference function it
+ * stands in for, so a binding (ctypes, XLA custom call, pybind11 ...) can replace that function's
+ * device work one-for-one.
+ *
+ * Conventions
+ *   - Plain C types only.  Device buffers are raw pointers owned by the caller; the library
+ *     allocates no device memory.  Scratch comes from the caller (splash_bwd_workspace_bytes).
+ *   - Every call enqueues work on the given stream and returns without synchronising.
+ *   - Return value: 0 (SPLASH_OK) or a negative SplashStatus.  Nothing aborts or throws.
+ *   - Asynchronous kernel faults (a bounded wait that ran out) are reported through a
+ *     caller-provided 4-word device error record, read back with splash_read_error.
+ *   - Tensors are (batch, heads, seq, head_dim) with element strides; head_dim must be
+ *     contiguous (stride 1) and every other stride a multiple of 8 elements (16 bytes), so the
+ *     reference's [heads, seq, dim] layout, the Op layout [batch, seq, heads, dim] and the
+ *     head-sharded layout the context-parallel exchange produces are all consumed without copies.
+ */
+#ifndef SPLASH_B200_H_
+#define SPLASH_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum SplashStatus {
+  SPLASH_OK = 0,
+  SPLASH_ERR_INVALID_ARGUMENT = -1, /* shapes / strides / block sizes the kernels do not take */
+  SPLASH_ERR_UNSUPPORTED = -2,      /* valid for the reference, not built here (maps to NotImplementedError) */
+  SPLASH_ERR_CUDA = -3,             /* a CUDA runtime / driver call failed */
+  SPLASH_ERR_NO_DEVICE = -4,        /* no sm_100 device / driver entry point missing */
+  SPLASH_ERR_KERNEL_TIMEOUT = -5,   /* a device-side bounded wait ran out (see error record) */
+  SPLASH_ERR_OUT_OF_MEMORY = -6,    /* host allocation failed */
+  SPLASH_ERR_TOO_LARGE = -7         /* size beyond a fixed built-in limit */
+} SplashStatus;
+
+typedef enum SplashDType {
+  SPLASH_BF16 = 0,
+  SPLASH_F32 = 1,
+  SPLASH_F8E4M3 = 2
+} SplashDType;
+
+/* (batch, heads, seq, head_dim) view of device memory. */
+typedef struct SplashTensor {
+  void* data;
+  int32_t dtype;      /* SplashDType */
+  int64_t size[4];    /* batch, heads, seq, head_dim */
+  int64_t stride[4];  /* element strides in the same order; stride[3] == 1 */
+} SplashTensor;
+
+/* In-kernel mask function for partially masked blocks; the counterpart of the reference's
+ * `mask_function` + `q_sequence` (splash_attention_mask.py:177-244, CausalMask :247,
+ * ChunkedCausalMask :303, LocalMask :363).  Every one of them keeps key j for query i iff
+ * lo(i) <= j <= hi(i):
+ *   CAUSAL : hi = i + offset
+ *   LOCAL  : lo = i + offset - left (if has_left), hi = i + offset + right (if has_right)
+ *   CHUNKED: lo = (i / chunk) * chunk, hi = i
+ * where i = q_sequence[row] (row itself when q_sequence is NULL).
+ * TABLE means: read the partial block from partial_mask_blocks instead. */
+typedef enum SplashMaskKind {
+  SPLASH_MASK_TABLE = 0,
+  SPLASH_MASK_CAUSAL = 1,
+  SPLASH_MASK_LOCAL = 2,
+  SPLASH_MASK_CHUNKED = 3
+} SplashMaskKind;
+
+typedef struct SplashMaskFn {
+  int32_t kind;       /* SplashMaskKind */
+  int32_t offset;     /* CAUSAL, LOCAL */
+  int32_t left;       /* LOCAL */
+  int32_t right;      /* LOCAL */
+  int32_t has_left;   /* LOCAL: 0 = unbounded */
+  int32_t has_right;  /* LOCAL: 0 = unbounded */
+  int32_t chunk;      /* CHUNKED */
+} SplashMaskFn;
+
+/* ------------------------------------------------------------------------------------------
+ * MaskInfo builder (host).  Replaces `_process_mask`
+ * (splash_attention_mask_info.py:357-570; process_mask / process_mask_dkv :573-574), including
+ * `_generate_shard_metadata` (:183-228) and `_downcast_to_small_type` (:91-124).
+ *
+ * The mask is given as an expression tree in post-order (children before parents); the last
+ * node is the root.  Leaves: FULL, CAUSAL, LOCAL, CHUNKED (evaluated analytically per block) and
+ * DENSE (a row-major bool[Sq, Skv] host array).  Inner nodes: AND, OR.
+ * ---------------------------------------------------------------------------------------- */
+typedef enum SplashMaskNodeKind {
+  SPLASH_NODE_FULL = 0,
+  SPLASH_NODE_CAUSAL = 1,
+  SPLASH_NODE_LOCAL = 2,
+  SPLASH_NODE_CHUNKED = 3,
+  SPLASH_NODE_DENSE = 4,
+  SPLASH_NODE_AND = 5,
+  SPLASH_NODE_OR = 6
+} SplashMaskNodeKind;
+
+typedef struct SplashMaskNode {
+  int32_t kind;            /* SplashMaskNodeKind */
+  int32_t left_child;      /* AND / OR: node indices */
+  int32_t right_child;
+  SplashMaskFn fn;         /* CAUSAL / LOCAL / CHUNKED parameters */
+  const uint8_t* dense;    /* DENSE: bool[Sq*Skv], row-major */
+} SplashMaskNode;
+
+/* Result tables, all int32 on this side of the ABI (the Python layer applies the reference's
+ * int8/int16 downcast rule, which only depends on the maximum value reported here).
+ * A pointer is NULL exactly where the reference returns None. */
+typedef struct SplashMaskInfoOut {
+  int32_t* mask_next;            /* [n_entries] or NULL */
+  int32_t* active_rows;          /* [n_entries] or NULL (static grid) */
+  int32_t* active_cols;          /* [n_entries] or NULL */
+  int32_t* block_mask;           /* [n_entries] or NULL (all-full mask) */
+  int32_t* num_active_blocks;    /* [n_shards] or NULL */
+  int8_t* partial_mask_blocks;   /* [n_partial, bq, bkv] ([n_partial, bkv, bq] for dkv) or NULL */
+  int64_t n_entries;
+  int32_t n_shards;
+  int32_t n_partial;
+  int32_t all_full;              /* 1: every field above is NULL (reference's early return) */
+} SplashMaskInfoOut;
+
+int splash_maskinfo_build(const SplashMaskNode* nodes, int32_t n_nodes, int64_t q_len,
+                          int64_t kv_len, int32_t block_q, int32_t block_kv, int32_t is_dkv,
+                          int32_t q_seq_shards, int32_t kv_seq_shards, int32_t return_dynamic_grid,
+                          SplashMaskInfoOut* out);
+void splash_maskinfo_free(SplashMaskInfoOut* out);
+
+/* ------------------------------------------------------------------------------------------
+ * Kernel schedule (host).  The device kernels walk 128x128 tiles.  This expands a block-level
+ * classification (what MaskInfo encodes: 0 empty / 1 partial / 2 full per (block_q, block_kv)
+ * block, plus the partial-block id) into per-CTA work lists.  It is the counterpart of the
+ * index maps the reference derives from MaskInfo at call time
+ * (splash_attention_kernel.py:663-696 forward, :1512-1592 backward; find_bounds,
+ * splash_attention_mask_info.py:33-47).
+ *
+ *   kind 0 (forward): one row per pair of q tiles; entry = kv tile.
+ *   kind 1 (dq)     : one row per q tile;          entry = kv tile.
+ *   kind 2 (dkv)    : one row per kv tile;         entry = q tile.
+ * Entry layout (4 x int32): [0] tile index along the walked axis, [1] state of sub-tile 0 in
+ * bits 0-1 and of sub-tile 1 in bits 2-3 (0 skip, 1 partial, 2 full), [2]/[3] partial-block id
+ * of sub-tile 0/1 (-1 if none).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct SplashScheduleOut {
+  int32_t* row_ptr;   /* [n_rows + 1] */
+  int32_t* entries;   /* [n_entries * 4] */
+  int32_t n_rows;
+  int64_t n_entries;
+} SplashScheduleOut;
+
+int splash_schedule_build(const int32_t* block_state, const int32_t* partial_id, int32_t n_q_blocks,
+                          int32_t n_kv_blocks, int32_t block_q, int32_t block_kv, int32_t kind,
+                          SplashScheduleOut* out);
+void splash_schedule_free(SplashScheduleOut* out);
+
+/* Device-resident schedule + mask data shared by the kernels. */
+typedef struct SplashDeviceSchedule {
+  const int32_t* row_ptr;            /* device, [n_rows + 1] */
+  const int32_t* entries;            /* device, [n_entries * 4], 16-byte aligned */
+  int32_t n_rows;
+  const int8_t* partial_mask_blocks; /* device, [n_partial, pm_rows, pm_cols] or NULL */
+  int32_t block_q;                   /* block shape the partial blocks were cut with */
+  int32_t block_kv;
+} SplashDeviceSchedule;
+
+/* ------------------------------------------------------------------------------------------
+ * Forward.  Replaces `_splash_attention_forward` + `flash_attention_kernel`
+ * (splash_attention_kernel.py:550-995, :299-527): o = softmax(mask(scale * q k^T)) v with fp32
+ * accumulation, plus logsumexp and max_logits (natural log, fp32 [batch, q_heads, q_len]).
+ * q head h reads kv head h / (q_heads / kv_heads) (:675-682).
+ * ---------------------------------------------------------------------------------------- */
+typedef struct SplashFwdArgs {
+  SplashTensor q, k, v, o;          /* bf16 */
+  float* logsumexp;                 /* may be NULL */
+  float* max_logits;                /* may be NULL */
+  const int32_t* q_segment_ids;     /* [batch, q_len] or NULL */
+  const int32_t* kv_segment_ids;    /* [batch, kv_len] or NULL (both or neither) */
+  const int32_t* q_sequence;        /* [q_len] or NULL (= arange) */
+  SplashDeviceSchedule sched;       /* kind 0 */
+  SplashMaskFn mask_fn;
+  float scale;                      /* multiplies q k^T in fp32 */
+  float mask_value;                 /* written to logsumexp / max_logits of rows with no work */
+  uint32_t* error_record;           /* device, 4 words, zeroed by the caller */
+} SplashFwdArgs;
+
+int splash_fwd(const SplashFwdArgs* args, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------
+ * Backward.  Replaces `_splash_attention_bwd` + `_splash_attention_bwd_dkv` +
+ * `_flash_attention_dkv_kernel` (splash_attention_kernel.py:1871-1947, :1462-1868, :1234-1459):
+ * di = sum(o * do), then dq (q-tile stationary) and dk/dv (kv-tile stationary, the q heads of a
+ * kv head summed inside one CTA in fp32 — no atomics, bitwise repeatable).
+ * Workspace: splash_bwd_workspace_bytes(batch, q_heads, q_len) bytes, 256-byte aligned.
+ * ---------------------------------------------------------------------------------------- */
+typedef struct SplashBwdArgs {
+  SplashTensor q, k, v, o, d_o;     /* bf16 inputs */
+  SplashTensor dq, dk, dv;          /* bf16 outputs */
+  const float* logsumexp;           /* forward result, natural log */
+  const int32_t* q_segment_ids;
+  const int32_t* kv_segment_ids;
+  const int32_t* q_sequence;
+  SplashDeviceSchedule sched_dq;    /* kind 1 */
+  SplashDeviceSchedule sched_dkv;   /* kind 2 */
+  SplashMaskFn mask_fn;
+  float scale;
+  void* workspace;
+  size_t workspace_bytes;
+  uint32_t* error_record;
+} SplashBwdArgs;
+
+size_t splash_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
+int splash_bwd(const SplashBwdArgs* args, void* cuda_stream);
+
+/* Copies the 4-word device error record to host (synchronises the stream) and maps it to a
+ * status: SPLASH_OK or SPLASH_ERR_KERNEL_TIMEOUT.  record_out may be NULL. */
+int splash_read_error(const uint32_t* error_record, void* cuda_stream, uint32_t record_out[4]);
+
+/* Human-readable text for a SplashStatus.  Never NULL. */
+const char* splash_status_str(int status);
+
+/* Library / build identification: "splash_b200 <version> sm_100a". */
+const char* splash_version(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SPLASH_B200_H_ */

@@ -1,0 +1,840 @@
+// Splash attention backward for sm_100a: bf16 inputs, head_dim 128, fp32 accumulation.
+//
+// Three kernels, all atomic-free and bitwise repeatable:
+//   1. delta      : di[b,h,q] = sum_d o * do                      (HBM-bound elementwise pass)
+//   2. dq kernel  : one CTA per (q tile, q head).  Per kv tile: S = Q K^T, dP = dO V^T,
+//                   dS = P o (dP - di), dQ += dS K.
+//   3. dkv kernel : one CTA per (kv tile, kv head).  Loops over the q heads that share the kv
+//                   head and their active q tiles: S^T = K Q^T, dP^T = V dO^T, dV += P^T dO,
+//                   dK += dS^T Q.  The whole GQA group is summed in the CTA's fp32 TMEM
+//                   accumulators, so dK/dV need no atomics and no second pass.
+// In both MMA kernels P / dS are written back to TMEM as bf16 and consumed as the A operand of
+// the next MMA; K, V, Q and dO tiles are each staged once by TMA and read both K-major and
+// MN-major from the same 128-byte-swizzled shared-memory image.
+//
+// Arithmetic follows the reference backward
+// (tokamax/_src/ops/experimental/tpu/splash_attention/splash_attention_kernel.py:1234-1459 and
+// base.py:115-173): P = exp(S - logsumexp), dS = (dP - di) * P, with the softmax scale applied
+// in fp32 inside the kernels.
+#include "splash_common.cuh"
+
+namespace sb {
+
+constexpr int kBwdStages = 4;
+constexpr int kBwdThreads = 320;  // 8 compute warps + TMA warp + MMA warp
+
+// ------------------------------------------------------------------------------------------
+// delta = rowsum(o * do)
+// ------------------------------------------------------------------------------------------
+struct DeltaParams {
+  const __nv_bfloat16* o;
+  const __nv_bfloat16* d_o;
+  int64_t o_sb, o_sh, o_ss, do_sb, do_sh, do_ss;
+  float* delta;  // [B, Hq, Sq]
+  int q_heads, q_len;
+  int64_t n_rows;
+};
+
+__global__ void __launch_bounds__(256) splash_delta_kernel(const DeltaParams p) {
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= p.n_rows) return;
+  const int q = (int)(row % p.q_len);
+  const int64_t bh = row / p.q_len;
+  const int h = (int)(bh % p.q_heads);
+  const int64_t b = bh / p.q_heads;
+  const uint2* po = reinterpret_cast<const uint2*>(p.o + b * p.o_sb + h * p.o_sh + (int64_t)q * p.o_ss);
+  const uint2* pd =
+      reinterpret_cast<const uint2*>(p.d_o + b * p.do_sb + h * p.do_sh + (int64_t)q * p.do_ss);
+  const uint2 a = __ldg(po + lane);
+  const uint2 g = __ldg(pd + lane);
+  const __nv_bfloat162 a0 = *reinterpret_cast<const __nv_bfloat162*>(&a.x);
+  const __nv_bfloat162 a1 = *reinterpret_cast<const __nv_bfloat162*>(&a.y);
+  const __nv_bfloat162 g0 = *reinterpret_cast<const __nv_bfloat162*>(&g.x);
+  const __nv_bfloat162 g1 = *reinterpret_cast<const __nv_bfloat162*>(&g.y);
+  float acc = __bfloat162float(a0.x) * __bfloat162float(g0.x) +
+              __bfloat162float(a0.y) * __bfloat162float(g0.y) +
+              __bfloat162float(a1.x) * __bfloat162float(g1.x) +
+              __bfloat162float(a1.y) * __bfloat162float(g1.y);
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+  if (lane == 0) p.delta[row] = acc;
+}
+
+// ------------------------------------------------------------------------------------------
+// shared pieces of the two MMA kernels
+// ------------------------------------------------------------------------------------------
+struct BwdParams {
+  // outputs (dq kernel: dq; dkv kernel: dk, dv)
+  __nv_bfloat16* out0;
+  int64_t out0_sb, out0_sh, out0_ss;
+  __nv_bfloat16* out1;
+  int64_t out1_sb, out1_sh, out1_ss;
+  const float* lse;    // [B, Hq, Sq] natural log
+  const float* delta;  // [B, Hq, Sq]
+  const int32_t* q_seg;
+  const int32_t* kv_seg;
+  const int32_t* q_sequence;
+  const int32_t* row_ptr;
+  const int4* entries;
+  const int8_t* pmb;
+  int pm_bq, pm_bkv;
+  SplashMaskFn fn;
+  int q_len, kv_len, q_heads, kv_heads, n_rows;
+  float scale, scale_log2;
+  uint32_t* err;
+};
+
+struct BwdBarriers {
+  uint64_t stat_full[2];              // stationary operand tiles
+  uint64_t ring_full[kBwdStages];
+  uint64_t ring_empty[kBwdStages];
+  uint64_t s_full[2];
+  uint64_t dp_full;
+  uint64_t p_full;                    // dkv: P^T ready; dq: unused
+  uint64_t ds_full;
+  uint64_t acc_done;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  uint32_t early_exit;
+};
+
+constexpr int kBwdSmemBytes = (2 + kBwdStages) * kTileBytes + 1024 + 1024;
+
+// Column offset (32-bit TMEM columns) at which compute warpgroup w stores its 32 packed bf16
+// columns: inside the 64 fp32 columns it has itself read, so the two warpgroups never race.
+__device__ __forceinline__ uint32_t packed_col(int w) { return (uint32_t)(w * 64); }
+// TMEM column of the A operand for K-slice k (16 values) of a tile written that way.
+__device__ __forceinline__ uint32_t packed_a_col(int k) {
+  return (uint32_t)((k >> 2) * 64 + (k & 3) * 8);
+}
+
+__device__ __forceinline__ void store_row_half(__nv_bfloat16* dst, const uint32_t (&v)[32],
+                                               float mul) {
+  uint4* d4 = reinterpret_cast<uint4*>(dst);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    uint4 w;
+    w.x = pack_bf16(__uint_as_float(v[8 * j + 0]) * mul, __uint_as_float(v[8 * j + 1]) * mul);
+    w.y = pack_bf16(__uint_as_float(v[8 * j + 2]) * mul, __uint_as_float(v[8 * j + 3]) * mul);
+    w.z = pack_bf16(__uint_as_float(v[8 * j + 4]) * mul, __uint_as_float(v[8 * j + 5]) * mul);
+    w.w = pack_bf16(__uint_as_float(v[8 * j + 6]) * mul, __uint_as_float(v[8 * j + 7]) * mul);
+    d4[j] = w;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// dq kernel
+// ------------------------------------------------------------------------------------------
+// TMEM: S0 [0,128) | S1 [128,256) | dP [256,384) | dQ [384,512)
+__global__ void __launch_bounds__(kBwdThreads, 1)
+splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                 const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                 const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* q_smem = smem;
+  uint8_t* do_smem = smem + kTileBytes;
+  uint8_t* ring = smem + 2 * kTileBytes;
+  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(smem + (2 + kBwdStages) * kTileBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int q_tile = p.n_rows - 1 - (int)blockIdx.x;
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv_head = head / (p.q_heads / p.kv_heads);
+  const int ebeg = p.row_ptr[q_tile];
+  const int eend = p.row_ptr[q_tile + 1];
+  const int n_ent = eend - ebeg;
+
+  if (threadIdx.x == 0) {
+    bars->early_exit = *reinterpret_cast<volatile uint32_t*>(p.err);
+    bars->abort_flag = 0;
+    mbar_init(&bars->stat_full[0], 1);
+    mbar_init(&bars->stat_full[1], 1);
+    for (int s = 0; s < kBwdStages; ++s) {
+      mbar_init(&bars->ring_full[s], 1);
+      mbar_init(&bars->ring_empty[s], 1);
+    }
+    mbar_init(&bars->s_full[0], 1);
+    mbar_init(&bars->s_full[1], 1);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->p_full, 256);
+    mbar_init(&bars->ds_full, 256);
+    mbar_init(&bars->acc_done, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (bars->early_exit != 0) return;
+  if (warp == 9) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  AbortCtx ab{&bars->abort_flag, p.err};
+
+  if (warp == 8) {
+    if (lane == 0 && n_ent > 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_do);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_arrive_expect_tx(&bars->stat_full[0], kTileBytes);
+      tma_load_4d(q_smem, &tm_q, &bars->stat_full[0], 0, q_tile * kTile, head, batch);
+      tma_load_4d(q_smem + kHalfBytes, &tm_q, &bars->stat_full[0], 64, q_tile * kTile, head, batch);
+      mbar_arrive_expect_tx(&bars->stat_full[1], kTileBytes);
+      tma_load_4d(do_smem, &tm_do, &bars->stat_full[1], 0, q_tile * kTile, head, batch);
+      tma_load_4d(do_smem + kHalfBytes, &tm_do, &bars->stat_full[1], 64, q_tile * kTile, head, batch);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int e = ebeg; e < eend && ok; ++e) {
+        const int col = p.entries[e].x;
+        for (int kv = 0; kv < 2 && ok; ++kv, ++it) {
+          const uint32_t s = it % kBwdStages;
+          ok = mbar_wait(&bars->ring_empty[s], ((it / kBwdStages) & 1u) ^ 1u, ab, 0x1100u + s);
+          if (!ok) break;
+          uint8_t* dst = ring + s * kTileBytes;
+          const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
+          mbar_arrive_expect_tx(&bars->ring_full[s], kTileBytes);
+          tma_load_4d(dst, tm, &bars->ring_full[s], 0, col * kTile, kv_head, batch);
+          tma_load_4d(dst + kHalfBytes, tm, &bars->ring_full[s], 64, col * kTile, kv_head, batch);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0 && n_ent > 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(kTile, kTile, false, false);
+      constexpr uint32_t idesc_mn = make_idesc_bf16(kTile, kHeadDim, false, true);
+      const uint32_t q_addr = smem_u32(q_smem), do_addr = smem_u32(do_smem), ring_addr = smem_u32(ring);
+      const uint32_t t_dp = tmem + 2 * kTile, t_dq = tmem + 3 * kTile;
+      auto ss_kmajor = [&](uint32_t d, uint32_t a0, uint32_t b0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_ss(d, make_smem_desc_sw128(a0 + off, 16, 1024), make_smem_desc_sw128(b0 + off, 16, 1024),
+                  idesc_kk, k > 0 ? 1u : 0u);
+        }
+      };
+      auto ring_wait = [&](uint32_t it, uint32_t tag) {
+        return mbar_wait(&bars->ring_full[it % kBwdStages], (it / kBwdStages) & 1u, ab, tag);
+      };
+      bool ok = mbar_wait(&bars->stat_full[0], 0, ab, 0x1200u) && mbar_wait(&bars->stat_full[1], 0, ab, 0x1201u);
+      // prologue: S_0, dP_0
+      ok = ok && ring_wait(0, 0x1210u);
+      if (ok) {
+        tc_fence_after();
+        ss_kmajor(tmem, q_addr, ring_addr);
+        tc_commit(&bars->s_full[0]);
+      }
+      ok = ok && ring_wait(1, 0x1211u);
+      if (ok) {
+        tc_fence_after();
+        ss_kmajor(t_dp, do_addr, ring_addr + kTileBytes);
+        tc_commit(&bars->dp_full);
+        tc_commit(&bars->ring_empty[1]);
+      }
+      for (int n = 0; n < n_ent && ok; ++n) {
+        const bool has_next = n + 1 < n_ent;
+        const uint32_t it_k = 2 * n, it_kn = 2 * n + 2, it_vn = 2 * n + 3;
+        if (has_next) {
+          ok = ring_wait(it_kn, 0x1220u);
+          if (!ok) break;
+          tc_fence_after();
+          ss_kmajor(tmem + ((n + 1) & 1) * kTile, q_addr, ring_addr + (it_kn % kBwdStages) * kTileBytes);
+          tc_commit(&bars->s_full[(n + 1) & 1]);
+        }
+        ok = mbar_wait(&bars->ds_full, n & 1u, ab, 0x1230u);
+        if (!ok) break;
+        tc_fence_after();
+        {
+          // dQ += dS_n K_n : A = packed dS in the S buffer, B = K tile read MN-major.
+          const uint32_t a_base = tmem + (n & 1) * kTile;
+          const uint32_t b0 = ring_addr + (it_k % kBwdStages) * kTileBytes;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma_ts(t_dq, a_base + packed_a_col(k), make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024),
+                    idesc_mn, (n > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&bars->ring_empty[it_k % kBwdStages]);
+        }
+        if (has_next) {
+          ok = ring_wait(it_vn, 0x1240u);
+          if (!ok) break;
+          tc_fence_after();
+          ss_kmajor(t_dp, do_addr, ring_addr + (it_vn % kBwdStages) * kTileBytes);
+          tc_commit(&bars->dp_full);
+          tc_commit(&bars->ring_empty[it_vn % kBwdStages]);
+        }
+      }
+      tc_commit(&bars->acc_done);
+    }
+  } else {
+    // ------------------------------------------------------------------ compute warpgroups
+    const int w = warp >> 2;       // column half this warpgroup owns
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;  // q row within the tile
+    const int q_row = q_tile * kTile + r;
+    const int qi = p.q_sequence ? p.q_sequence[q_row] : q_row;
+    const RowInterval iv = mask_fn_interval(p.fn, qi);
+    const bool has_seg = p.q_seg != nullptr;
+    const int q_seg = has_seg ? p.q_seg[(int64_t)batch * p.q_len + q_row] : 0;
+    const int32_t* kv_seg_row = has_seg ? p.kv_seg + (int64_t)batch * p.kv_len : nullptr;
+    const int64_t stat = ((int64_t)batch * p.q_heads + head) * p.q_len + q_row;
+    const float lse2 = p.lse[stat] * kLog2e;
+    const float delta = p.delta[stat];
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    const float c = p.scale_log2;
+    bool ok = true;
+
+    for (int n = 0; n < n_ent; ++n) {
+      const int4 ent = p.entries[ebeg + n];
+      const int st = ent.y & 3;
+      const int kv0 = ent.x * kTile + w * 64;
+      const uint32_t t_s = tmem + lane_addr + (n & 1) * kTile;
+      ok = mbar_wait(&bars->s_full[n & 1], (n >> 1) & 1u, ab, 0x1400u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      float pr[64];
+      {
+        uint32_t v[32];
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          tmem_ld32(t_s + w * 64 + g * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) pr[g * 32 + j] = __uint_as_float(v[j]);
+        }
+      }
+      if (st == 1) {
+        if (p.fn.kind != SPLASH_MASK_TABLE) {
+          const int lo_rel = iv.lo <= kv0 ? 0 : iv.lo - kv0;
+          const int hi_rel = iv.hi >= kv0 + 63 ? 63 : iv.hi - kv0;
+#pragma unroll
+          for (int j = 0; j < 64; ++j)
+            if (j < lo_rel || j > hi_rel) pr[j] = kMaskedLogit;
+        } else {
+          const int8_t* mrow = p.pmb + ((int64_t)ent.z * p.pm_bq + (q_row % p.pm_bq)) * p.pm_bkv +
+                               (kv0 % p.pm_bkv);
+          const int4* m4 = reinterpret_cast<const int4*>(mrow);
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const int4 mv = __ldg(m4 + g);
+            const uint32_t wd[4] = {(uint32_t)mv.x, (uint32_t)mv.y, (uint32_t)mv.z, (uint32_t)mv.w};
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (((wd[j >> 2] >> ((j & 3) * 8)) & 0xffu) == 0u) pr[g * 16 + j] = kMaskedLogit;
+          }
+        }
+      }
+      if (has_seg) {
+        const int4* sg4 = reinterpret_cast<const int4*>(kv_seg_row + kv0);
+#pragma unroll
+        for (int g = 0; g < 16; ++g) {
+          const int4 sv = __ldg(sg4 + g);
+          if (sv.x != q_seg) pr[g * 4 + 0] = kMaskedLogit;
+          if (sv.y != q_seg) pr[g * 4 + 1] = kMaskedLogit;
+          if (sv.z != q_seg) pr[g * 4 + 2] = kMaskedLogit;
+          if (sv.w != q_seg) pr[g * 4 + 3] = kMaskedLogit;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 64; ++j) pr[j] = ex2(fmaf(pr[j], c, -lse2));
+
+      ok = mbar_wait(&bars->dp_full, n & 1u, ab, 0x1410u);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t pk[32];
+      {
+        uint32_t v[32];
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          tmem_ld32(tmem + lane_addr + 2 * kTile + w * 64 + g * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float d0 = pr[g * 32 + 2 * j] * (__uint_as_float(v[2 * j]) - delta);
+            const float d1 = pr[g * 32 + 2 * j + 1] * (__uint_as_float(v[2 * j + 1]) - delta);
+            pk[g * 16 + j] = pack_bf16(d0, d1);
+          }
+        }
+      }
+      tmem_st32(t_s + packed_col(w), pk);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->ds_full);
+    }
+
+    // epilogue
+    __nv_bfloat16* dst = p.out0 + (int64_t)batch * p.out0_sb + (int64_t)head * p.out0_sh +
+                         (int64_t)q_row * p.out0_ss + w * 64;
+    if (n_ent > 0) {
+      if (ok) {
+        ok = mbar_wait(&bars->acc_done, 0, ab, 0x1500u);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int g = 0; g < 2; ++g) {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_addr + 3 * kTile + w * 64 + g * 32, v);
+          tmem_ld_wait();
+          store_row_half(dst + g * 32, v, p.scale);
+        }
+      }
+    } else {
+      uint32_t v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = 0u;
+      store_row_half(dst, v, 0.f);
+      store_row_half(dst + 32, v, 0.f);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// dkv kernel
+// ------------------------------------------------------------------------------------------
+// TMEM: S^T [0,128) | dP^T [128,256) | dK [256,384) | dV [384,512)
+__global__ void __launch_bounds__(kBwdThreads, 1)
+splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
+                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                  const BwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* k_smem = smem;
+  uint8_t* v_smem = smem + kTileBytes;
+  uint8_t* ring = smem + 2 * kTileBytes;
+  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(smem + (2 + kBwdStages) * kTileBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int kv_tile = blockIdx.x;  // for causal masks low kv tiles carry the most work
+  const int kv_head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int group = p.q_heads / p.kv_heads;
+  const int ebeg = p.row_ptr[kv_tile];
+  const int eend = p.row_ptr[kv_tile + 1];
+  const int n_ent = eend - ebeg;
+  const int n_steps = n_ent * group;
+
+  if (threadIdx.x == 0) {
+    bars->early_exit = *reinterpret_cast<volatile uint32_t*>(p.err);
+    bars->abort_flag = 0;
+    mbar_init(&bars->stat_full[0], 1);
+    mbar_init(&bars->stat_full[1], 1);
+    for (int s = 0; s < kBwdStages; ++s) {
+      mbar_init(&bars->ring_full[s], 1);
+      mbar_init(&bars->ring_empty[s], 1);
+    }
+    mbar_init(&bars->s_full[0], 1);
+    mbar_init(&bars->s_full[1], 1);
+    mbar_init(&bars->dp_full, 1);
+    mbar_init(&bars->p_full, 256);
+    mbar_init(&bars->ds_full, 256);
+    mbar_init(&bars->acc_done, 1);
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (bars->early_exit != 0) return;
+  if (warp == 9) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  AbortCtx ab{&bars->abort_flag, p.err};
+
+  if (warp == 8) {
+    if (lane == 0 && n_steps > 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_do);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      mbar_arrive_expect_tx(&bars->stat_full[0], kTileBytes);
+      tma_load_4d(k_smem, &tm_k, &bars->stat_full[0], 0, kv_tile * kTile, kv_head, batch);
+      tma_load_4d(k_smem + kHalfBytes, &tm_k, &bars->stat_full[0], 64, kv_tile * kTile, kv_head, batch);
+      mbar_arrive_expect_tx(&bars->stat_full[1], kTileBytes);
+      tma_load_4d(v_smem, &tm_v, &bars->stat_full[1], 0, kv_tile * kTile, kv_head, batch);
+      tma_load_4d(v_smem + kHalfBytes, &tm_v, &bars->stat_full[1], 64, kv_tile * kTile, kv_head, batch);
+      uint32_t it = 0;
+      bool ok = true;
+      for (int g = 0; g < group && ok; ++g) {
+        const int head = kv_head * group + g;
+        for (int e = ebeg; e < eend && ok; ++e) {
+          const int qt = p.entries[e].x;
+          for (int which = 0; which < 2 && ok; ++which, ++it) {
+            const uint32_t s = it % kBwdStages;
+            ok = mbar_wait(&bars->ring_empty[s], ((it / kBwdStages) & 1u) ^ 1u, ab, 0x2100u + s);
+            if (!ok) break;
+            uint8_t* dst = ring + s * kTileBytes;
+            const CUtensorMap* tm = which == 0 ? &tm_q : &tm_do;
+            mbar_arrive_expect_tx(&bars->ring_full[s], kTileBytes);
+            tma_load_4d(dst, tm, &bars->ring_full[s], 0, qt * kTile, head, batch);
+            tma_load_4d(dst + kHalfBytes, tm, &bars->ring_full[s], 64, qt * kTile, head, batch);
+          }
+        }
+      }
+    }
+  } else if (warp == 9) {
+    if (lane == 0 && n_steps > 0) {
+      constexpr uint32_t idesc_kk = make_idesc_bf16(kTile, kTile, false, false);
+      constexpr uint32_t idesc_mn = make_idesc_bf16(kTile, kHeadDim, false, true);
+      const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem), ring_addr = smem_u32(ring);
+      const uint32_t t_st = tmem, t_dpt = tmem + kTile, t_dk = tmem + 2 * kTile, t_dv = tmem + 3 * kTile;
+      auto ss_kmajor = [&](uint32_t d, uint32_t a0, uint32_t b0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_ss(d, make_smem_desc_sw128(a0 + off, 16, 1024), make_smem_desc_sw128(b0 + off, 16, 1024),
+                  idesc_kk, k > 0 ? 1u : 0u);
+        }
+      };
+      auto ts_mn = [&](uint32_t d, uint32_t a_base, uint32_t b0, bool acc) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ts(d, a_base + packed_a_col(k), make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024),
+                  idesc_mn, (acc || k > 0) ? 1u : 0u);
+      };
+      bool ok = mbar_wait(&bars->stat_full[0], 0, ab, 0x2200u) && mbar_wait(&bars->stat_full[1], 0, ab, 0x2201u);
+      for (int n = 0; n < n_steps && ok; ++n) {
+        const uint32_t it_q = 2 * n, it_do = 2 * n + 1;
+        const uint32_t q_slot = ring_addr + (it_q % kBwdStages) * kTileBytes;
+        const uint32_t do_slot = ring_addr + (it_do % kBwdStages) * kTileBytes;
+        ok = mbar_wait(&bars->ring_full[it_q % kBwdStages], (it_q / kBwdStages) & 1u, ab, 0x2210u);
+        if (!ok) break;
+        tc_fence_after();
+        ss_kmajor(t_st, k_addr, q_slot);  // S^T = K Q^T
+        tc_commit(&bars->s_full[0]);
+        ok = mbar_wait(&bars->ring_full[it_do % kBwdStages], (it_do / kBwdStages) & 1u, ab, 0x2211u);
+        if (!ok) break;
+        tc_fence_after();
+        ss_kmajor(t_dpt, v_addr, do_slot);  // dP^T = V dO^T
+        tc_commit(&bars->dp_full);
+        ok = mbar_wait(&bars->p_full, n & 1u, ab, 0x2220u);
+        if (!ok) break;
+        tc_fence_after();
+        ts_mn(t_dv, t_st, do_slot, n > 0);  // dV += P^T dO
+        tc_commit(&bars->ring_empty[it_do % kBwdStages]);
+        ok = mbar_wait(&bars->ds_full, n & 1u, ab, 0x2230u);
+        if (!ok) break;
+        tc_fence_after();
+        ts_mn(t_dk, t_dpt, q_slot, n > 0);  // dK += dS^T Q
+        tc_commit(&bars->ring_empty[it_q % kBwdStages]);
+      }
+      tc_commit(&bars->acc_done);
+    }
+  } else {
+    const int w = warp >> 2;       // q-column half this warpgroup owns
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;  // kv row within the tile
+    const int kv_row = kv_tile * kTile + r;
+    const bool has_seg = p.q_seg != nullptr;
+    const int kv_seg = has_seg ? p.kv_seg[(int64_t)batch * p.kv_len + kv_row] : 0;
+    const int32_t* q_seg_row = has_seg ? p.q_seg + (int64_t)batch * p.q_len : nullptr;
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    const uint32_t t_st = tmem + lane_addr, t_dpt = tmem + lane_addr + kTile;
+    const float c = p.scale_log2;
+    bool ok = true;
+    int n = 0;
+
+    for (int g = 0; g < group && ok; ++g) {
+      const int head = kv_head * group + g;
+      const float* lse_row = p.lse + ((int64_t)batch * p.q_heads + head) * p.q_len;
+      const float* delta_row = p.delta + ((int64_t)batch * p.q_heads + head) * p.q_len;
+      for (int e = ebeg; e < eend; ++e, ++n) {
+        const int4 ent = p.entries[e];
+        const int st = ent.y & 3;
+        const int q0 = ent.x * kTile + w * 64;  // first q column of this half
+        ok = mbar_wait(&bars->s_full[0], n & 1u, ab, 0x2400u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        float pr[64];
+        {
+          uint32_t v[32];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            tmem_ld32(t_st + w * 64 + h * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) pr[h * 32 + j] = __uint_as_float(v[j]);
+          }
+        }
+        if (st == 1) {
+          if (p.fn.kind != SPLASH_MASK_TABLE) {
+            if (p.q_sequence == nullptr) {
+#pragma unroll
+              for (int j = 0; j < 64; ++j) {
+                const RowInterval iv = mask_fn_interval(p.fn, q0 + j);
+                if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
+              }
+            } else {
+#pragma unroll 4
+              for (int j = 0; j < 64; ++j) {
+                const RowInterval iv = mask_fn_interval(p.fn, __ldg(p.q_sequence + q0 + j));
+                if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
+              }
+            }
+          } else {
+            // dkv partial blocks are stored transposed: [id, kv, q]
+            const int8_t* mrow = p.pmb + ((int64_t)ent.z * p.pm_bkv + (kv_row % p.pm_bkv)) * p.pm_bq +
+                                 (q0 % p.pm_bq);
+            const int4* m4 = reinterpret_cast<const int4*>(mrow);
+#pragma unroll
+            for (int h = 0; h < 4; ++h) {
+              const int4 mv = __ldg(m4 + h);
+              const uint32_t wd[4] = {(uint32_t)mv.x, (uint32_t)mv.y, (uint32_t)mv.z, (uint32_t)mv.w};
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (((wd[j >> 2] >> ((j & 3) * 8)) & 0xffu) == 0u) pr[h * 16 + j] = kMaskedLogit;
+            }
+          }
+        }
+        if (has_seg) {
+          const int4* sg4 = reinterpret_cast<const int4*>(q_seg_row + q0);
+#pragma unroll
+          for (int h = 0; h < 16; ++h) {
+            const int4 sv = __ldg(sg4 + h);
+            if (sv.x != kv_seg) pr[h * 4 + 0] = kMaskedLogit;
+            if (sv.y != kv_seg) pr[h * 4 + 1] = kMaskedLogit;
+            if (sv.z != kv_seg) pr[h * 4 + 2] = kMaskedLogit;
+            if (sv.w != kv_seg) pr[h * 4 + 3] = kMaskedLogit;
+          }
+        }
+        {
+          const float4* l4 = reinterpret_cast<const float4*>(lse_row + q0);
+          uint32_t pk[32];
+#pragma unroll
+          for (int h = 0; h < 16; ++h) {
+            const float4 lv = __ldg(l4 + h);
+            pr[h * 4 + 0] = ex2(fmaf(pr[h * 4 + 0], c, -lv.x * kLog2e));
+            pr[h * 4 + 1] = ex2(fmaf(pr[h * 4 + 1], c, -lv.y * kLog2e));
+            pr[h * 4 + 2] = ex2(fmaf(pr[h * 4 + 2], c, -lv.z * kLog2e));
+            pr[h * 4 + 3] = ex2(fmaf(pr[h * 4 + 3], c, -lv.w * kLog2e));
+            pk[h * 2 + 0] = pack_bf16(pr[h * 4 + 0], pr[h * 4 + 1]);
+            pk[h * 2 + 1] = pack_bf16(pr[h * 4 + 2], pr[h * 4 + 3]);
+          }
+          tmem_st32(t_st + packed_col(w), pk);
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(&bars->p_full);
+        }
+        ok = mbar_wait(&bars->dp_full, n & 1u, ab, 0x2410u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        {
+          const float4* d4 = reinterpret_cast<const float4*>(delta_row + q0);
+          uint32_t pk[32];
+          uint32_t v[32];
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            tmem_ld32(t_dpt + w * 64 + h * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const float4 dv = __ldg(d4 + h * 8 + j);
+              const float a0 = pr[h * 32 + 4 * j + 0] * (__uint_as_float(v[4 * j + 0]) - dv.x);
+              const float a1 = pr[h * 32 + 4 * j + 1] * (__uint_as_float(v[4 * j + 1]) - dv.y);
+              const float a2 = pr[h * 32 + 4 * j + 2] * (__uint_as_float(v[4 * j + 2]) - dv.z);
+              const float a3 = pr[h * 32 + 4 * j + 3] * (__uint_as_float(v[4 * j + 3]) - dv.w);
+              pk[h * 16 + 2 * j + 0] = pack_bf16(a0, a1);
+              pk[h * 16 + 2 * j + 1] = pack_bf16(a2, a3);
+            }
+          }
+          tmem_st32(t_dpt + packed_col(w), pk);
+          tmem_st_wait();
+          tc_fence_before();
+          mbar_arrive(&bars->ds_full);
+        }
+      }
+    }
+
+    // epilogue: dK (scaled) and dV halves
+    __nv_bfloat16* dk = p.out0 + (int64_t)batch * p.out0_sb + (int64_t)kv_head * p.out0_sh +
+                        (int64_t)kv_row * p.out0_ss + w * 64;
+    __nv_bfloat16* dv = p.out1 + (int64_t)batch * p.out1_sb + (int64_t)kv_head * p.out1_sh +
+                        (int64_t)kv_row * p.out1_ss + w * 64;
+    if (n_steps > 0) {
+      if (ok) {
+        ok = mbar_wait(&bars->acc_done, 0, ab, 0x2500u);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        tc_fence_after();
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint32_t v[32];
+          tmem_ld32(tmem + lane_addr + 2 * kTile + w * 64 + h * 32, v);
+          tmem_ld_wait();
+          store_row_half(dk + h * 32, v, p.scale);
+          tmem_ld32(tmem + lane_addr + 3 * kTile + w * 64 + h * 32, v);
+          tmem_ld_wait();
+          store_row_half(dv + h * 32, v, 1.0f);
+        }
+      }
+    } else {
+      uint32_t v[32];
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = 0u;
+      store_row_half(dk, v, 0.f);
+      store_row_half(dk + 32, v, 0.f);
+      store_row_half(dv, v, 0.f);
+      store_row_half(dv + 32, v, 0.f);
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host launcher
+// ------------------------------------------------------------------------------------------
+size_t bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {
+  if (batch <= 0 || q_heads <= 0 || q_len <= 0) return 0;
+  const size_t n = (size_t)batch * (size_t)q_heads * (size_t)q_len * sizeof(float);
+  return (n + 255) & ~(size_t)255;
+}
+
+int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
+  int st;
+  const SplashTensor* ts[8] = {&a.q, &a.k, &a.v, &a.o, &a.d_o, &a.dq, &a.dk, &a.dv};
+  for (int i = 0; i < 8; ++i)
+    if ((st = check_bf16_tensor(*ts[i]))) return st;
+  const int64_t B = a.q.size[0], Hq = a.q.size[1], Sq = a.q.size[2], D = a.q.size[3];
+  const int64_t Hkv = a.k.size[1], Skv = a.k.size[2];
+  if (D != kHeadDim) return SPLASH_ERR_UNSUPPORTED;
+  auto same = [](const SplashTensor& x, const SplashTensor& y) {
+    return x.size[0] == y.size[0] && x.size[1] == y.size[1] && x.size[2] == y.size[2] &&
+           x.size[3] == y.size[3];
+  };
+  if (!same(a.q, a.o) || !same(a.q, a.d_o) || !same(a.q, a.dq) || !same(a.k, a.v) ||
+      !same(a.k, a.dk) || !same(a.k, a.dv) || a.k.size[0] != B || a.k.size[3] != D)
+    return SPLASH_ERR_INVALID_ARGUMENT;
+  if (Hkv <= 0 || Hq % Hkv != 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  if (Sq % kTile != 0 || Skv % kTile != 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  if ((a.q_segment_ids == nullptr) != (a.kv_segment_ids == nullptr))
+    return SPLASH_ERR_INVALID_ARGUMENT;
+  if (a.logsumexp == nullptr || a.error_record == nullptr || a.workspace == nullptr)
+    return SPLASH_ERR_INVALID_ARGUMENT;
+  if (a.workspace_bytes < bwd_workspace_bytes(B, Hq, Sq)) return SPLASH_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  if (a.sched_dq.row_ptr == nullptr || a.sched_dq.entries == nullptr ||
+      a.sched_dkv.row_ptr == nullptr || a.sched_dkv.entries == nullptr)
+    return SPLASH_ERR_INVALID_ARGUMENT;
+  if (a.sched_dq.n_rows != Sq / kTile || a.sched_dkv.n_rows != Skv / kTile)
+    return SPLASH_ERR_INVALID_ARGUMENT;
+  if (a.mask_fn.kind == SPLASH_MASK_CHUNKED && a.mask_fn.chunk <= 0)
+    return SPLASH_ERR_INVALID_ARGUMENT;
+  if (Hq > 65535 || B > 65535) return SPLASH_ERR_TOO_LARGE;
+
+  CUtensorMap tm_q, tm_do, tm_k, tm_v;
+  if ((st = make_tile_tensor_map(&tm_q, a.q, kTile)) || (st = make_tile_tensor_map(&tm_do, a.d_o, kTile)) ||
+      (st = make_tile_tensor_map(&tm_k, a.k, kTile)) || (st = make_tile_tensor_map(&tm_v, a.v, kTile)))
+    return st;
+
+  float* delta = static_cast<float*>(a.workspace);
+  {
+    DeltaParams dp;
+    dp.o = static_cast<const __nv_bfloat16*>(a.o.data);
+    dp.d_o = static_cast<const __nv_bfloat16*>(a.d_o.data);
+    dp.o_sb = a.o.stride[0];
+    dp.o_sh = a.o.stride[1];
+    dp.o_ss = a.o.stride[2];
+    dp.do_sb = a.d_o.stride[0];
+    dp.do_sh = a.d_o.stride[1];
+    dp.do_ss = a.d_o.stride[2];
+    dp.delta = delta;
+    dp.q_heads = (int)Hq;
+    dp.q_len = (int)Sq;
+    dp.n_rows = B * Hq * Sq;
+    const unsigned blocks = (unsigned)((dp.n_rows + 7) / 8);
+    splash_delta_kernel<<<blocks, 256, 0, stream>>>(dp);
+    if (cudaGetLastError() != cudaSuccess) return SPLASH_ERR_CUDA;
+  }
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(splash_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kBwdSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(splash_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kBwdSmemBytes) != cudaSuccess)
+      return SPLASH_ERR_CUDA;
+    attr_set = true;
+  }
+
+  BwdParams p;
+  p.lse = a.logsumexp;
+  p.delta = delta;
+  p.q_seg = a.q_segment_ids;
+  p.kv_seg = a.kv_segment_ids;
+  p.q_sequence = a.q_sequence;
+  p.fn = a.mask_fn;
+  p.q_len = (int)Sq;
+  p.kv_len = (int)Skv;
+  p.q_heads = (int)Hq;
+  p.kv_heads = (int)Hkv;
+  p.scale = a.scale;
+  p.scale_log2 = a.scale * kLog2e;
+  p.err = a.error_record;
+
+  // dq
+  p.out0 = static_cast<__nv_bfloat16*>(a.dq.data);
+  p.out0_sb = a.dq.stride[0];
+  p.out0_sh = a.dq.stride[1];
+  p.out0_ss = a.dq.stride[2];
+  p.out1 = nullptr;
+  p.out1_sb = p.out1_sh = p.out1_ss = 0;
+  p.row_ptr = a.sched_dq.row_ptr;
+  p.entries = reinterpret_cast<const int4*>(a.sched_dq.entries);
+  p.pmb = a.sched_dq.partial_mask_blocks;
+  p.pm_bq = a.sched_dq.block_q > 0 ? a.sched_dq.block_q : kTile;
+  p.pm_bkv = a.sched_dq.block_kv > 0 ? a.sched_dq.block_kv : kTile;
+  p.n_rows = a.sched_dq.n_rows;
+  splash_dq_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hq, (unsigned)B), kBwdThreads, kBwdSmemBytes,
+                     stream>>>(tm_q, tm_do, tm_k, tm_v, p);
+  if (cudaGetLastError() != cudaSuccess) return SPLASH_ERR_CUDA;
+
+  // dkv
+  p.out0 = static_cast<__nv_bfloat16*>(a.dk.data);
+  p.out0_sb = a.dk.stride[0];
+  p.out0_sh = a.dk.stride[1];
+  p.out0_ss = a.dk.stride[2];
+  p.out1 = static_cast<__nv_bfloat16*>(a.dv.data);
+  p.out1_sb = a.dv.stride[0];
+  p.out1_sh = a.dv.stride[1];
+  p.out1_ss = a.dv.stride[2];
+  p.row_ptr = a.sched_dkv.row_ptr;
+  p.entries = reinterpret_cast<const int4*>(a.sched_dkv.entries);
+  p.pmb = a.sched_dkv.partial_mask_blocks;
+  p.pm_bq = a.sched_dkv.block_q > 0 ? a.sched_dkv.block_q : kTile;
+  p.pm_bkv = a.sched_dkv.block_kv > 0 ? a.sched_dkv.block_kv : kTile;
+  p.n_rows = a.sched_dkv.n_rows;
+  splash_dkv_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hkv, (unsigned)B), kBwdThreads, kBwdSmemBytes,
+                      stream>>>(tm_q, tm_do, tm_k, tm_v, p);
+  return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
+}
+
+}  // namespace sb

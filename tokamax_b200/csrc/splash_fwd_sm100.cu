@@ -1,0 +1,468 @@
+// Splash attention forward for sm_100a: bf16 Q/K/V, head_dim 128, fp32 accumulation.
+//
+// One CTA owns two adjacent 128-row q tiles of one (batch, q head) and walks the kv tiles its
+// schedule row lists.  Roles (320 threads):
+//   warps 0-3 / 4-7 : softmax warpgroup of q tile 0 / 1 — one thread per score row
+//   warp 8          : TMA producer (Q once, then a 4-slot ring of K and V tiles)
+//   warp 9          : tcgen05 MMA issuer (and TMEM allocator)
+// TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  P (bf16, two values per
+// column) overwrites the first 64 columns of its S tile and feeds the PV MMA straight from TMEM.
+// The two tiles ping-pong: while the softmax of tile 0 runs on the SIMT lanes, the tensor core
+// computes QK^T of tile 1 and PV of the previous step.
+//
+// Online softmax keeps a possibly stale running maximum: O and l are rescaled only when the
+// new row maximum exceeds the one in use by more than 2^8, which keeps the TMEM round trip of
+// O off the common path.  logsumexp is exact regardless (it is formed from the maximum in use
+// and the matching l).
+//
+// Follows the arithmetic of the reference forward kernel
+// (tokamax/_src/ops/experimental/tpu/splash_attention/splash_attention_kernel.py:299-527,
+// masking :202-296) with the softmax scale applied in fp32 inside the kernel.
+#include "splash_common.cuh"
+
+namespace sb {
+
+constexpr int kFwdStages = 4;
+constexpr int kFwdThreads = 320;
+constexpr float kRescaleThreshold = 8.0f;  // log2 units
+
+struct FwdParams {
+  __nv_bfloat16* o;
+  int64_t o_sb, o_sh, o_ss;
+  float* lse;
+  float* maxl;
+  const int32_t* q_seg;
+  const int32_t* kv_seg;
+  const int32_t* q_sequence;
+  const int32_t* row_ptr;
+  const int4* entries;
+  const int8_t* pmb;
+  int pm_bq, pm_bkv;
+  SplashMaskFn fn;
+  int q_len, kv_len, q_heads, kv_heads, n_q_tiles, n_rows;
+  float scale, scale_log2, mask_value;
+  uint32_t* err;
+};
+
+struct FwdBarriers {
+  uint64_t q_full[2];
+  uint64_t kv_full[kFwdStages];
+  uint64_t kv_empty[kFwdStages];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t o_done[2];
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  uint32_t early_exit;
+};
+
+constexpr int kFwdSmemBytes = 2 * kTileBytes + kFwdStages * kTileBytes + 1024 /*barriers*/ +
+                              1024 /*alignment slack*/;
+
+__global__ void __launch_bounds__(kFwdThreads, 1)
+splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                  const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* q_smem = smem;                                  // 2 tiles
+  uint8_t* kv_smem = smem + 2 * kTileBytes;                // ring
+  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(smem + (2 + kFwdStages) * kTileBytes);
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int row = p.n_rows - 1 - (int)blockIdx.x;  // long causal rows first
+  const int head = blockIdx.y;
+  const int batch = blockIdx.z;
+  const int kv_head = head / (p.q_heads / p.kv_heads);
+  const int ebeg = p.row_ptr[row];
+  const int eend = p.row_ptr[row + 1];
+  const int qt0 = row * 2;
+
+  if (threadIdx.x == 0) {
+    bars->early_exit = *reinterpret_cast<volatile uint32_t*>(p.err);
+    bars->abort_flag = 0;
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->q_full[i], 1);
+      mbar_init(&bars->s_full[i], 1);
+      mbar_init(&bars->p_full[i], 128);
+      mbar_init(&bars->o_done[i], 1);
+    }
+    for (int s = 0; s < kFwdStages; ++s) {
+      mbar_init(&bars->kv_full[s], 1);
+      mbar_init(&bars->kv_empty[s], 1);
+    }
+    mbar_fence_init();
+  }
+  __syncthreads();
+  if (bars->early_exit != 0) return;  // an earlier CTA already reported a fault
+
+  if (warp == 9) {
+    tmem_alloc(&bars->tmem_base, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = bars->tmem_base;
+  AbortCtx ab{&bars->abort_flag, p.err};
+
+  if (warp == 8) {
+    // ------------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      tma_prefetch_desc(&tm_q);
+      tma_prefetch_desc(&tm_k);
+      tma_prefetch_desc(&tm_v);
+      for (int i = 0; i < 2; ++i) {
+        if (qt0 + i < p.n_q_tiles) {
+          uint8_t* dst = q_smem + i * kTileBytes;
+          mbar_arrive_expect_tx(&bars->q_full[i], kTileBytes);
+          tma_load_4d(dst, &tm_q, &bars->q_full[i], 0, (qt0 + i) * kTile, head, batch);
+          tma_load_4d(dst + kHalfBytes, &tm_q, &bars->q_full[i], 64, (qt0 + i) * kTile, head, batch);
+        }
+      }
+      uint32_t it = 0;
+      bool ok = true;
+      for (int e = ebeg; e < eend && ok; ++e) {
+        const int col = p.entries[e].x;
+        for (int kv = 0; kv < 2 && ok; ++kv, ++it) {
+          const uint32_t s = it % kFwdStages;
+          const uint32_t ph = (it / kFwdStages) & 1u;
+          ok = mbar_wait(&bars->kv_empty[s], ph ^ 1u, ab, 0x100u + s);
+          if (!ok) break;
+          uint8_t* dst = kv_smem + s * kTileBytes;
+          const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
+          mbar_arrive_expect_tx(&bars->kv_full[s], kTileBytes);
+          tma_load_4d(dst, tm, &bars->kv_full[s], 0, col * kTile, kv_head, batch);
+          tma_load_4d(dst + kHalfBytes, tm, &bars->kv_full[s], 64, col * kTile, kv_head, batch);
+        }
+      }
+    }
+  } else if (warp == 9) {
+    // ------------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(kTile, kTile, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(kTile, kHeadDim, false, true);
+      const uint32_t q_addr = smem_u32(q_smem);
+      const uint32_t kv_addr = smem_u32(kv_smem);
+      bool ok = true;
+      for (int i = 0; i < 2 && ok; ++i)
+        if (qt0 + i < p.n_q_tiles) ok = mbar_wait(&bars->q_full[i], 0, ab, 0x200u + i);
+
+      // S_i = Q_i K^T : both operands K-major, eight K=16 slices across two swizzle halves.
+      auto issue_qk = [&](int i, uint32_t slot) {
+        const uint32_t a0 = q_addr + i * kTileBytes;
+        const uint32_t b0 = kv_addr + slot * kTileBytes;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_ss(tmem + i * kTile, make_smem_desc_sw128(a0 + off, 16, 1024),
+                  make_smem_desc_sw128(b0 + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+        }
+        tc_commit(&bars->s_full[i]);
+      };
+      // O_i (+)= P_i V : A from TMEM, B = V tile read MN-major (head_dim contiguous):
+      // 8 kv rows x 128 B per core group (SBO 1024), 64-column halves 16 KiB apart (LBO).
+      auto issue_pv = [&](int i, uint32_t slot, bool acc) {
+        const uint32_t b0 = kv_addr + slot * kTileBytes;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          umma_ts(tmem + 2 * kTile + i * kTile, tmem + i * kTile + k * 8,
+                  make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024), idesc_pv,
+                  (acc || k > 0) ? 1u : 0u);
+        }
+      };
+
+      const int n_ent = eend - ebeg;
+      uint32_t pcnt[2] = {0, 0};
+      bool started[2] = {false, false};
+      if (n_ent > 0 && ok) {
+        const int4 e0 = p.entries[ebeg];
+        ok = mbar_wait(&bars->kv_full[0], 0, ab, 0x300u);
+        if (ok) {
+          tc_fence_after();
+          for (int i = 0; i < 2; ++i)
+            if ((e0.y >> (2 * i)) & 3) issue_qk(i, 0);
+          tc_commit(&bars->kv_empty[0]);
+        }
+        for (int n = 0; n < n_ent && ok; ++n) {
+          const int4 cur = p.entries[ebeg + n];
+          const bool has_next = n + 1 < n_ent;
+          int4 nxt = cur;
+          if (has_next) nxt = p.entries[ebeg + n + 1];
+          const uint32_t itv = 2 * n + 1, itk = 2 * n + 2;
+          const uint32_t vslot = itv % kFwdStages, kslot = itk % kFwdStages;
+          ok = mbar_wait(&bars->kv_full[vslot], (itv / kFwdStages) & 1u, ab, 0x310u + vslot);
+          if (ok && has_next)
+            ok = mbar_wait(&bars->kv_full[kslot], (itk / kFwdStages) & 1u, ab, 0x320u + kslot);
+          if (!ok) break;
+          tc_fence_after();
+          for (int i = 0; i < 2 && ok; ++i) {
+            if ((cur.y >> (2 * i)) & 3) {
+              ok = mbar_wait(&bars->p_full[i], pcnt[i] & 1u, ab, 0x330u + i);
+              if (!ok) break;
+              ++pcnt[i];
+              tc_fence_after();
+              issue_pv(i, vslot, started[i]);
+              started[i] = true;
+            }
+            if (i == 1) tc_commit(&bars->kv_empty[vslot]);
+            if (has_next && ((nxt.y >> (2 * i)) & 3)) issue_qk(i, kslot);
+          }
+          if (ok && has_next) tc_commit(&bars->kv_empty[kslot]);
+        }
+      }
+      tc_commit(&bars->o_done[0]);
+      tc_commit(&bars->o_done[1]);
+    }
+  } else {
+    // ------------------------------------------------------------------ softmax warpgroups
+    const int i = warp >> 2;           // q tile within the pair
+    const int wq = warp & 3;           // TMEM lane quarter this warp may touch
+    const int r = wq * 32 + lane;      // row within the tile
+    const int q_tile = qt0 + i;
+    const bool valid = q_tile < p.n_q_tiles;
+    const int q_row = valid ? q_tile * kTile + r : 0;
+    const int qi = p.q_sequence ? p.q_sequence[q_row] : q_row;
+    const RowInterval iv = mask_fn_interval(p.fn, qi);
+    const bool has_seg = p.q_seg != nullptr;
+    const int q_seg = has_seg ? p.q_seg[(int64_t)batch * p.q_len + q_row] : 0;
+    const int32_t* kv_seg_row = has_seg ? p.kv_seg + (int64_t)batch * p.kv_len : nullptr;
+    const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    const uint32_t t_s = tmem + lane_addr + i * kTile;
+    const uint32_t t_o = tmem + lane_addr + 2 * kTile + i * kTile;
+    const float c = p.scale_log2;
+
+    float m_used = -INFINITY;  // scaled (log2) units
+    float m_true = kMaskedLogit;
+    float l = 0.f;
+    uint32_t cnt = 0;
+    bool started = false;
+    bool ok = true;
+
+    for (int e = ebeg; e < eend; ++e) {
+      const int4 ent = p.entries[e];
+      const int st = (ent.y >> (2 * i)) & 3;
+      if (st == 0) continue;
+      ok = mbar_wait(&bars->s_full[i], cnt & 1u, ab, 0x400u + i);
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
+      ++cnt;
+      tc_fence_after();
+
+      float s[kTile];
+      {
+        uint32_t v[32];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          tmem_ld32(t_s + g * 32, v);
+          tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) s[g * 32 + j] = __uint_as_float(v[j]);
+        }
+      }
+      const int kv0 = ent.x * kTile;
+      if (st == 1) {
+        if (p.fn.kind != SPLASH_MASK_TABLE) {
+          const int lo_rel = iv.lo <= kv0 ? 0 : iv.lo - kv0;
+          const int hi_rel = iv.hi >= kv0 + (kTile - 1) ? kTile - 1 : iv.hi - kv0;
+#pragma unroll
+          for (int j = 0; j < kTile; ++j)
+            if (j < lo_rel || j > hi_rel) s[j] = kMaskedLogit;
+        } else {
+          const int pid = i == 0 ? ent.z : ent.w;
+          const int8_t* mrow = p.pmb + ((int64_t)pid * p.pm_bq + (q_row % p.pm_bq)) * p.pm_bkv +
+                               (kv0 % p.pm_bkv);
+          const int4* m4 = reinterpret_cast<const int4*>(mrow);
+#pragma unroll
+          for (int g = 0; g < 8; ++g) {
+            const int4 mv = __ldg(m4 + g);
+            const uint32_t w[4] = {(uint32_t)mv.x, (uint32_t)mv.y, (uint32_t)mv.z, (uint32_t)mv.w};
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+              if (((w[j >> 2] >> ((j & 3) * 8)) & 0xffu) == 0u) s[g * 16 + j] = kMaskedLogit;
+          }
+        }
+      }
+      if (has_seg) {
+        const int4* sg4 = reinterpret_cast<const int4*>(kv_seg_row + kv0);
+#pragma unroll
+        for (int g = 0; g < 32; ++g) {
+          const int4 sv = __ldg(sg4 + g);
+          if (sv.x != q_seg) s[g * 4 + 0] = kMaskedLogit;
+          if (sv.y != q_seg) s[g * 4 + 1] = kMaskedLogit;
+          if (sv.z != q_seg) s[g * 4 + 2] = kMaskedLogit;
+          if (sv.w != q_seg) s[g * 4 + 3] = kMaskedLogit;
+        }
+      }
+
+      float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+#pragma unroll
+      for (int j = 4; j < kTile; j += 4) {
+        mx0 = fmaxf(mx0, s[j]);
+        mx1 = fmaxf(mx1, s[j + 1]);
+        mx2 = fmaxf(mx2, s[j + 2]);
+        mx3 = fmaxf(mx3, s[j + 3]);
+      }
+      const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
+      m_true = fmaxf(m_true, mx);
+      const float m_new = mx * c;
+      const bool need = m_new > m_used + kRescaleThreshold;
+      if (__any_sync(0xffffffffu, need)) {
+        const float m_next = fmaxf(m_used, m_new);
+        const float alpha = ex2(m_used - m_next);
+        l *= alpha;
+        if (started) {
+          uint32_t v[32];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            tmem_ld32(t_o + g * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = __float_as_uint(__uint_as_float(v[j]) * alpha);
+            tmem_st32(t_o + g * 32, v);
+          }
+        }
+        m_used = m_next;
+      }
+
+      float ls0 = 0.f, ls1 = 0.f;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint32_t pk[16];
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float p0 = ex2(fmaf(s[g * 32 + 2 * j], c, -m_used));
+          const float p1 = ex2(fmaf(s[g * 32 + 2 * j + 1], c, -m_used));
+          ls0 += p0;
+          ls1 += p1;
+          pk[j] = pack_bf16(p0, p1);
+        }
+        tmem_st16(t_s + g * 16, pk);
+      }
+      l += ls0 + ls1;
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(&bars->p_full[i]);
+      started = true;
+    }
+
+    // ---- epilogue: O / l -> bf16, logsumexp, max_logits
+    if (ok) {
+      ok = mbar_wait(&bars->o_done[i], 0, ab, 0x500u + i);
+      ok = __all_sync(0xffffffffu, ok);
+    }
+    if (ok && valid) {
+      tc_fence_after();
+      __nv_bfloat16* orow = p.o + (int64_t)batch * p.o_sb + (int64_t)head * p.o_sh +
+                            (int64_t)q_row * p.o_ss;
+      uint4* o4 = reinterpret_cast<uint4*>(orow);
+      const float inv = started ? 1.0f / l : 0.f;
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        uint32_t v[32];
+        if (started) {
+          tmem_ld32(t_o + g * 32, v);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) v[j] = 0u;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          uint4 w;
+          w.x = pack_bf16(__uint_as_float(v[8 * j + 0]) * inv, __uint_as_float(v[8 * j + 1]) * inv);
+          w.y = pack_bf16(__uint_as_float(v[8 * j + 2]) * inv, __uint_as_float(v[8 * j + 3]) * inv);
+          w.z = pack_bf16(__uint_as_float(v[8 * j + 4]) * inv, __uint_as_float(v[8 * j + 5]) * inv);
+          w.w = pack_bf16(__uint_as_float(v[8 * j + 6]) * inv, __uint_as_float(v[8 * j + 7]) * inv);
+          o4[g * 4 + j] = w;
+        }
+      }
+      const int64_t stat = ((int64_t)batch * p.q_heads + head) * p.q_len + q_row;
+      if (p.lse) p.lse[stat] = started ? (m_used + log2f(l)) * kLn2 : p.mask_value;
+      if (p.maxl) p.maxl[stat] = started ? m_true * p.scale : p.mask_value;
+    }
+  }
+
+  // ---- teardown
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 9) {
+    __syncwarp();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// host launcher
+// ------------------------------------------------------------------------------------------
+int launch_fwd(const SplashFwdArgs& a, cudaStream_t stream) {
+  int st;
+  if ((st = check_bf16_tensor(a.q)) || (st = check_bf16_tensor(a.k)) ||
+      (st = check_bf16_tensor(a.v)) || (st = check_bf16_tensor(a.o)))
+    return st;
+  const int64_t B = a.q.size[0], Hq = a.q.size[1], Sq = a.q.size[2], D = a.q.size[3];
+  const int64_t Hkv = a.k.size[1], Skv = a.k.size[2];
+  if (D != kHeadDim || a.k.size[3] != kHeadDim || a.v.size[3] != kHeadDim)
+    return SPLASH_ERR_UNSUPPORTED;
+  if (a.k.size[0] != B || a.v.size[0] != B || a.o.size[0] != B) return SPLASH_ERR_INVALID_ARGUMENT;
+  if (a.v.size[1] != Hkv || a.v.size[2] != Skv || a.o.size[1] != Hq || a.o.size[2] != Sq ||
+      a.o.size[3] != D)
+    return SPLASH_ERR_INVALID_ARGUMENT;
+  if (Hkv <= 0 || Hq % Hkv != 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  if (Sq % kTile != 0 || Skv % kTile != 0 || Sq <= 0 || Skv <= 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  if ((a.q_segment_ids == nullptr) != (a.kv_segment_ids == nullptr))
+    return SPLASH_ERR_INVALID_ARGUMENT;
+  if (a.error_record == nullptr || a.sched.row_ptr == nullptr || a.sched.entries == nullptr)
+    return SPLASH_ERR_INVALID_ARGUMENT;
+  const int n_q_tiles = (int)(Sq / kTile);
+  if (a.sched.n_rows != (n_q_tiles + 1) / 2) return SPLASH_ERR_INVALID_ARGUMENT;
+  if (a.mask_fn.kind == SPLASH_MASK_CHUNKED && a.mask_fn.chunk <= 0)
+    return SPLASH_ERR_INVALID_ARGUMENT;
+  if (Hq > 65535 || B > 65535) return SPLASH_ERR_TOO_LARGE;
+
+  CUtensorMap tm_q, tm_k, tm_v;
+  if ((st = make_tile_tensor_map(&tm_q, a.q, kTile)) || (st = make_tile_tensor_map(&tm_k, a.k, kTile)) ||
+      (st = make_tile_tensor_map(&tm_v, a.v, kTile)))
+    return st;
+
+  FwdParams p;
+  p.o = static_cast<__nv_bfloat16*>(a.o.data);
+  p.o_sb = a.o.stride[0];
+  p.o_sh = a.o.stride[1];
+  p.o_ss = a.o.stride[2];
+  p.lse = a.logsumexp;
+  p.maxl = a.max_logits;
+  p.q_seg = a.q_segment_ids;
+  p.kv_seg = a.kv_segment_ids;
+  p.q_sequence = a.q_sequence;
+  p.row_ptr = a.sched.row_ptr;
+  p.entries = reinterpret_cast<const int4*>(a.sched.entries);
+  p.pmb = a.sched.partial_mask_blocks;
+  p.pm_bq = a.sched.block_q > 0 ? a.sched.block_q : kTile;
+  p.pm_bkv = a.sched.block_kv > 0 ? a.sched.block_kv : kTile;
+  p.fn = a.mask_fn;
+  p.q_len = (int)Sq;
+  p.kv_len = (int)Skv;
+  p.q_heads = (int)Hq;
+  p.kv_heads = (int)Hkv;
+  p.n_q_tiles = n_q_tiles;
+  p.n_rows = a.sched.n_rows;
+  p.scale = a.scale;
+  p.scale_log2 = a.scale * kLog2e;
+  p.mask_value = a.mask_value;
+  p.err = a.error_record;
+
+  static bool attr_set = false;
+  if (!attr_set) {
+    if (cudaFuncSetAttribute(splash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             kFwdSmemBytes) != cudaSuccess)
+      return SPLASH_ERR_CUDA;
+    attr_set = true;
+  }
+  dim3 grid((unsigned)p.n_rows, (unsigned)Hq, (unsigned)B);
+  splash_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
+}
+
+}  // namespace sb

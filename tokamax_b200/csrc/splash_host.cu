@@ -1,0 +1,113 @@
+// Host side of the C ABI: argument checks, TMA tensor maps, status strings, error read-back.
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "splash_common.cuh"
+
+namespace sb {
+
+int launch_fwd(const SplashFwdArgs& a, cudaStream_t stream);
+int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream);
+size_t bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static std::mutex mu;
+  static EncodeTiledFn fn = nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (fn == nullptr) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) ==
+            cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  }
+  return fn;
+}
+
+int check_bf16_tensor(const SplashTensor& t) {
+  if (t.data == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;
+  if (t.dtype != SPLASH_BF16) return SPLASH_ERR_UNSUPPORTED;
+  if (t.stride[3] != 1) return SPLASH_ERR_INVALID_ARGUMENT;
+  for (int i = 0; i < 4; ++i)
+    if (t.size[i] <= 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  for (int i = 0; i < 3; ++i)
+    if (t.stride[i] % 8 != 0 || t.stride[i] < 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(t.data) & 15u) != 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  return SPLASH_OK;
+}
+
+// Tensor map over (head_dim, seq, heads, batch) with a (64 x box_rows) box and 128-byte
+// swizzle: one box is one swizzle half of an MMA operand tile.
+int make_tile_tensor_map(CUtensorMap* out, const SplashTensor& t, int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (enc == nullptr) return SPLASH_ERR_NO_DEVICE;
+  const cuuint64_t dims[4] = {(cuuint64_t)t.size[3], (cuuint64_t)t.size[2], (cuuint64_t)t.size[1],
+                              (cuuint64_t)t.size[0]};
+  // A size-1 dimension may carry any stride; give it a legal one.
+  auto stride_bytes = [&](int i) -> cuuint64_t {
+    cuuint64_t s = (cuuint64_t)t.stride[i] * 2u;
+    if (s == 0) s = 16;
+    return s;
+  };
+  const cuuint64_t strides[3] = {stride_bytes(2), stride_bytes(1), stride_bytes(0)};
+  const cuuint32_t box[4] = {64u, (cuuint32_t)box_rows, 1u, 1u};
+  const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.data, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? SPLASH_OK : SPLASH_ERR_CUDA;
+}
+
+}  // namespace sb
+
+extern "C" {
+
+int splash_fwd(const SplashFwdArgs* args, void* cuda_stream) {
+  if (args == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;
+  return sb::launch_fwd(*args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+size_t splash_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {
+  return sb::bwd_workspace_bytes(batch, q_heads, q_len);
+}
+
+int splash_bwd(const SplashBwdArgs* args, void* cuda_stream) {
+  if (args == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;
+  return sb::launch_bwd(*args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int splash_read_error(const uint32_t* error_record, void* cuda_stream, uint32_t record_out[4]) {
+  if (error_record == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;
+  uint32_t host[4] = {0, 0, 0, 0};
+  cudaStream_t s = static_cast<cudaStream_t>(cuda_stream);
+  if (cudaMemcpyAsync(host, error_record, sizeof(host), cudaMemcpyDeviceToHost, s) != cudaSuccess)
+    return SPLASH_ERR_CUDA;
+  if (cudaStreamSynchronize(s) != cudaSuccess) return SPLASH_ERR_CUDA;
+  if (record_out != nullptr) std::memcpy(record_out, host, sizeof(host));
+  return host[0] == 0 ? SPLASH_OK : SPLASH_ERR_KERNEL_TIMEOUT;
+}
+
+const char* splash_status_str(int status) {
+  switch (status) {
+    case SPLASH_OK: return "ok";
+    case SPLASH_ERR_INVALID_ARGUMENT: return "invalid argument (shape, stride, alignment or table)";
+    case SPLASH_ERR_UNSUPPORTED: return "unsupported configuration (NotImplementedError)";
+    case SPLASH_ERR_CUDA: return "CUDA call failed";
+    case SPLASH_ERR_NO_DEVICE: return "no usable sm_100 device or driver entry point";
+    case SPLASH_ERR_KERNEL_TIMEOUT: return "device-side bounded wait ran out";
+    case SPLASH_ERR_OUT_OF_MEMORY: return "host allocation failed";
+    case SPLASH_ERR_TOO_LARGE: return "size beyond a built-in limit";
+    default: return "unknown status";
+  }
+}
+
+const char* splash_version(void) { return "splash_b200 0.1 sm_100a"; }
+
+}  // extern "C"
