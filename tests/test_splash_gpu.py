@@ -1,0 +1,272 @@
+"""GPU parity tests: the CUDA kernels (through the Python API -> C ABI) against the CPU oracle.
+
+Tolerances are the ones the task states: forward output max-abs <= 1e-2, logsumexp <= 1e-3
+against the fp32 oracle; dQ / dK / dV relative L2 <= 1e-2.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention_ref
+from tokamax_b200 import _native
+from tokamax_b200 import splash_attention_kernel as splash
+from tokamax_b200 import splash_attention_mask as mask_lib
+
+pytestmark = pytest.mark.gpu
+
+O_ATOL, LSE_ATOL, GRAD_REL = 1e-2, 1e-3, 1e-2
+D = 128
+
+
+def _inputs(seed, b, hq, hkv, sq, skv, mqa=False):
+  g = torch.Generator().manual_seed(seed)
+  mk = lambda *s: torch.randn(*s, generator=g, dtype=torch.float32).to(torch.bfloat16)
+  q, do = mk(b, hq, sq, D), mk(b, hq, sq, D)
+  if mqa:
+    k, v = mk(b, skv, D), mk(b, skv, D)
+  else:
+    k, v = mk(b, hkv, skv, D), mk(b, hkv, skv, D)
+  return q, k, v, do
+
+
+def _dense(mask):
+  q, kv = mask.shape
+  return np.asarray(mask[(slice(0, q), slice(0, kv))]).astype(np.bool_)
+
+
+def _rel(a, ref):
+  return ((a.float().cpu() - ref).norm() / ref.norm().clamp_min(1e-20)).item()
+
+
+def _run_and_compare(kernel, mask_dense, q, k, v, do, seg=None, scale=1.0 / math.sqrt(D)):
+  dev = torch.device("cuda:0")
+  qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+  seg_dev = None if seg is None else splash.SegmentIds(seg[0].to(dev), seg[1].to(dev))
+  out, res = kernel(qd, kd, vd, seg_dev, logits_scale=scale, save_residuals=True)
+  out.backward(do.to(dev))
+  kernel.check_errors()
+  k4 = k if k.dim() == 4 else k[:, None]
+  v4 = v if v.dim() == 4 else v[:, None]
+  ro, rlse, rmax, rdq, rdk, rdv = attention_ref.fwd_bwd(q, k4, v4, do, mask_dense, seg, scale=scale)
+  assert (out.float().cpu() - ro).abs().max().item() <= O_ATOL
+  assert (res["logsumexp"].cpu() - rlse).abs().max().item() <= LSE_ATOL
+  assert (res["max_logits"].cpu() - rmax).abs().max().item() <= 1e-3 * max(1.0, rmax.abs().max().item())
+  dk, dv = kd.grad, vd.grad
+  if k.dim() == 3:
+    dk, dv = dk[:, None], dv[:, None]
+  assert _rel(qd.grad, rdq) <= GRAD_REL
+  assert _rel(dk, rdk) <= GRAD_REL
+  assert _rel(dv, rdv) <= GRAD_REL
+  return out, res, qd.grad, dk, dv
+
+
+def test_library_loaded_and_identifies_itself():
+  assert b"sm_100a" in _native.lib().splash_version()
+
+
+def test_c1_causal_mha_1024():
+  """BASELINE config 1: causal, B=2, Hq=Hkv=8, S=1024, D=128."""
+  q, k, v, do = _inputs(1000, 2, 8, 8, 1024, 1024)
+  mask = mask_lib.CausalMask((1024, 1024))
+  kernel = splash.make_splash_mha(mask, q_seq_shards=1)
+  _run_and_compare(kernel, _dense(mask), q, k, v, do)
+
+
+@pytest.mark.parametrize("hq,hkv", [(8, 2), (4, 1), (6, 2)])
+def test_gqa_causal(hq, hkv):
+  q, k, v, do = _inputs(7, 1, hq, hkv, 512, 512)
+  mask = mask_lib.CausalMask((512, 512))
+  _run_and_compare(splash.make_splash_mha(mask, q_seq_shards=1), _dense(mask), q, k, v, do)
+
+
+def test_mqa_unbatched():
+  q, k, v, do = _inputs(11, 1, 4, 1, 384, 384, mqa=True)
+  mask = mask_lib.CausalMask((384, 384))
+  kernel = splash.make_splash_mqa(mask, q_seq_shards=1, save_residuals=True)
+  dev = torch.device("cuda:0")
+  out, res = kernel(q[0].to(dev), k[0].to(dev), v[0].to(dev), logits_scale=0.1)
+  ro, rlse, _ = attention_ref.attention_reference(q[0], k[0], v[0], _dense(mask), scale=0.1)
+  assert out.shape == (4, 384, D) and res["logsumexp"].shape == (4, 384)
+  assert (out.float().cpu() - ro).abs().max().item() <= O_ATOL
+  assert (res["logsumexp"].cpu() - rlse).abs().max().item() <= LSE_ATOL
+  q4, k4, v4, do4 = q, k, v, do
+  _run_and_compare(splash.make_splash_mqa(mask, q_seq_shards=1), _dense(mask), q4, k4, v4, do4)
+
+
+MASKS = {
+    "full": lambda s: mask_lib.FullMask((s, s)),
+    "local_lazy": lambda s: mask_lib.LocalMask((s, s), (200, 72), 0),
+    "local_causal_lazy": lambda s: mask_lib.LocalMask((s, s), (300, 0), 0),
+    "chunked_lazy": lambda s: mask_lib.ChunkedCausalMask((s, s), 192),
+    "causal_offset": lambda s: mask_lib.CausalMask((s, s), 37),
+    "and_local_causal": lambda s: mask_lib.LocalMask((s, s), (260, None), 0) & mask_lib.CausalMask((s, s)),
+    "or_chunk_local": lambda s: mask_lib.ChunkedCausalMask((s, s), 256) | mask_lib.LocalMask((s, s), (40, 40), 0),
+    "random_or_diag": lambda s: mask_lib.NumpyMask(mask_lib.make_random_mask((s, s), 0.7, 5))
+    | mask_lib.LocalMask((s, s), (0, 0), 0),
+    "numpy_causal": lambda s: mask_lib.NumpyMask(mask_lib.make_causal_mask((s, s))),
+}
+
+
+@pytest.mark.parametrize("name", sorted(MASKS))
+def test_mask_kinds(name):
+  s = 768
+  q, k, v, do = _inputs(3, 1, 4, 2, s, s)
+  mask = MASKS[name](s)
+  _run_and_compare(splash.make_splash_mha(mask, q_seq_shards=1), _dense(mask), q, k, v, do)
+
+
+def test_rectangular_cross_attention():
+  q, k, v, do = _inputs(5, 2, 2, 2, 256, 640)
+  mask = mask_lib.CausalMask((256, 640), offset=384)
+  _run_and_compare(splash.make_splash_mha(mask, q_seq_shards=1), _dense(mask), q, k, v, do)
+
+
+def test_odd_number_of_q_tiles():
+  q, k, v, do = _inputs(6, 1, 2, 1, 384, 384)
+  mask = mask_lib.CausalMask((384, 384))
+  _run_and_compare(splash.make_splash_mha(mask, q_seq_shards=1), _dense(mask), q, k, v, do)
+
+
+def _packed_segments(batch, s, seed, lo, hi):
+  rng = np.random.default_rng(seed)
+  ids = np.zeros((batch, s), np.int32)
+  for b in range(batch):
+    pos, doc = 0, 0
+    while pos < s:
+      n = int(rng.integers(lo, hi + 1))
+      ids[b, pos:pos + n] = doc
+      pos += n
+      doc += 1
+  return torch.from_numpy(ids)
+
+
+def test_segment_ids_with_local_window():
+  """Shape of BASELINE config 3, scaled down: window+causal composed with packed documents."""
+  s = 1024
+  q, k, v, do = _inputs(3000, 2, 4, 4, s, s)
+  mask = mask_lib.LocalMask((s, s), (256, 0), 0)
+  seg = _packed_segments(2, s, 1, 32, 256)
+  _run_and_compare(splash.make_splash_mha(mask, q_seq_shards=1), _dense(mask), q, k, v, do, seg=(seg, seg))
+
+
+def test_segment_ids_unbatched_vector():
+  s = 512
+  q, k, v, do = _inputs(9, 1, 2, 2, s, s)
+  mask = mask_lib.CausalMask((s, s))
+  seg = _packed_segments(1, s, 2, 64, 200)
+  kernel = splash.make_splash_mha(mask, q_seq_shards=1, save_residuals=True)
+  dev = torch.device("cuda:0")
+  out, _ = kernel(q[0].to(dev), k[0].to(dev), v[0].to(dev), splash.SegmentIds(seg[0].to(dev), seg[0].to(dev)),
+                  logits_scale=0.0884)
+  ro, _, _ = attention_ref.attention_reference(q[0], k[0], v[0], _dense(mask), (seg[0], seg[0]), scale=0.0884)
+  assert (out.float().cpu() - ro).abs().max().item() <= O_ATOL
+
+
+@pytest.mark.parametrize("bq,bkv", [(256, 128), (128, 256), (512, 512)])
+def test_block_sizes(bq, bkv):
+  s = 1024
+  q, k, v, do = _inputs(13, 1, 2, 2, s, s)
+  cfg = splash.SplashConfig(block_q=bq, block_kv=bkv, block_q_dkv=bq, block_kv_dkv=bkv)
+  for mask in (mask_lib.CausalMask((s, s)),
+               mask_lib.LocalMask((s, s), (300, None), 0) & mask_lib.CausalMask((s, s))):
+    _run_and_compare(splash.make_splash_mha(mask, config=cfg, q_seq_shards=1), _dense(mask), q, k, v, do)
+
+
+def test_op_layout_strided_views():
+  """[B, T, H, D] storage viewed as [B, H, T, D]: consumed through strides, no copies."""
+  b, t, hq, hkv = 2, 512, 4, 2
+  g = torch.Generator().manual_seed(21)
+  mk = lambda h: torch.randn(b, t, h, D, generator=g).to(torch.bfloat16)
+  q_bthd, k_bthd, v_bthd, do_bthd = mk(hq), mk(hkv), mk(hkv), mk(hq)
+  mask = mask_lib.CausalMask((t, t))
+  kernel = splash.make_splash_mha(mask, q_seq_shards=1)
+  perm = lambda x: x.permute(0, 2, 1, 3)
+  _run_and_compare(kernel, _dense(mask), perm(q_bthd), perm(k_bthd), perm(v_bthd), perm(do_bthd))
+  dev = torch.device("cuda:0")
+  qd = q_bthd.to(dev).permute(0, 2, 1, 3)
+  assert not qd.is_contiguous()
+  out = kernel(qd, k_bthd.to(dev).permute(0, 2, 1, 3), v_bthd.to(dev).permute(0, 2, 1, 3))
+  assert out.shape == (b, hq, t, D)
+
+
+def test_dynamic_mask_kernel():
+  s = 512
+  q, k, v, do = _inputs(17, 1, 2, 2, s, s)
+  dense = mask_lib.make_random_mask((s, s), 0.6, 2) | mask_lib.make_causal_mask((s, s), 0) & \
+      mask_lib.make_local_attention_mask((s, s), (0, 0))
+  kernel = splash.make_dynamic_splash_mha(torch.from_numpy(dense))
+  _run_and_compare(kernel, dense, q, k, v, do)
+
+
+def test_bitwise_repeatable():
+  q, k, v, do = _inputs(23, 1, 8, 2, 1024, 1024)
+  mask = mask_lib.CausalMask((1024, 1024))
+  kernel = splash.make_splash_mha(mask, q_seq_shards=1)
+  dev = torch.device("cuda:0")
+  runs = []
+  for _ in range(2):
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    out = kernel(qd, kd, vd, logits_scale=0.0884)
+    out.backward(do.to(dev))
+    runs.append((out.detach(), qd.grad, kd.grad, vd.grad))
+  for a, b in zip(*runs):
+    assert torch.equal(a, b)
+
+
+def test_full_size_properties_llama_shape():
+  """BASELINE config 2 at full size, checked through size-independent identities.
+
+  (1) rows of P sum to one, so with V = 1 the output is exactly 1; (2) the first causal row
+  attends to key 0 only; (3) sum_kv dV = sum_q dO over each kv-head group; (4) <q, dq> = <k, dk>
+  because both equal sum(dS * S) / scale-free logits.
+  """
+  dev = torch.device("cuda:0")
+  b, hq, hkv, s = 4, 32, 8, 8192
+  g = torch.Generator(device=dev).manual_seed(2000)
+  mk = lambda h: torch.randn(b, h, s, D, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+  q, k, v, do = mk(hq), mk(hkv), mk(hkv), mk(hq)
+  kernel = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1)
+  scale = 1 / math.sqrt(D)
+  ones = torch.ones_like(v)
+  out1 = kernel(q, k, ones, logits_scale=scale)
+  assert (out1.float() - 1).abs().max().item() <= 8e-3  # bf16 half-ulp at 1.0 is 3.9e-3
+  qd, kd, vd = (t.clone().requires_grad_(True) for t in (q, k, v))
+  out = kernel(qd, kd, vd, logits_scale=scale)
+  assert torch.equal(out[:, :, 0], v.repeat_interleave(hq // hkv, 1)[:, :, 0])
+  out.backward(do)
+  kernel.check_errors()
+  group = hq // hkv
+  lhs = vd.grad.float().sum(2)
+  rhs = do.float().view(b, hkv, group, s, D).sum((2, 3))
+  assert ((lhs - rhs).norm() / rhs.norm()).item() <= 5e-3
+  qdq = (qd.grad.float() * q.float()).view(b, hkv, group, s, D).sum((2, 3, 4))
+  kdk = (kd.grad.float() * k.float()).sum((2, 3))
+  # both sides are sums of ~1e8 signed terms; compare as vectors over (batch, kv head)
+  assert ((qdq - kdk).norm() / kdk.norm()).item() <= 1e-2
+
+
+def test_unsupported_and_invalid_arguments():
+  dev = torch.device("cuda:0")
+  s = 256
+  mask = mask_lib.CausalMask((s, s))
+  kernel = splash.make_splash_mha(mask, q_seq_shards=1)
+  q = torch.zeros(2, s, D, dtype=torch.bfloat16, device=dev)
+  with pytest.raises(NotImplementedError):
+    kernel(q, q, q, sinks=torch.zeros(2, device=dev))
+  with pytest.raises(NotImplementedError):
+    kernel(q.float(), q.float(), q.float())
+  with pytest.raises(NotImplementedError):
+    kernel(q[..., :64], q[..., :64], q[..., :64])
+  with pytest.raises(ValueError):
+    kernel(q[:, :128], q, q)
+  with pytest.raises(RuntimeError):
+    kernel(q.cpu(), q.cpu(), q.cpu())
+  cfg = splash.SplashConfig(block_q=128, block_kv=128, attn_logits_soft_cap=30.0)
+  with pytest.raises(NotImplementedError):
+    splash.make_splash_mha(mask, config=cfg, q_seq_shards=1)(q, q, q)
+  with pytest.raises(NotImplementedError):
+    splash.make_splash_mha(mask_lib.CausalMask((64, 64)), q_seq_shards=1,
+                           config=splash.SplashConfig(block_q=16, block_kv=16))(
+                               q[:, :64], q[:, :64], q[:, :64])

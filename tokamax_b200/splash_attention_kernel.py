@@ -1,0 +1,521 @@
+"""Splash attention on B200: the user-facing kernel objects.
+
+Mirrors the public surface of the reference's
+``tokamax/_src/ops/experimental/tpu/splash_attention/splash_attention_kernel.py``:
+``QKVLayout`` (:103-111), ``SplashConfig`` (:114-196), ``SplashAttentionKernel`` (:2002-2067) and
+the factories ``make_splash_mha`` / ``make_splash_mqa`` (+ ``_single_device``) (:2070-2131,
+:2229-2237) and ``make_dynamic_splash_mha`` / ``_mqa`` (:2134-2226), with torch tensors in
+place of ``jax.Array`` and ``torch.autograd`` in place of ``jax.custom_vjp`` (:998-1108,
+:1871-1950).
+
+All device work goes through the C ABI of ``libsplash_b200.so`` (``splash_fwd`` / ``splash_bwd``);
+there is no PyTorch or CPU fallback — an unsupported configuration raises
+``NotImplementedError`` and a missing CUDA device raises ``RuntimeError``.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+import dataclasses
+import enum
+import functools
+from typing import Any
+
+import numpy as np
+import torch
+
+from tokamax_b200 import _native
+from tokamax_b200 import base
+from tokamax_b200 import splash_attention_mask as mask_lib
+from tokamax_b200 import splash_attention_mask_info as mask_info_lib
+
+SegmentIds = base.SegmentIds
+MaskInfo = mask_info_lib.MaskInfo
+DEFAULT_MASK_VALUE = base.DEFAULT_MASK_VALUE
+partial = functools.partial
+
+_TILE = 128
+_HEAD_DIM = 128
+
+
+def get_kernel_name(is_mqa: bool, save_residuals: bool, is_segmented: bool, phase: str) -> str:
+  """Name of a kernel variant, in the reference's scheme (kernel.py:86-96)."""
+  assert phase in ["dq", "dkv", "fwd"]
+  assert not save_residuals or phase == "fwd"
+  residuals = "_residuals" if save_residuals else "_no_residuals"
+  attention_type = "mqa" if is_mqa else "mha"
+  segments = "_segmented" if is_segmented else ""
+  return f"splash_{attention_type}_{phase}{segments}{residuals}"
+
+
+class QKVLayout(enum.IntEnum):
+  HEAD_DIM_MINOR = enum.auto()  # [..., seq_len, head_dim]
+  SEQ_MINOR = enum.auto()  # [..., head_dim, seq_len]
+
+
+@dataclasses.dataclass(frozen=True, slots=True)
+class SplashConfig:
+  """Tile sizes and feature switches of the splash kernels (field-compatible with the reference).
+
+  On B200 the MMA tile is fixed at 128x128; ``block_*`` choose the granularity of the MaskInfo
+  tables (multiples of 128).  Fields that only steer the TPU code generator are accepted and
+  ignored; fields that change results and are not built raise ``NotImplementedError`` at call
+  time.
+  """
+
+  block_q: int
+  block_kv: int
+  block_kv_compute: int | None = None
+
+  block_q_dkv: int | None = None
+  block_kv_dkv: int | None = None
+  block_kv_dkv_compute: int | None = None
+
+  block_q_dq: int | None = None
+  block_kv_dq: int | None = None
+  use_fused_bwd_kernel: bool = True
+  num_stacked_q_heads: int = 1
+  q_layout: QKVLayout = QKVLayout.HEAD_DIM_MINOR
+  k_layout: QKVLayout = QKVLayout.HEAD_DIM_MINOR
+  v_layout: QKVLayout = QKVLayout.HEAD_DIM_MINOR
+
+  fwd_cost_estimate: Any = None
+  bwd_cost_estimate: Any = None
+
+  residual_checkpoint_name: str | None = None
+  attn_logits_soft_cap: float | None = None
+  fuse_reciprocal: bool = True
+  use_base2_exp: bool = True
+  max_logit_const: float | None = None
+  interpret: bool = False
+  dq_reduction_steps: int | None = None
+  use_experimental_scheduler: bool = False
+
+  def __post_init__(self):
+    if self.block_kv_compute is None:
+      object.__setattr__(self, "block_kv_compute", self.block_kv)
+    if self.block_kv_dkv_compute is None:
+      object.__setattr__(self, "block_kv_dkv_compute", self.block_kv_dkv)
+    if self.dq_reduction_steps is not None and self.dq_reduction_steps != 3:
+      raise ValueError(
+          f"Invalid dq_reduction_steps: {self.dq_reduction_steps}, only 3 or None are supported."
+      )
+    if not self.use_fused_bwd_kernel:
+      raise ValueError("Only the fused bwd kernel is supported.")
+
+  @property
+  def has_backward_blocks(self) -> bool:
+    return all(b is not None for b in (self.block_q_dkv, self.block_kv_dkv, self.block_kv_dkv_compute))
+
+  @classmethod
+  def get_default(cls):
+    return SplashConfig(
+        block_q=128, block_kv=128, block_kv_compute=128,
+        block_q_dkv=128, block_kv_dkv=128, block_kv_dkv_compute=128,
+        block_q_dq=128, block_kv_dq=128, fuse_reciprocal=True,
+    )
+
+
+# ----------------------------------------------------------------------------------------------
+# device-side tables
+# ----------------------------------------------------------------------------------------------
+def _require_cuda(t: torch.Tensor) -> None:
+  if not t.is_cuda:
+    raise RuntimeError(
+        "splash attention runs on CUDA (sm_100a) only and has no CPU path; got a tensor on "
+        f"{t.device}"
+    )
+
+
+def _build_schedule(state: np.ndarray, pid: np.ndarray, block_q: int, block_kv: int, kind: int):
+  out = _native.SplashScheduleOut()
+  lib = _native.lib()
+  state = np.ascontiguousarray(state, dtype=np.int32)
+  pid = np.ascontiguousarray(pid, dtype=np.int32)
+  _native.check(
+      lib.splash_schedule_build(state.ctypes.data, pid.ctypes.data, state.shape[0], state.shape[1],
+                                block_q, block_kv, kind, C.byref(out)),
+      "splash_schedule_build",
+  )
+  try:
+    row_ptr = np.ctypeslib.as_array(out.row_ptr, shape=(out.n_rows + 1,)).copy()
+    n = max(int(out.n_entries), 1)
+    entries = np.ctypeslib.as_array(out.entries, shape=(n * 4,)).copy()
+    if out.n_entries == 0:
+      entries[:] = 0
+  finally:
+    lib.splash_schedule_free(C.byref(out))
+  return row_ptr, entries
+
+
+class _DeviceTables:
+  """Schedules, partial-mask blocks and the error record of one kernel object on one device."""
+
+  def __init__(self, kernel: "SplashAttentionKernel", device: torch.device):
+    cfg = kernel.config
+    fwd, dkv = kernel.fwd_mask_info, kernel.dkv_mask_info
+    q_len, kv_len = kernel.mask_shape
+    for b in (cfg.block_q, cfg.block_kv):
+      if b % _TILE != 0:
+        raise NotImplementedError(f"block sizes must be multiples of {_TILE} on B200, got {b}")
+    nq, nkv = q_len // cfg.block_q, kv_len // cfg.block_kv
+    state, pid = mask_info_lib.block_grids(fwd, nq, nkv, is_dkv=False)
+    self.keep = []
+    self.fwd = self._upload(state, pid, cfg.block_q, cfg.block_kv, 0, fwd.partial_mask_blocks, device)
+    self.dq = self._upload(state, pid, cfg.block_q, cfg.block_kv, 1, fwd.partial_mask_blocks, device)
+    if dkv is not None:
+      bq, bkv = cfg.block_q_dkv, cfg.block_kv_dkv
+      for b in (bq, bkv):
+        if b % _TILE != 0:
+          raise NotImplementedError(f"block sizes must be multiples of {_TILE} on B200, got {b}")
+      st2, pid2 = mask_info_lib.block_grids(dkv, q_len // bq, kv_len // bkv, is_dkv=True)
+      self.dkv = self._upload(st2, pid2, bq, bkv, 2, dkv.partial_mask_blocks, device)
+    else:
+      pmb_t = None
+      if fwd.partial_mask_blocks is not None:
+        pmb_t = np.ascontiguousarray(np.swapaxes(np.asarray(fwd.partial_mask_blocks), -1, -2))
+      self.dkv = self._upload(state, pid, cfg.block_q, cfg.block_kv, 2, pmb_t, device)
+    self.error_record = torch.zeros(4, dtype=torch.int32, device=device)
+    q_seq = fwd.q_sequence
+    self.q_sequence = None
+    if q_seq is not None and not np.array_equal(np.asarray(q_seq), np.arange(q_len, dtype=np.int32)):
+      self.q_sequence = torch.from_numpy(np.ascontiguousarray(q_seq, dtype=np.int32)).to(device)
+
+  def _upload(self, state, pid, bq, bkv, kind, pmb, device) -> _native.SplashDeviceSchedule:
+    row_ptr, entries = _build_schedule(state, pid, bq, bkv, kind)
+    rp = torch.from_numpy(row_ptr).to(device)
+    en = torch.from_numpy(entries).to(device)
+    self.keep += [rp, en]
+    d = _native.SplashDeviceSchedule()
+    d.row_ptr = rp.data_ptr()
+    d.entries = en.data_ptr()
+    d.n_rows = len(row_ptr) - 1
+    d.block_q, d.block_kv = bq, bkv
+    d.partial_mask_blocks = None
+    if pmb is not None:
+      pm = torch.from_numpy(np.ascontiguousarray(np.asarray(pmb), dtype=np.int8)).to(device)
+      self.keep.append(pm)
+      d.partial_mask_blocks = pm.data_ptr()
+    return d
+
+
+def _tensor_desc(t: torch.Tensor) -> _native.SplashTensor:
+  d = _native.SplashTensor()
+  d.data = t.data_ptr()
+  d.dtype = 0
+  for i in range(4):
+    d.size[i] = t.shape[i]
+    d.stride[i] = t.stride(i)
+  return d
+
+
+def _usable(t: torch.Tensor) -> torch.Tensor:
+  """Returns ``t`` if the kernels can read it in place, else a contiguous copy."""
+  ok = t.stride(-1) == 1 and all(s % 8 == 0 for s in t.stride()[:-1]) and t.data_ptr() % 16 == 0
+  return t if ok else t.contiguous()
+
+
+def _mask_fn_struct(mask_function_rule) -> _native.SplashMaskFn:
+  fn = _native.SplashMaskFn()
+  if mask_function_rule is not None:
+    for name, value in zip(mask_function_rule._fields, mask_function_rule):
+      setattr(fn, name, int(value))
+  return fn
+
+
+class _SplashFunction(torch.autograd.Function):
+  """forward = splash_fwd, backward = splash_bwd (reference custom_vjp: kernel.py:998-1108)."""
+
+  @staticmethod
+  def forward(ctx, q, k, v, q_seg, kv_seg, kernel, scale):
+    _require_cuda(q)
+    tables = kernel._tables(q.device)  # pylint: disable=protected-access
+    q, k, v = _usable(q), _usable(k), _usable(v)
+    b, hq, sq, d = q.shape
+    o = torch.empty((b, hq, sq, d), dtype=q.dtype, device=q.device)
+    lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
+    max_logits = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
+    args = _native.SplashFwdArgs()
+    args.q, args.k, args.v, args.o = map(_tensor_desc, (q, k, v, o))
+    args.logsumexp = lse.data_ptr()
+    args.max_logits = max_logits.data_ptr()
+    args.q_segment_ids = q_seg.data_ptr() if q_seg is not None else None
+    args.kv_segment_ids = kv_seg.data_ptr() if kv_seg is not None else None
+    args.q_sequence = tables.q_sequence.data_ptr() if tables.q_sequence is not None else None
+    args.sched = tables.fwd
+    args.mask_fn = _mask_fn_struct(kernel.mask_function_rule)
+    args.scale = scale
+    args.mask_value = max(kernel.mask_value, -3.0e38)
+    args.error_record = tables.error_record.data_ptr()
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+      _native.check(_native.lib().splash_fwd(C.byref(args), C.c_void_p(stream)), "splash_fwd")
+    ctx.save_for_backward(q, k, v, o, lse, q_seg, kv_seg)
+    ctx.kernel = kernel
+    ctx.scale = scale
+    ctx.mark_non_differentiable(lse, max_logits)
+    return o, lse, max_logits
+
+  @staticmethod
+  def backward(ctx, d_o, _dlse, _dmax):
+    q, k, v, o, lse, q_seg, kv_seg = ctx.saved_tensors
+    kernel = ctx.kernel
+    tables = kernel._tables(q.device)  # pylint: disable=protected-access
+    d_o = _usable(d_o)
+    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+    lib = _native.lib()
+    ws_bytes = lib.splash_bwd_workspace_bytes(q.shape[0], q.shape[1], q.shape[2])
+    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+    args = _native.SplashBwdArgs()
+    args.q, args.k, args.v, args.o, args.d_o = map(_tensor_desc, (q, k, v, o, d_o))
+    args.dq, args.dk, args.dv = map(_tensor_desc, (dq, dk, dv))
+    args.logsumexp = lse.data_ptr()
+    args.q_segment_ids = q_seg.data_ptr() if q_seg is not None else None
+    args.kv_segment_ids = kv_seg.data_ptr() if kv_seg is not None else None
+    args.q_sequence = tables.q_sequence.data_ptr() if tables.q_sequence is not None else None
+    args.sched_dq = tables.dq
+    args.sched_dkv = tables.dkv
+    args.mask_fn = _mask_fn_struct(kernel.mask_function_rule)
+    args.scale = ctx.scale
+    args.workspace = workspace.data_ptr()
+    args.workspace_bytes = ws_bytes
+    args.error_record = tables.error_record.data_ptr()
+    stream = torch.cuda.current_stream(q.device).cuda_stream
+    with torch.cuda.device(q.device):
+      _native.check(lib.splash_bwd(C.byref(args), C.c_void_p(stream)), "splash_bwd")
+    return dq, dk, dv, None, None, None, None
+
+
+class SplashAttentionKernel:
+  """Callable splash attention for one mask (reference: kernel.py:2002-2067).
+
+  ``kernel(q, k, v, segment_ids=None, sinks=None, *, max_logit_value=None, logits_scale=1.0)``
+  with q ``[q_heads, q_len, 128]`` (or batched ``[batch, q_heads, q_len, 128]``), k / v
+  ``[kv_heads, kv_len, 128]`` (``[kv_len, 128]`` for MQA), bf16 on a CUDA device.  Returns ``out``,
+  or ``(out, {"logsumexp", "max_logits"})`` when built with ``save_residuals=True``.  As in the
+  reference no softmax scale is applied unless ``logits_scale`` is given (an extension that folds
+  the caller's ``q * scale`` into the kernel in fp32).  Differentiable through torch autograd.
+  """
+
+  def __init__(self, fwd_mask_info: MaskInfo, dkv_mask_info: MaskInfo | None, **kwargs):
+    self.kwargs = kwargs
+    self.fwd_mask_info = fwd_mask_info
+    self.dkv_mask_info = dkv_mask_info
+    self._device_tables: dict = {}
+
+  # attribute views of kwargs
+  config = property(lambda self: self.kwargs["config"])
+  is_mqa = property(lambda self: self.kwargs["is_mqa"])
+  save_residuals = property(lambda self: self.kwargs.get("save_residuals", False))
+  mask_value = property(lambda self: self.kwargs.get("mask_value", DEFAULT_MASK_VALUE))
+  mask_function = property(lambda self: self.kwargs.get("mask_function"))
+  mask_function_rule = property(lambda self: self.kwargs.get("mask_function_rule"))
+  mask_shape = property(lambda self: self.kwargs["mask_shape"])
+
+  def _tables(self, device: torch.device) -> _DeviceTables:
+    key = (device.type, device.index)
+    if key not in self._device_tables:
+      self._device_tables[key] = _DeviceTables(self, device)
+    return self._device_tables[key]
+
+  def check_errors(self) -> None:
+    """Synchronises and raises if a kernel reported a device-side fault (bounded wait ran out)."""
+    lib = _native.lib()
+    for tables in self._device_tables.values():
+      rec = (C.c_uint32 * 4)()
+      dev = tables.error_record.device
+      stream = torch.cuda.current_stream(dev).cuda_stream
+      with torch.cuda.device(dev):
+        st = lib.splash_read_error(tables.error_record.data_ptr(), C.c_void_p(stream), C.byref(rec))
+      if st != 0:
+        raise _native.SplashError(st, f"device error record {list(rec)}")
+
+  def _reject_unsupported(self, q, k, sinks, max_logit_value):
+    cfg = self.config
+    if sinks is not None:
+      raise NotImplementedError("attention sinks are not built on B200 yet")
+    if max_logit_value is not None or cfg.max_logit_const is not None:
+      raise NotImplementedError("max_logit_value / max_logit_const are not built on B200 yet")
+    if cfg.attn_logits_soft_cap is not None:
+      raise NotImplementedError("attn_logits_soft_cap is not built on B200 yet")
+    if any(l != QKVLayout.HEAD_DIM_MINOR for l in (cfg.q_layout, cfg.k_layout, cfg.v_layout)):
+      raise NotImplementedError("only HEAD_DIM_MINOR layouts are built on B200")
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16:
+      raise NotImplementedError(f"only bfloat16 inputs are built on B200, got {q.dtype}")
+    if q.shape[-1] != _HEAD_DIM:
+      raise NotImplementedError(f"only head_dim {_HEAD_DIM} is built on B200, got {q.shape[-1]}")
+
+  def __call__(self, q, k, v, segment_ids: SegmentIds | None = None, sinks=None, *,
+               max_logit_value=None, logits_scale: float = 1.0, **overrides):
+    kw = dict(self.kwargs, **overrides)
+    save_residuals = kw.get("save_residuals", False)
+    self._reject_unsupported(q, k, sinks, max_logit_value)
+    batched = q.dim() == 4
+    is_mqa = self.is_mqa
+    if not batched:
+      q = q[None]
+      k, v = k[None], v[None]
+    if is_mqa:
+      if k.dim() != 3:
+        raise ValueError(f"MQA expects k/v without a head axis, got k of rank {k.dim() - 1}")
+      k, v = k[:, None], v[:, None]
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+      raise ValueError(f"Unexpected ranks: q {q.shape}, k {k.shape}, v {v.shape}")
+    q_len, kv_len = self.mask_shape
+    if q.shape[2] != q_len or k.shape[2] != kv_len or v.shape[2] != kv_len:
+      raise ValueError(f"Sequence lengths {q.shape[2]}, {k.shape[2]} do not match the mask {self.mask_shape}")
+    if k.shape[1] == 0 or q.shape[1] % k.shape[1] != 0:
+      raise ValueError(f"q heads ({q.shape[1]}) must be a multiple of kv heads ({k.shape[1]})")
+    if v.shape[-1] != q.shape[-1]:
+      raise NotImplementedError("head_dim_v != head_dim_qk is not built on B200 yet")
+    q_seg = kv_seg = None
+    if segment_ids is not None:
+      q_seg = torch.as_tensor(segment_ids.q, device=q.device).to(torch.int32)
+      kv_seg = torch.as_tensor(segment_ids.kv, device=q.device).to(torch.int32)
+      if q_seg.dim() == 1:
+        q_seg = q_seg[None].expand(q.shape[0], -1)
+        kv_seg = kv_seg[None].expand(q.shape[0], -1)
+      if q_seg.shape != (q.shape[0], q_len) or kv_seg.shape != (q.shape[0], kv_len):
+        raise ValueError(f"segment id shapes {tuple(q_seg.shape)}, {tuple(kv_seg.shape)} do not match q/kv")
+      q_seg, kv_seg = q_seg.contiguous(), kv_seg.contiguous()
+    o, lse, max_logits = _SplashFunction.apply(q, k, v, q_seg, kv_seg, self, float(logits_scale))
+    if not batched:
+      o, lse, max_logits = o[0], lse[0], max_logits[0]
+    if save_residuals:
+      return o, {"logsumexp": lse, "max_logits": max_logits}
+    return o
+
+  def manual_sharding_spec(self, sharding):
+    raise NotImplementedError(
+        "q-sequence sharding under shard_map is a JAX construct; on B200 sequence parallelism is "
+        "tokamax_b200.ulysses.UlyssesSplashAttention"
+    )
+
+  # pytree-style helpers kept for API parity with the reference
+  def tree_flatten(self):
+    return ((self.fwd_mask_info, self.dkv_mask_info), self.kwargs)
+
+  @classmethod
+  def tree_unflatten(cls, kwargs, values):
+    fwd_mask_info, dkv_mask_info = values
+    dkv_mask_info = MaskInfo(*dkv_mask_info) if dkv_mask_info is not None else None
+    return SplashAttentionKernel(MaskInfo(*fwd_mask_info), dkv_mask_info, **kwargs)
+
+
+# ----------------------------------------------------------------------------------------------
+# factories
+# ----------------------------------------------------------------------------------------------
+def _make_splash_attention(
+    mask: np.ndarray | mask_lib.Mask,
+    *,
+    config: SplashConfig | None = None,
+    is_mqa: bool,
+    save_residuals: bool = False,
+    mask_value: float = DEFAULT_MASK_VALUE,
+    downcast_smem_data: bool = True,
+    partial_mask_blocks_dtype: Any = np.int8,
+    q_seq_shards: int,
+):
+  if len(mask.shape) != 2:
+    raise ValueError(f"Unexpected mask shape: {mask.shape}")
+  if isinstance(mask, np.ndarray):
+    mask = mask_lib.NumpyMask(mask)
+  if config is None:
+    config = SplashConfig.get_default()
+  if q_seq_shards != 1:
+    raise NotImplementedError(
+        "q_seq_shards > 1 builds tables for shard_map; on B200 use tokamax_b200.ulysses for "
+        "sequence parallelism (MaskInfo tables for shards are available from process_mask)"
+    )
+  process_fn = partial(
+      mask_info_lib.process_mask,
+      downcast_smem_data=downcast_smem_data,
+      partial_mask_blocks_dtype=partial_mask_blocks_dtype,
+      q_seq_shards=q_seq_shards,
+  )
+  fwd_mask_info, mask_function_fwd = process_fn(mask, (config.block_q, config.block_kv))
+  fwd_mask_sparsity = (
+      float(np.mean(fwd_mask_info.block_mask != 0)) if fwd_mask_info.block_mask is not None else 1.0
+  )
+  dkv_mask_info = None
+  dkv_mask_sparsity = 1.0
+  if config.has_backward_blocks:
+    dkv_mask_info, mask_function_dkv = process_fn(
+        mask,
+        (config.block_q_dkv, config.block_kv_dkv),
+        is_dkv=True,
+        return_dynamic_grid=config.dq_reduction_steps == 3,
+    )
+    assert (mask_function_fwd is None) == (mask_function_dkv is None)
+    if dkv_mask_info.block_mask is not None:
+      dkv_mask_sparsity = float(np.mean(dkv_mask_info.block_mask != 0))
+  rule = mask.interval_rule if mask_function_fwd is not None else None
+  return SplashAttentionKernel(
+      fwd_mask_info,
+      dkv_mask_info,
+      config=config,
+      is_mqa=is_mqa,
+      save_residuals=save_residuals,
+      mask_value=mask_value,
+      mask_function=mask_function_fwd,
+      mask_function_rule=rule,
+      mask_shape=tuple(mask.shape),
+      fwd_mask_sparsity=fwd_mask_sparsity,
+      dkv_mask_sparsity=dkv_mask_sparsity,
+  )
+
+
+def _make_dynamic_splash_attention(
+    mask,
+    *,
+    mesh=None,
+    mask_spec=None,
+    config: SplashConfig | None = None,
+    is_mqa: bool,
+    save_residuals: bool = False,
+    mask_value: float = DEFAULT_MASK_VALUE,
+    downcast_smem_data: bool = True,
+    partial_mask_blocks_dtype: Any = np.int8,
+):
+  """Kernel for a mask that is data (a bool array / tensor) rather than a static object."""
+  if (mesh is not None) != (mask_spec is not None):
+    raise ValueError("Either both or neither of mesh and mask_spec must be specified.")
+  if mesh is not None:
+    raise NotImplementedError("mesh / mask_spec belong to shard_map; not applicable on B200")
+  if len(mask.shape) != 2:
+    raise ValueError(f"Unexpected mask shape: {mask.shape}")
+  if config is None:
+    config = SplashConfig.get_default()
+  config = dataclasses.replace(config, dq_reduction_steps=3)
+  process = partial(
+      mask_info_lib._process_dynamic_mask,  # pylint: disable=protected-access
+      downcast_smem_data=downcast_smem_data,
+      partial_mask_blocks_dtype=partial_mask_blocks_dtype,
+  )
+  fwd_mask_info = process(mask, (config.block_q, config.block_kv), is_dkv=False)
+  dkv_mask_info = None
+  if config.has_backward_blocks:
+    dkv_mask_info = process(mask, (config.block_q_dkv, config.block_kv_dkv), is_dkv=True)
+  return SplashAttentionKernel(
+      fwd_mask_info,
+      dkv_mask_info,
+      config=config,
+      is_mqa=is_mqa,
+      save_residuals=save_residuals,
+      mask_value=mask_value,
+      mask_function=None,
+      mask_function_rule=None,
+      mask_shape=tuple(mask.shape),
+      fwd_mask_sparsity=1.0,
+      dkv_mask_sparsity=1.0,
+  )
+
+
+make_splash_mha = partial(_make_splash_attention, is_mqa=False)
+make_splash_mqa = partial(_make_splash_attention, is_mqa=True)
+
+make_splash_mha_single_device = partial(make_splash_mha, q_seq_shards=1)
+make_splash_mqa_single_device = partial(make_splash_mqa, q_seq_shards=1)
+
+make_dynamic_splash_mqa = partial(_make_dynamic_splash_attention, is_mqa=True)
+make_dynamic_splash_mha = partial(_make_dynamic_splash_attention, is_mqa=False)
