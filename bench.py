@@ -1,0 +1,533 @@
+#!/usr/bin/env python3
+"""Benchmark of the splash-attention hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload ...]
+
+A step is one forward + backward of splash attention over one batch of synthetic inputs
+(Q, K, V, dO ~ N(0,1) in bf16 from fixed seeds, softmax scale 1/sqrt(128)).  The metric is
+mask-counted TFLOP/s: 14 * D * B * Hq * N_live FLOPs per step, N_live = number of unmasked
+(query, key) pairs.  Workloads (BASELINE.json configs):
+
+  c2  causal, B=4, S=8192, Hq=32, Hkv=8, D=128 (Llama-3-8B shape)        -- default at N=1
+  c4  causal, B=1, S=131072, Hq=64, Hkv=8, D=128, Ulysses context parallel -- default at N>1
+  c1  causal, B=2, S=1024, Hq=Hkv=8                                        -- the CPU-sized case
+  c3  local window 4096 + causal with packed-document segment ids, B=8, S=16384, Hq=Hkv=16
+
+One JSON line is printed by rank 0.  ``--impl reference`` times the CPU restatement of the
+reference's own fp32 attention (oracle/) on the host cores on a bounded sample of the same
+workload (JAX, which the reference needs, is not installed on this image).
+"""
+
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+D = 128
+SCALE = 1.0 / math.sqrt(D)
+
+WORKLOADS = {
+    "c1": dict(config_id=1, batch=2, q_heads=8, kv_heads=8, seq=1024, mask="causal"),
+    "c2": dict(config_id=2, batch=4, q_heads=32, kv_heads=8, seq=8192, mask="causal"),
+    "c3": dict(config_id=3, batch=8, q_heads=16, kv_heads=16, seq=16384, mask="local4096_causal_segments"),
+    "c4": dict(config_id=4, batch=1, q_heads=64, kv_heads=8, seq=131072, mask="causal"),
+}
+
+
+# ----------------------------------------------------------------------------------------------
+# workload construction
+# ----------------------------------------------------------------------------------------------
+def packed_segments(batch: int, seq: int, seed: int) -> np.ndarray:
+  """Documents of length U{512..4096} packed into each row (last one truncated)."""
+  rng = np.random.default_rng(seed)
+  ids = np.zeros((batch, seq), np.int32)
+  for b in range(batch):
+    pos, doc = 0, 0
+    while pos < seq:
+      n = int(rng.integers(512, 4097))
+      ids[b, pos:pos + n] = doc
+      pos += n
+      doc += 1
+  return ids
+
+
+def live_pairs(w: dict, segments: np.ndarray | None) -> int:
+  """Unmasked (q, k) pairs summed over the batch (per q head)."""
+  s = w["seq"]
+  if w["mask"] == "causal":
+    return w["batch"] * (s * (s + 1) // 2)
+  # window 4096 + causal and documents <= 4096 long: the window never cuts inside a document,
+  # so a row keeps exactly its causal prefix within its own document.
+  total = 0
+  for b in range(w["batch"]):
+    _, counts = np.unique(segments[b], return_counts=True)
+    total += int(sum(int(c) * (int(c) + 1) // 2 for c in counts))
+  return total
+
+
+def host_inputs(w: dict, heads_q=None, heads_kv=None, batch=None, pin=False):
+  cid = w["config_id"]
+  b = batch or w["batch"]
+  hq, hkv, s = heads_q or w["q_heads"], heads_kv or w["kv_heads"], w["seq"]
+
+  def gen(seed, h):
+    g = torch.Generator(device="cpu").manual_seed(seed)
+    t = torch.randn(b, h, s, D, generator=g, dtype=torch.float32).to(torch.bfloat16)
+    return t.pin_memory() if pin else t
+
+  return gen(1000 * cid + 0, hq), gen(1000 * cid + 1, hkv), gen(1000 * cid + 2, hkv), gen(1000 * cid + 3, hq)
+
+
+def device_inputs(w: dict, device, heads_q=None, heads_kv=None, seq_slice=None):
+  """Same distribution generated on the device (the large configs would take minutes on CPU)."""
+  cid = w["config_id"]
+  hq, hkv, s = heads_q or w["q_heads"], heads_kv or w["kv_heads"], w["seq"]
+  s_loc = s if seq_slice is None else seq_slice
+  out = []
+  for i, h in enumerate((hq, hkv, hkv, hq)):
+    g = torch.Generator(device=device).manual_seed(1000 * cid + i + 17 * (device.index or 0))
+    out.append(torch.randn(w["batch"], h, s_loc, D, generator=g, device=device, dtype=torch.float32).to(torch.bfloat16))
+  return out
+
+
+def make_kernel(w: dict):
+  from tokamax_b200 import splash_attention_kernel as splash
+  from tokamax_b200 import splash_attention_mask as mask_lib
+
+  s = w["seq"]
+  if w["mask"] == "causal":
+    mask = mask_lib.CausalMask((s, s))
+  else:
+    mask = mask_lib.LocalMask((s, s), (4096, 0), 0)
+  return splash.make_splash_mha(mask, q_seq_shards=1)
+
+
+# ----------------------------------------------------------------------------------------------
+# clocks
+# ----------------------------------------------------------------------------------------------
+class ClockSampler:
+  """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+  FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+            "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+            "clocks_event_reasons.sw_power_cap")
+
+  def __init__(self, index: int):
+    self.index = index
+    self.rows: list[list[str]] = []
+    self.proc = None
+    self.thread = None
+
+  def start(self):
+    try:
+      self.proc = subprocess.Popen(
+          ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+           "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+    except OSError:
+      self.proc = None
+      return
+    def pump():
+      for line in self.proc.stdout:
+        self.rows.append([c.strip() for c in line.split(",")])
+    self.thread = threading.Thread(target=pump, daemon=True)
+    self.thread.start()
+
+  def stop(self) -> dict:
+    if self.proc is None:
+      return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+    self.proc.terminate()
+    try:
+      self.proc.wait(timeout=5)
+    except subprocess.TimeoutExpired:
+      self.proc.kill()
+    if self.thread:
+      self.thread.join(timeout=2)
+    sm, smax, reasons = [], [], set()
+    names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+    for r in self.rows:
+      if len(r) < 7:
+        continue
+      try:
+        sm.append(float(r[0]))
+        smax.append(float(r[1]))
+      except ValueError:
+        continue
+      for name, val in zip(names, r[3:7]):
+        if val.lower().startswith("active"):
+          reasons.add(name)
+    return {
+        "sm_mhz": float(np.median(sm)) if sm else None,
+        "sm_max_mhz": float(max(smax)) if smax else None,
+        "samples": len(sm),
+        "reasons": sorted(reasons),
+    }
+
+
+# ----------------------------------------------------------------------------------------------
+# timing helpers
+# ----------------------------------------------------------------------------------------------
+def timed_steps(step_fn, steps: int, warmup: int, barrier=None) -> float:
+  """ms per step: warm-up, then `steps` steps between two events on the current stream."""
+  for _ in range(warmup):
+    step_fn()
+  if barrier:
+    barrier()
+  torch.cuda.synchronize()
+  e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  e0.record()
+  for _ in range(steps):
+    step_fn()
+  e1.record()
+  torch.cuda.synchronize()
+  if barrier:
+    barrier()
+  return e0.elapsed_time(e1) / steps
+
+
+def measured_peaks():
+  path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+  if os.path.exists(path):
+    with open(path) as f:
+      p = json.load(f)
+    return float(p["bf16_tflops"]), float(p.get("bf16_tflops_sustained", p["bf16_tflops"])), "measured"
+  return 1590.0, 1400.0, "fallback"
+
+
+# DRAM traffic of one dkv-kernel launch on the c2 workload (dram__bytes_read.sum +
+# dram__bytes_write.sum), taken from the ncu capture summarised in profiles/; None until one exists.
+DKV_TRAFFIC_BYTES_C2 = None
+
+
+def per_kernel_times(kernel, q, k, v, do, seg, iters: int = 5) -> dict:
+  """Average device time of each kernel of one step, timed alone through the C ABI."""
+  from tokamax_b200 import _native
+  from tokamax_b200 import splash_attention_kernel as splash
+
+  lib = _native.lib()
+  dev = q.device
+  tables = kernel._tables(dev)  # pylint: disable=protected-access
+  b, hq, s, _ = q.shape
+  o = torch.empty_like(q)
+  lse = torch.empty((b, hq, s), dtype=torch.float32, device=dev)
+  dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+  fa = _native.SplashFwdArgs()
+  fa.q, fa.k, fa.v, fa.o = map(splash._tensor_desc, (q, k, v, o))  # pylint: disable=protected-access
+  fa.logsumexp = lse.data_ptr()
+  fa.q_segment_ids = seg[0].data_ptr() if seg else None
+  fa.kv_segment_ids = seg[1].data_ptr() if seg else None
+  fa.sched = tables.fwd
+  fa.mask_fn = splash._mask_fn_struct(kernel.mask_function_rule)  # pylint: disable=protected-access
+  fa.scale = SCALE
+  fa.mask_value = -1e30
+  fa.error_record = tables.error_record.data_ptr()
+  ws_bytes = lib.splash_bwd_workspace_bytes(b, hq, s)
+  ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
+  ba = _native.SplashBwdArgs()
+  ba.q, ba.k, ba.v, ba.o, ba.d_o = map(splash._tensor_desc, (q, k, v, o, do))  # pylint: disable=protected-access
+  ba.dq, ba.dk, ba.dv = map(splash._tensor_desc, (dq, dk, dv))  # pylint: disable=protected-access
+  ba.logsumexp = lse.data_ptr()
+  ba.q_segment_ids, ba.kv_segment_ids = fa.q_segment_ids, fa.kv_segment_ids
+  ba.sched_dq, ba.sched_dkv = tables.dq, tables.dkv
+  ba.mask_fn = fa.mask_fn
+  ba.scale = SCALE
+  ba.workspace, ba.workspace_bytes = ws.data_ptr(), ws_bytes
+  ba.error_record = fa.error_record
+  stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+
+  def run_fwd():
+    _native.check(lib.splash_fwd(C.byref(fa), stream), "splash_fwd")
+
+  def run_bwd(mask):
+    ba.launch_mask = mask
+    _native.check(lib.splash_bwd(C.byref(ba), stream), "splash_bwd")
+
+  out = {}
+  out["fwd"] = timed_steps(run_fwd, iters, 2)
+  run_bwd(1)
+  out["delta"] = timed_steps(lambda: run_bwd(1), iters, 1)
+  out["dq"] = timed_steps(lambda: run_bwd(2), iters, 2)
+  out["dkv"] = timed_steps(lambda: run_bwd(4), iters, 2)
+  kernel.check_errors()
+  return out
+
+
+def cpu_baseline(w: dict, seconds_budget: float = 20.0) -> dict:
+  """Oracle forward + backward on the host cores over a bounded sample of the workload."""
+  from oracle import attention_ref
+  from tokamax_b200 import splash_attention_mask as mask_lib
+
+  s = min(w["seq"], 8192)  # the dense fp32 oracle holds S x S logits; cap the sample's sequence
+  group = w["q_heads"] // w["kv_heads"]
+  g = torch.Generator().manual_seed(1000 * w["config_id"])
+  mk = lambda h: torch.randn(1, h, s, D, generator=g, dtype=torch.float32).to(torch.bfloat16)
+  q, k, v, do = mk(group), mk(1), mk(1), mk(group)
+  if w["mask"] == "causal":
+    mask = mask_lib.make_causal_mask((s, s))
+    seg = None
+    n_live = s * (s + 1) // 2
+  else:
+    mask = mask_lib.make_local_attention_mask((s, s), (4096, 0))
+    ids = packed_segments(1, s, 3)
+    seg = (torch.from_numpy(ids), torch.from_numpy(ids))
+    n_live = live_pairs(dict(w, batch=1, seq=s), ids)
+  flops = 14 * D * group * n_live
+  t0 = time.perf_counter()
+  reps = 0
+  while True:
+    attention_ref.fwd_bwd(q, k, v, do, mask, seg, scale=SCALE)
+    reps += 1
+    dt = time.perf_counter() - t0
+    if dt > seconds_budget or reps >= 5:
+      break
+  return {
+      "value": flops * reps / dt / 1e12,
+      "unit": "TFLOP/s",
+      "cores": torch.get_num_threads(),
+      "kind": "port",
+      "sample": (f"1 batch row x 1 kv head ({group} q heads) of {w['mask']} seq {s}, fwd+bwd, {reps} reps in "
+                 f"{dt:.1f} s; torch-CPU fp32 restatement of the reference's attention_reference[_vjp]"),
+  }
+
+
+# ----------------------------------------------------------------------------------------------
+# arms
+# ----------------------------------------------------------------------------------------------
+def run_reference(args, w, wname):
+  """CPU arm: the reference's fp32 attention (restated; JAX is absent) on the host cores."""
+  rank = int(os.environ.get("RANK", "0"))
+  if rank != 0:
+    return
+  for _ in range(min(args.warmup, 1)):
+    cpu_baseline(w, seconds_budget=1.0)
+  t0 = time.perf_counter()
+  vals = [cpu_baseline(w, seconds_budget=4.0) for _ in range(args.steps)]
+  dt = (time.perf_counter() - t0) / max(args.steps, 1)
+  base = vals[-1]
+  value = float(np.mean([v["value"] for v in vals]))
+  base["value"] = value
+  line = {
+      "impl": "reference", "metric": "splash fwd+bwd TFLOP/s (masked FLOPs)", "value": value, "unit": "TFLOP/s",
+      "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
+      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+      "config": {"workload": wname, **{k: w[k] for k in ("batch", "q_heads", "kv_heads", "seq", "mask")},
+                 "head_dim": D, "note": "bounded sample per step on host cores"},
+      "cpu_baseline": base,
+      "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+      "gpu_launches": 0,
+  }
+  print(json.dumps(line), flush=True)
+
+
+def run_single_gpu(args, w, wname):
+  from tokamax_b200 import splash_attention_kernel as splash
+
+  dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+  torch.cuda.set_device(dev)
+  kernel = make_kernel(w)
+  seg = seg_np = None
+  if "segments" in w["mask"]:
+    seg_np = packed_segments(w["batch"], w["seq"], 3000)
+    seg_t = torch.from_numpy(seg_np).to(dev)
+    seg = (seg_t, seg_t)
+  n_live = live_pairs(w, seg_np)
+  flops = 14 * D * w["q_heads"] * n_live
+  big = w["batch"] * w["q_heads"] * w["seq"] > (1 << 22)
+  q, k, v, do = device_inputs(w, dev) if big else [t.to(dev) for t in host_inputs(w)]
+  seg_ids = splash.SegmentIds(*seg) if seg else None
+
+  def step():
+    qd, kd, vd = q.detach().requires_grad_(True), k.detach().requires_grad_(True), v.detach().requires_grad_(True)
+    out = kernel(qd, kd, vd, seg_ids, logits_scale=SCALE)
+    out.backward(do)
+    return out, qd.grad, kd.grad, vd.grad
+
+  sampler = ClockSampler(dev.index or 0)
+  for _ in range(args.warmup):
+    step()
+  torch.cuda.synchronize()
+  sampler.start()
+  ms = timed_steps(step, args.steps, 0)
+  clocks = sampler.stop()
+  kernel.check_errors()
+  value = flops / ms / 1e9
+
+  # ---- end to end: host buffers in, host buffers out, through the public API
+  e2e = None
+  if not args.no_e2e:
+    hq, hk, hv, hdo = [t.cpu().pin_memory() for t in (q, k, v, do)]
+    outs_host = [torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv)]
+    def e2e_step():
+      dq_, dk_, dv_, ddo_ = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
+      qd, kd, vd = dq_.requires_grad_(True), dk_.requires_grad_(True), dv_.requires_grad_(True)
+      out = kernel(qd, kd, vd, seg_ids, logits_scale=SCALE)
+      out.backward(ddo_)
+      for dst, src in zip(outs_host, (out.detach(), qd.grad, kd.grad, vd.grad)):
+        dst.copy_(src, non_blocking=True)
+    ms_e2e = timed_steps(e2e_step, max(2, min(args.steps, 5)), 1)
+    h2d = sum(t.numel() * 2 for t in (hq, hk, hv, hdo))
+    d2h = sum(t.numel() * 2 for t in outs_host)
+    e2e = {"value": flops / ms_e2e / 1e9, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h}
+
+  # ---- per-kernel times and the roofline of the dominant kernel
+  peak, peak_sustained, peak_src = measured_peaks()
+  kt = per_kernel_times(kernel, q, k, v, do, seg)
+  dominant = max(("fwd", "dq", "dkv"), key=lambda n: kt[n])
+  # Split of the 14*D FLOPs per live pair: forward 4*D (QK^T, PV); backward 10*D, attributed as dq
+  # kernel 4*D (dQ = dS K plus half of the shared S / dP recomputation) and dkv kernel 6*D (dK, dV
+  # plus the other half).
+  share = {"fwd": 4, "dq": 4, "dkv": 6}[dominant]
+  k_flops = share * D * w["q_heads"] * n_live
+  achieved = k_flops / kt[dominant] / 1e9
+  roofline = {
+      "kernel": {"fwd": "splash_fwd_kernel", "dq": "splash_dq_kernel", "dkv": "splash_dkv_kernel"}[dominant],
+      "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+      "peak_source": f"{peak_src} bf16 burst", "traffic": DKV_TRAFFIC_BYTES_C2 if (dominant == "dkv" and wname == "c2") else None,
+      "kernel_ms": kt,
+      "whole_step_frac_of_peak": value / peak, "whole_step_frac_of_sustained": value / peak_sustained,
+      "whole_step_frac_of_datasheet_2250": value / 2250.0,
+  }
+
+  line = {
+      "metric": "splash fwd+bwd TFLOP/s (masked FLOPs)", "value": value, "unit": "TFLOP/s", "n_gpus": 1,
+      "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+      "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+      "config": {"workload": wname, **{k_: w[k_] for k_ in ("batch", "q_heads", "kv_heads", "seq", "mask")},
+                 "head_dim": D, "n_live_pairs": n_live, "flops_per_step": flops,
+                 "l2": "inputs (>= 640 MB per step for c2) are larger than the 126 MB L2"},
+      "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * args.steps, "roofline": roofline,
+  }
+  if not args.no_cpu_baseline:
+    line["cpu_baseline"] = cpu_baseline(w)
+  print(json.dumps(line), flush=True)
+
+
+def run_context_parallel(args, w, wname):
+  import torch.distributed as dist
+  from tokamax_b200 import ulysses
+
+  rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+  local = int(os.environ.get("LOCAL_RANK", rank))
+  dev = torch.device("cuda", local)
+  torch.cuda.set_device(dev)
+  dist.init_process_group("nccl", device_id=dev)
+  kernel = make_kernel(w)
+  s_loc = w["seq"] // world
+  q, k, v, do = device_inputs(w, dev, seq_slice=s_loc)
+  cp = ulysses.UlyssesSplashAttention(kernel)
+  n_live = live_pairs(w, None)
+  flops = 14 * D * w["q_heads"] * n_live
+
+  def step():
+    qd, kd, vd = q.detach().requires_grad_(True), k.detach().requires_grad_(True), v.detach().requires_grad_(True)
+    out = cp(qd, kd, vd, logits_scale=SCALE)
+    out.backward(do)
+
+  def max_over_ranks(ms):
+    t = torch.tensor([ms], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return t.item()
+
+  sampler = ClockSampler(local)
+  for _ in range(args.warmup):
+    step()
+  dist.barrier()
+  torch.cuda.synchronize()
+  sampler.start()
+  ms = max_over_ranks(timed_steps(step, args.steps, 0, barrier=dist.barrier))
+  clocks = sampler.stop()
+  kernel.check_errors()
+
+  # exchange alone: the 4 + 4 all-to-alls of one step (q, k, v, o forward; do, dq, dk, dv backward)
+  def exchanges():
+    for t in (q, k, v, do):
+      ulysses._exchange(t, None, True)  # pylint: disable=protected-access
+    qh = torch.empty((w["batch"], w["q_heads"] // world, w["seq"], D), dtype=q.dtype, device=dev)
+    kh = torch.empty((w["batch"], w["kv_heads"] // world, w["seq"], D), dtype=q.dtype, device=dev)
+    for t in (qh, qh, kh, kh):
+      ulysses._exchange(t, None, False)  # pylint: disable=protected-access
+  a2a_ms = max_over_ranks(timed_steps(exchanges, 3, 1, barrier=dist.barrier))
+  sent = 2 * (2 * ulysses.exchange_bytes_sent(q.shape, 2, world) + 2 * ulysses.exchange_bytes_sent(k.shape, 2, world))
+
+  # end to end: each rank's sequence shard starts and ends in pinned host memory
+  e2e = None
+  if not args.no_e2e:
+    hq, hk, hv, hdo = [t.cpu().pin_memory() for t in (q, k, v, do)]
+    outs_host = [torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv)]
+    def e2e_step():
+      a, b_, c, d_ = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
+      qd, kd, vd = a.requires_grad_(True), b_.requires_grad_(True), c.requires_grad_(True)
+      out = cp(qd, kd, vd, logits_scale=SCALE)
+      out.backward(d_)
+      for dst, src in zip(outs_host, (out.detach(), qd.grad, kd.grad, vd.grad)):
+        dst.copy_(src, non_blocking=True)
+    ms_e2e = max_over_ranks(timed_steps(e2e_step, 2, 1, barrier=dist.barrier))
+    e2e = {"value": flops / ms_e2e / 1e9, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": world * sum(t.numel() * 2 for t in (hq, hk, hv, hdo)),
+           "d2h_bytes_per_step": world * sum(t.numel() * 2 for t in outs_host)}
+
+  if rank == 0:
+    peak, peak_sustained, peak_src = measured_peaks()
+    value = flops / ms / 1e9
+    line = {
+        "metric": "splash fwd+bwd TFLOP/s (masked FLOPs)", "value": value, "unit": "TFLOP/s", "n_gpus": world,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wname, **{k_: w[k_] for k_ in ("batch", "q_heads", "kv_heads", "seq", "mask")},
+                   "head_dim": D, "parallelism": f"ulysses cp{world}", "n_live_pairs": n_live,
+                   "flops_per_step": flops, "l2": "inputs are larger than the 126 MB L2"},
+        "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * args.steps,
+        "cp": {"tokens_per_s": w["batch"] * w["seq"] / (ms / 1e3), "a2a_ms_per_step": a2a_ms,
+               "a2a_bytes_sent_per_gpu": sent, "a2a_gbs_per_direction": sent / a2a_ms / 1e6,
+               "nvlink_nominal_gbs_per_direction": 900.0},
+        "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak_sustained, "unit": "TFLOP/s",
+                     "frac": value / world / peak_sustained, "peak_source": f"{peak_src} bf16 sustained, per GPU",
+                     "traffic": None},
+    }
+    print(json.dumps(line), flush=True)
+  dist.barrier()
+  dist.destroy_process_group()
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=10)
+  ap.add_argument("--warmup", type=int, default=3)
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+  ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4"])
+  ap.add_argument("--no-e2e", action="store_true")
+  ap.add_argument("--no-cpu-baseline", action="store_true")
+  args = ap.parse_args()
+  args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+  world = int(os.environ.get("WORLD_SIZE", "1"))
+  wname = args.workload
+  if wname == "auto":
+    wname = "c2" if world == 1 else "c4"
+  w = WORKLOADS[wname]
+  if args.impl == "reference":
+    run_reference(args, w, wname)
+    return
+  if not torch.cuda.is_available():
+    raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path for the kernels")
+  if world == 1:
+    run_single_gpu(args, w, wname)
+  else:
+    run_context_parallel(args, w, wname)
+
+
+if __name__ == "__main__":
+  main()

@@ -209,6 +209,9 @@ typedef struct SplashBwdArgs {
   void* workspace;
   size_t workspace_bytes;
   uint32_t* error_record;
+  uint32_t launch_mask;             /* 0 = everything; else bit 0 di pass, bit 1 dq kernel, bit 2
+                                       dkv kernel (for timing / profiling one kernel alone; the di
+                                       pass must have run on this workspace before bits 1 or 2) */
 } SplashBwdArgs;
 
 size_t splash_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);

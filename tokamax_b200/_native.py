@@ -141,6 +141,7 @@ class SplashBwdArgs(C.Structure):
       ("workspace", C.c_void_p),
       ("workspace_bytes", C.c_size_t),
       ("error_record", C.c_void_p),
+      ("launch_mask", C.c_uint32),
   ]
 
 

@@ -408,7 +408,25 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // ------------------------------------------------------------------------------------------
 // dkv kernel
 // ------------------------------------------------------------------------------------------
-// TMEM: S^T [0,128) | dP^T [128,256) | dK [256,384) | dV [384,512)
+// The q tile of a step is processed as two 64-column halves so that the score tiles can be
+// double-buffered next to the two 128-column accumulators:
+//   TMEM: S^T0 [0,64) | S^T1 [64,128) | dP^T0 [128,192) | dP^T1 [192,256) | dK [256,384) | dV [384,512)
+// While the compute warps turn S^T / dP^T of half h+1 into P^T / dS^T, the tensor core runs
+// dV += P^T dO and dK += dS^T Q of half h and the score MMAs of half h+2.
+struct DkvBarriers {
+  uint64_t stat_full[2];
+  uint64_t ring_full[kBwdStages];
+  uint64_t ring_empty[kBwdStages];
+  uint64_t st_full[2];
+  uint64_t dpt_full[2];
+  uint64_t p_full[2];
+  uint64_t ds_full[2];
+  uint64_t acc_done;
+  uint32_t tmem_base;
+  uint32_t abort_flag;
+  uint32_t early_exit;
+};
+
 __global__ void __launch_bounds__(kBwdThreads, 1)
 splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                   const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -419,7 +437,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint8_t* k_smem = smem;
   uint8_t* v_smem = smem + kTileBytes;
   uint8_t* ring = smem + 2 * kTileBytes;
-  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(smem + (2 + kBwdStages) * kTileBytes);
+  DkvBarriers* bars = reinterpret_cast<DkvBarriers*>(smem + (2 + kBwdStages) * kTileBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -431,6 +449,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int eend = p.row_ptr[kv_tile + 1];
   const int n_ent = eend - ebeg;
   const int n_steps = n_ent * group;
+  const int n_half = 2 * n_steps;
 
   if (threadIdx.x == 0) {
     bars->early_exit = *reinterpret_cast<volatile uint32_t*>(p.err);
@@ -441,11 +460,12 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(&bars->ring_full[s], 1);
       mbar_init(&bars->ring_empty[s], 1);
     }
-    mbar_init(&bars->s_full[0], 1);
-    mbar_init(&bars->s_full[1], 1);
-    mbar_init(&bars->dp_full, 1);
-    mbar_init(&bars->p_full, 256);
-    mbar_init(&bars->ds_full, 256);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->st_full[i], 1);
+      mbar_init(&bars->dpt_full[i], 1);
+      mbar_init(&bars->p_full[i], 8);   // one arrival per compute warp
+      mbar_init(&bars->ds_full[i], 8);
+    }
     mbar_init(&bars->acc_done, 1);
     mbar_fence_init();
   }
@@ -494,54 +514,80 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
   } else if (warp == 9) {
     if (lane == 0 && n_steps > 0) {
-      constexpr uint32_t idesc_kk = make_idesc_bf16(kTile, kTile, false, false);
-      constexpr uint32_t idesc_mn = make_idesc_bf16(kTile, kHeadDim, false, true);
+      constexpr uint32_t idesc_s = make_idesc_bf16(kTile, 64, false, false);
+      constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, kHeadDim, false, true);
       const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem), ring_addr = smem_u32(ring);
-      const uint32_t t_st = tmem, t_dpt = tmem + kTile, t_dk = tmem + 2 * kTile, t_dv = tmem + 3 * kTile;
-      auto ss_kmajor = [&](uint32_t d, uint32_t a0, uint32_t b0) {
+      const uint32_t t_dk = tmem + 2 * kTile, t_dv = tmem + 3 * kTile;
+      // scores of half h: S^T = K Q_h^T and dP^T = V dO_h^T, 128 x 64, K = head_dim
+      auto issue_scores = [&](int h) {
+        const int n = h >> 1, hh = h & 1;
+        const uint32_t q_slot = ring_addr + ((2 * n) % kBwdStages) * kTileBytes + hh * 8192;
+        const uint32_t do_slot = ring_addr + ((2 * n + 1) % kBwdStages) * kTileBytes + hh * 8192;
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(d, make_smem_desc_sw128(a0 + off, 16, 1024), make_smem_desc_sw128(b0 + off, 16, 1024),
-                  idesc_kk, k > 0 ? 1u : 0u);
+          umma_ss(tmem + hh * 64, make_smem_desc_sw128(k_addr + off, 16, 1024),
+                  make_smem_desc_sw128(q_slot + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
         }
-      };
-      auto ts_mn = [&](uint32_t d, uint32_t a_base, uint32_t b0, bool acc) {
+        tc_commit(&bars->st_full[hh]);
 #pragma unroll
-        for (int k = 0; k < 8; ++k)
-          umma_ts(d, a_base + packed_a_col(k), make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024),
-                  idesc_mn, (acc || k > 0) ? 1u : 0u);
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_ss(tmem + kTile + hh * 64, make_smem_desc_sw128(v_addr + off, 16, 1024),
+                  make_smem_desc_sw128(do_slot + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+        }
+        tc_commit(&bars->dpt_full[hh]);
+      };
+      // acc (+)= A_h B_h with A = packed bf16 [128 x 64] in TMEM, B = 64 rows of a q-side tile
+      // read MN-major.  K = 64 -> four K=16 slices; the two compute warpgroups wrote their 16
+      // packed columns at column offsets 0 and 32.
+      auto issue_acc = [&](uint32_t d, uint32_t a_base, uint32_t b0, bool acc) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_ts(d, a_base + (k >> 1) * 32 + (k & 1) * 8,
+                  make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024), idesc_acc,
+                  (acc || k > 0) ? 1u : 0u);
+      };
+      auto ring_wait = [&](uint32_t it, uint32_t tag) {
+        return mbar_wait(&bars->ring_full[it % kBwdStages], (it / kBwdStages) & 1u, ab, tag);
       };
       bool ok = mbar_wait(&bars->stat_full[0], 0, ab, 0x2200u) && mbar_wait(&bars->stat_full[1], 0, ab, 0x2201u);
-      for (int n = 0; n < n_steps && ok; ++n) {
-        const uint32_t it_q = 2 * n, it_do = 2 * n + 1;
-        const uint32_t q_slot = ring_addr + (it_q % kBwdStages) * kTileBytes;
-        const uint32_t do_slot = ring_addr + (it_do % kBwdStages) * kTileBytes;
-        ok = mbar_wait(&bars->ring_full[it_q % kBwdStages], (it_q / kBwdStages) & 1u, ab, 0x2210u);
+      ok = ok && ring_wait(0, 0x2210u) && ring_wait(1, 0x2211u);
+      if (ok) {
+        tc_fence_after();
+        issue_scores(0);
+        issue_scores(1);
+      }
+      for (int h = 0; h < n_half && ok; ++h) {
+        const int n = h >> 1, hh = h & 1;
+        const uint32_t ph = (uint32_t)n & 1u;
+        const uint32_t q_slot = ring_addr + ((2 * n) % kBwdStages) * kTileBytes + hh * 8192;
+        const uint32_t do_slot = ring_addr + ((2 * n + 1) % kBwdStages) * kTileBytes + hh * 8192;
+        ok = mbar_wait(&bars->p_full[hh], ph, ab, 0x2220u + hh);
         if (!ok) break;
         tc_fence_after();
-        ss_kmajor(t_st, k_addr, q_slot);  // S^T = K Q^T
-        tc_commit(&bars->s_full[0]);
-        ok = mbar_wait(&bars->ring_full[it_do % kBwdStages], (it_do / kBwdStages) & 1u, ab, 0x2211u);
+        issue_acc(t_dv, tmem + hh * 64, do_slot, h > 0);          // dV += P^T dO
+        ok = mbar_wait(&bars->ds_full[hh], ph, ab, 0x2230u + hh);
         if (!ok) break;
         tc_fence_after();
-        ss_kmajor(t_dpt, v_addr, do_slot);  // dP^T = V dO^T
-        tc_commit(&bars->dp_full);
-        ok = mbar_wait(&bars->p_full, n & 1u, ab, 0x2220u);
-        if (!ok) break;
-        tc_fence_after();
-        ts_mn(t_dv, t_st, do_slot, n > 0);  // dV += P^T dO
-        tc_commit(&bars->ring_empty[it_do % kBwdStages]);
-        ok = mbar_wait(&bars->ds_full, n & 1u, ab, 0x2230u);
-        if (!ok) break;
-        tc_fence_after();
-        ts_mn(t_dk, t_dpt, q_slot, n > 0);  // dK += dS^T Q
-        tc_commit(&bars->ring_empty[it_q % kBwdStages]);
+        issue_acc(t_dk, tmem + kTile + hh * 64, q_slot, h > 0);   // dK += dS^T Q
+        if (hh == 1) {
+          tc_commit(&bars->ring_empty[(2 * n) % kBwdStages]);
+          tc_commit(&bars->ring_empty[(2 * n + 1) % kBwdStages]);
+        }
+        if (h + 2 < n_half) {
+          if (hh == 0) {  // half h+2 opens step n+1: its tiles must have landed
+            ok = ring_wait(2 * (n + 1), 0x2240u) && ring_wait(2 * (n + 1) + 1, 0x2241u);
+            if (!ok) break;
+            tc_fence_after();
+          }
+          issue_scores(h + 2);
+        }
       }
       tc_commit(&bars->acc_done);
     }
   } else {
-    const int w = warp >> 2;       // q-column half this warpgroup owns
+    const int w = warp >> 2;       // 32-column quarter pair: this warpgroup owns columns [32w, 32w+32) of a half
     const int wq = warp & 3;
     const int r = wq * 32 + lane;  // kv row within the tile
     const int kv_row = kv_tile * kTile + r;
@@ -549,125 +595,135 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int kv_seg = has_seg ? p.kv_seg[(int64_t)batch * p.kv_len + kv_row] : 0;
     const int32_t* q_seg_row = has_seg ? p.q_seg + (int64_t)batch * p.q_len : nullptr;
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    const uint32_t t_st = tmem + lane_addr, t_dpt = tmem + lane_addr + kTile;
     const float c = p.scale_log2;
     bool ok = true;
-    int n = 0;
+    int h = 0;
 
     for (int g = 0; g < group && ok; ++g) {
       const int head = kv_head * group + g;
       const float* lse_row = p.lse + ((int64_t)batch * p.q_heads + head) * p.q_len;
       const float* delta_row = p.delta + ((int64_t)batch * p.q_heads + head) * p.q_len;
-      for (int e = ebeg; e < eend; ++e, ++n) {
+      for (int e = ebeg; e < eend && ok; ++e) {
         const int4 ent = p.entries[e];
         const int st = ent.y & 3;
-        const int q0 = ent.x * kTile + w * 64;  // first q column of this half
-        ok = mbar_wait(&bars->s_full[0], n & 1u, ab, 0x2400u);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        float pr[64];
-        {
-          uint32_t v[32];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            tmem_ld32(t_st + w * 64 + h * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int j = 0; j < 32; ++j) pr[h * 32 + j] = __uint_as_float(v[j]);
-          }
-        }
-        if (st == 1) {
-          if (p.fn.kind != SPLASH_MASK_TABLE) {
-            if (p.q_sequence == nullptr) {
-#pragma unroll
-              for (int j = 0; j < 64; ++j) {
-                const RowInterval iv = mask_fn_interval(p.fn, q0 + j);
-                if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
-              }
-            } else {
-#pragma unroll 4
-              for (int j = 0; j < 64; ++j) {
-                const RowInterval iv = mask_fn_interval(p.fn, __ldg(p.q_sequence + q0 + j));
-                if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
-              }
-            }
-          } else {
-            // dkv partial blocks are stored transposed: [id, kv, q]
-            const int8_t* mrow = p.pmb + ((int64_t)ent.z * p.pm_bkv + (kv_row % p.pm_bkv)) * p.pm_bq +
-                                 (q0 % p.pm_bq);
-            const int4* m4 = reinterpret_cast<const int4*>(mrow);
-#pragma unroll
-            for (int h = 0; h < 4; ++h) {
-              const int4 mv = __ldg(m4 + h);
-              const uint32_t wd[4] = {(uint32_t)mv.x, (uint32_t)mv.y, (uint32_t)mv.z, (uint32_t)mv.w};
-#pragma unroll
-              for (int j = 0; j < 16; ++j)
-                if (((wd[j >> 2] >> ((j & 3) * 8)) & 0xffu) == 0u) pr[h * 16 + j] = kMaskedLogit;
-            }
-          }
-        }
-        if (has_seg) {
-          const int4* sg4 = reinterpret_cast<const int4*>(q_seg_row + q0);
-#pragma unroll
-          for (int h = 0; h < 16; ++h) {
-            const int4 sv = __ldg(sg4 + h);
-            if (sv.x != kv_seg) pr[h * 4 + 0] = kMaskedLogit;
-            if (sv.y != kv_seg) pr[h * 4 + 1] = kMaskedLogit;
-            if (sv.z != kv_seg) pr[h * 4 + 2] = kMaskedLogit;
-            if (sv.w != kv_seg) pr[h * 4 + 3] = kMaskedLogit;
-          }
-        }
-        {
-          const float4* l4 = reinterpret_cast<const float4*>(lse_row + q0);
-          uint32_t pk[32];
-#pragma unroll
-          for (int h = 0; h < 16; ++h) {
-            const float4 lv = __ldg(l4 + h);
-            pr[h * 4 + 0] = ex2(fmaf(pr[h * 4 + 0], c, -lv.x * kLog2e));
-            pr[h * 4 + 1] = ex2(fmaf(pr[h * 4 + 1], c, -lv.y * kLog2e));
-            pr[h * 4 + 2] = ex2(fmaf(pr[h * 4 + 2], c, -lv.z * kLog2e));
-            pr[h * 4 + 3] = ex2(fmaf(pr[h * 4 + 3], c, -lv.w * kLog2e));
-            pk[h * 2 + 0] = pack_bf16(pr[h * 4 + 0], pr[h * 4 + 1]);
-            pk[h * 2 + 1] = pack_bf16(pr[h * 4 + 2], pr[h * 4 + 3]);
-          }
-          tmem_st32(t_st + packed_col(w), pk);
-          tmem_st_wait();
-          tc_fence_before();
-          mbar_arrive(&bars->p_full);
-        }
-        ok = mbar_wait(&bars->dp_full, n & 1u, ab, 0x2410u);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        tc_fence_after();
-        {
-          const float4* d4 = reinterpret_cast<const float4*>(delta_row + q0);
-          uint32_t pk[32];
-          uint32_t v[32];
-#pragma unroll
-          for (int h = 0; h < 2; ++h) {
-            tmem_ld32(t_dpt + w * 64 + h * 32, v);
-            tmem_ld_wait();
+#pragma unroll 1
+        for (int hh = 0; hh < 2; ++hh, ++h) {
+          const uint32_t ph = (uint32_t)(h >> 1) & 1u;
+          const int q0 = ent.x * kTile + hh * 64 + w * 32;  // first q column of this thread's 32
+          const uint32_t t_st = tmem + lane_addr + hh * 64 + w * 32;
+          const uint32_t t_dpt = tmem + lane_addr + kTile + hh * 64 + w * 32;
+          // per-column statistics, fetched before the waits so their latency hides there
+          float nlse[32], dlt[32];
+          {
+            const float4* l4 = reinterpret_cast<const float4*>(lse_row + q0);
+            const float4* d4 = reinterpret_cast<const float4*>(delta_row + q0);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float4 dv = __ldg(d4 + h * 8 + j);
-              const float a0 = pr[h * 32 + 4 * j + 0] * (__uint_as_float(v[4 * j + 0]) - dv.x);
-              const float a1 = pr[h * 32 + 4 * j + 1] * (__uint_as_float(v[4 * j + 1]) - dv.y);
-              const float a2 = pr[h * 32 + 4 * j + 2] * (__uint_as_float(v[4 * j + 2]) - dv.z);
-              const float a3 = pr[h * 32 + 4 * j + 3] * (__uint_as_float(v[4 * j + 3]) - dv.w);
-              pk[h * 16 + 2 * j + 0] = pack_bf16(a0, a1);
-              pk[h * 16 + 2 * j + 1] = pack_bf16(a2, a3);
+              const float4 lv = __ldg(l4 + j);
+              const float4 dv = __ldg(d4 + j);
+              nlse[4 * j + 0] = -lv.x * kLog2e;
+              nlse[4 * j + 1] = -lv.y * kLog2e;
+              nlse[4 * j + 2] = -lv.z * kLog2e;
+              nlse[4 * j + 3] = -lv.w * kLog2e;
+              dlt[4 * j + 0] = dv.x;
+              dlt[4 * j + 1] = dv.y;
+              dlt[4 * j + 2] = dv.z;
+              dlt[4 * j + 3] = dv.w;
             }
           }
-          tmem_st32(t_dpt + packed_col(w), pk);
-          tmem_st_wait();
-          tc_fence_before();
-          mbar_arrive(&bars->ds_full);
+          ok = mbar_wait(&bars->st_full[hh], ph, ab, 0x2400u + hh);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          float pr[32];
+          {
+            uint32_t v[32];
+            tmem_ld32(t_st, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 32; ++j) pr[j] = __uint_as_float(v[j]);
+          }
+          if (st == 1) {
+            if (p.fn.kind != SPLASH_MASK_TABLE) {
+              if (p.q_sequence == nullptr) {
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                  const RowInterval iv = mask_fn_interval(p.fn, q0 + j);
+                  if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
+                }
+              } else {
+#pragma unroll 4
+                for (int j = 0; j < 32; ++j) {
+                  const RowInterval iv = mask_fn_interval(p.fn, __ldg(p.q_sequence + q0 + j));
+                  if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
+                }
+              }
+            } else {
+              // dkv partial blocks are stored transposed: [id, kv, q]
+              const int8_t* mrow = p.pmb + ((int64_t)ent.z * p.pm_bkv + (kv_row % p.pm_bkv)) * p.pm_bq +
+                                   (q0 % p.pm_bq);
+              const int4* m4 = reinterpret_cast<const int4*>(mrow);
+#pragma unroll
+              for (int t = 0; t < 2; ++t) {
+                const int4 mv = __ldg(m4 + t);
+                const uint32_t wd[4] = {(uint32_t)mv.x, (uint32_t)mv.y, (uint32_t)mv.z, (uint32_t)mv.w};
+#pragma unroll
+                for (int j = 0; j < 16; ++j)
+                  if (((wd[j >> 2] >> ((j & 3) * 8)) & 0xffu) == 0u) pr[t * 16 + j] = kMaskedLogit;
+              }
+            }
+          }
+          if (has_seg) {
+            const int4* sg4 = reinterpret_cast<const int4*>(q_seg_row + q0);
+#pragma unroll
+            for (int t = 0; t < 8; ++t) {
+              const int4 sv = __ldg(sg4 + t);
+              if (sv.x != kv_seg) pr[t * 4 + 0] = kMaskedLogit;
+              if (sv.y != kv_seg) pr[t * 4 + 1] = kMaskedLogit;
+              if (sv.z != kv_seg) pr[t * 4 + 2] = kMaskedLogit;
+              if (sv.w != kv_seg) pr[t * 4 + 3] = kMaskedLogit;
+            }
+          }
+          {
+            uint32_t pk[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              pr[2 * j] = ex2(fmaf(pr[2 * j], c, nlse[2 * j]));
+              pr[2 * j + 1] = ex2(fmaf(pr[2 * j + 1], c, nlse[2 * j + 1]));
+              pk[j] = pack_bf16(pr[2 * j], pr[2 * j + 1]);
+            }
+            tmem_st16(t_st, pk);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->p_full[hh]);
+          }
+          ok = mbar_wait(&bars->dpt_full[hh], ph, ab, 0x2410u + hh);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          {
+            uint32_t pk[16];
+            uint32_t v[32];
+            tmem_ld32(t_dpt, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 16; ++j) {
+              const float a0 = pr[2 * j] * (__uint_as_float(v[2 * j]) - dlt[2 * j]);
+              const float a1 = pr[2 * j + 1] * (__uint_as_float(v[2 * j + 1]) - dlt[2 * j + 1]);
+              pk[j] = pack_bf16(a0, a1);
+            }
+            tmem_st16(t_dpt, pk);
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->ds_full[hh]);
+          }
         }
       }
     }
 
-    // epilogue: dK (scaled) and dV halves
+    // epilogue: dK (scaled) and dV, 64 columns per warpgroup
     __nv_bfloat16* dk = p.out0 + (int64_t)batch * p.out0_sb + (int64_t)kv_head * p.out0_sh +
                         (int64_t)kv_row * p.out0_ss + w * 64;
     __nv_bfloat16* dv = p.out1 + (int64_t)batch * p.out1_sb + (int64_t)kv_head * p.out1_sh +
@@ -680,14 +736,14 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       if (ok) {
         tc_fence_after();
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+        for (int t = 0; t < 2; ++t) {
           uint32_t v[32];
-          tmem_ld32(tmem + lane_addr + 2 * kTile + w * 64 + h * 32, v);
+          tmem_ld32(tmem + lane_addr + 2 * kTile + w * 64 + t * 32, v);
           tmem_ld_wait();
-          store_row_half(dk + h * 32, v, p.scale);
-          tmem_ld32(tmem + lane_addr + 3 * kTile + w * 64 + h * 32, v);
+          store_row_half(dk + t * 32, v, p.scale);
+          tmem_ld32(tmem + lane_addr + 3 * kTile + w * 64 + t * 32, v);
           tmem_ld_wait();
-          store_row_half(dv + h * 32, v, 1.0f);
+          store_row_half(dv + t * 32, v, 1.0f);
         }
       }
     } else {
@@ -708,6 +764,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     tmem_dealloc(tmem, 512);
   }
 }
+
 
 // ------------------------------------------------------------------------------------------
 // host launcher
@@ -755,8 +812,9 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
       (st = make_tile_tensor_map(&tm_k, a.k, kTile)) || (st = make_tile_tensor_map(&tm_v, a.v, kTile)))
     return st;
 
+  const uint32_t mask = a.launch_mask == 0 ? 7u : a.launch_mask;
   float* delta = static_cast<float*>(a.workspace);
-  {
+  if (mask & 1u) {
     DeltaParams dp;
     dp.o = static_cast<const __nv_bfloat16*>(a.o.data);
     dp.d_o = static_cast<const __nv_bfloat16*>(a.d_o.data);
@@ -813,7 +871,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.pm_bq = a.sched_dq.block_q > 0 ? a.sched_dq.block_q : kTile;
   p.pm_bkv = a.sched_dq.block_kv > 0 ? a.sched_dq.block_kv : kTile;
   p.n_rows = a.sched_dq.n_rows;
-  splash_dq_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hq, (unsigned)B), kBwdThreads, kBwdSmemBytes,
+  if (mask & 2u) splash_dq_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hq, (unsigned)B), kBwdThreads, kBwdSmemBytes,
                      stream>>>(tm_q, tm_do, tm_k, tm_v, p);
   if (cudaGetLastError() != cudaSuccess) return SPLASH_ERR_CUDA;
 
@@ -832,7 +890,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.pm_bq = a.sched_dkv.block_q > 0 ? a.sched_dkv.block_q : kTile;
   p.pm_bkv = a.sched_dkv.block_kv > 0 ? a.sched_dkv.block_kv : kTile;
   p.n_rows = a.sched_dkv.n_rows;
-  splash_dkv_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hkv, (unsigned)B), kBwdThreads, kBwdSmemBytes,
+  if (mask & 4u) splash_dkv_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hkv, (unsigned)B), kBwdThreads, kBwdSmemBytes,
                       stream>>>(tm_q, tm_do, tm_k, tm_v, p);
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
 }
