@@ -1,0 +1,92 @@
+"""Pins the numeric oracle (oracle/attention_ref.py).
+
+The reference keeps no stored tensors for this path (its kernel tests call its fp32 oracle at run
+time), and JAX is absent, so the restatement is checked against two independent evaluations:
+a float64 numpy softmax attention written from the definition, and torch autograd of the
+oracle's own forward for the backward formulas (both the "flash" and the "vanilla" di).
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention_ref
+from tokamax_b200 import splash_attention_mask as mask_lib
+
+
+def _numpy_attention(q, k, v, mask, scale):
+  q, k, v = (t.double().numpy() for t in (q, k, v))
+  group = q.shape[0] // k.shape[0]
+  outs, lses = [], []
+  for h in range(q.shape[0]):
+    logits = (q[h] @ k[h // group].T) * scale
+    logits = np.where(mask, logits, -np.inf)
+    m = logits.max(-1, keepdims=True)
+    e = np.exp(logits - m)
+    l = e.sum(-1, keepdims=True)
+    outs.append((e / l) @ v[h // group])
+    lses.append((m + np.log(l))[:, 0])
+  return np.stack(outs), np.stack(lses)
+
+
+@pytest.mark.parametrize("hq,hkv", [(2, 2), (4, 1), (6, 2)])
+def test_forward_matches_float64_definition(hq, hkv):
+  g = torch.Generator().manual_seed(hq * 10 + hkv)
+  s, t, d = 48, 80, 16
+  q, k, v = (torch.randn(h, n, d, generator=g) for h, n in ((hq, s), (hkv, t), (hkv, t)))
+  mask = mask_lib.make_causal_mask((s, t), offset=32)
+  o, lse, mx = attention_ref.attention_reference(q, k, v, mask, scale=0.3)
+  ro, rlse = _numpy_attention(q, k, v, mask, 0.3)
+  np.testing.assert_allclose(o.numpy(), ro, rtol=2e-5, atol=2e-6)
+  np.testing.assert_allclose(lse.numpy(), rlse, rtol=2e-6, atol=2e-6)
+  assert torch.all(mx <= lse + 1e-6)
+
+
+@pytest.mark.parametrize("impl", ["flash", "vanilla"])
+def test_backward_matches_autograd(impl):
+  g = torch.Generator().manual_seed(5)
+  hq, hkv, s, d = 4, 2, 40, 8
+  q = torch.randn(hq, s, d, generator=g, requires_grad=True)
+  k = torch.randn(hkv, s, d, generator=g, requires_grad=True)
+  v = torch.randn(hkv, s, d, generator=g, requires_grad=True)
+  do = torch.randn(hq, s, d, generator=g)
+  mask = mask_lib.make_local_attention_mask((s, s), (9, 0))
+  seg = torch.from_numpy(np.repeat(np.arange(4, dtype=np.int32), 10))
+  o, lse, _ = attention_ref.attention_reference(q, k, v, mask, (seg, seg), scale=0.5)
+  o.backward(do)
+  dq, dk, dv = attention_ref.attention_reference_vjp(
+      do, q.detach(), k.detach(), v.detach(), mask, (seg, seg), o.detach(), lse.detach(), scale=0.5,
+      backward_impl=impl)
+  torch.testing.assert_close(dq, q.grad, rtol=1e-4, atol=1e-5)
+  torch.testing.assert_close(dk, k.grad, rtol=1e-4, atol=1e-5)
+  torch.testing.assert_close(dv, v.grad, rtol=1e-4, atol=1e-5)
+
+
+def test_soft_cap_and_mqa_paths():
+  g = torch.Generator().manual_seed(9)
+  q = torch.randn(3, 16, 8, generator=g, requires_grad=True)
+  k = torch.randn(16, 8, generator=g, requires_grad=True)
+  v = torch.randn(16, 8, generator=g, requires_grad=True)
+  do = torch.randn(3, 16, 8, generator=g)
+  mask = mask_lib.make_causal_mask((16, 16))
+  o, lse, _ = attention_ref.attention_reference(q, k, v, mask, scale=1.0, attn_logits_soft_cap=5.0)
+  o.backward(do)
+  dq, dk, dv = attention_ref.attention_reference_vjp(do, q.detach(), k.detach(), v.detach(), mask, None,
+                                                     o.detach(), lse.detach(), attn_logits_soft_cap=5.0)
+  torch.testing.assert_close(dq, q.grad, rtol=1e-4, atol=1e-5)
+  torch.testing.assert_close(dk, k.grad, rtol=1e-4, atol=1e-5)
+  torch.testing.assert_close(dv, v.grad, rtol=1e-4, atol=1e-5)
+  assert dk.shape == k.shape
+
+
+def test_masked_rows_use_the_finite_mask_value():
+  """A fully masked row averages V (the reference's finite mask value, base.py:28-30,99)."""
+  q = torch.zeros(1, 4, 8)
+  k = torch.zeros(1, 4, 8)
+  v = torch.arange(32, dtype=torch.float32).view(1, 4, 8)
+  mask = np.zeros((4, 4), bool)
+  mask[1:] = np.tril(np.ones((4, 4), bool))[1:]
+  o, lse, mx = attention_ref.attention_reference(q, k, v, mask)
+  torch.testing.assert_close(o[0, 0], v[0].mean(0))
+  assert mx[0, 0].item() == pytest.approx(attention_ref.DEFAULT_MASK_VALUE)

@@ -30,7 +30,9 @@ struct DeltaParams {
   const __nv_bfloat16* o;
   const __nv_bfloat16* d_o;
   int64_t o_sb, o_sh, o_ss, do_sb, do_sh, do_ss;
-  float* delta;  // [B, Hq, Sq]
+  float* delta;      // [B, Hq, Sq]
+  const float* lse;  // [B, Hq, Sq] natural log
+  float* nlse2;      // [B, Hq, Sq]  -lse * log2(e): the exponent offset the MMA kernels subtract
   int q_heads, q_len;
   int64_t n_rows;
 };
@@ -58,7 +60,10 @@ __global__ void __launch_bounds__(256) splash_delta_kernel(const DeltaParams p) 
               __bfloat162float(a1.y) * __bfloat162float(g1.y);
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) p.delta[row] = acc;
+  if (lane == 0) {
+    p.delta[row] = acc;
+    p.nlse2[row] = -p.lse[row] * kLog2e;
+  }
 }
 
 // ------------------------------------------------------------------------------------------
@@ -70,7 +75,7 @@ struct BwdParams {
   int64_t out0_sb, out0_sh, out0_ss;
   __nv_bfloat16* out1;
   int64_t out1_sb, out1_sh, out1_ss;
-  const float* lse;    // [B, Hq, Sq] natural log
+  const float* nlse2;  // [B, Hq, Sq]  -logsumexp * log2(e)
   const float* delta;  // [B, Hq, Sq]
   const int32_t* q_seg;
   const int32_t* kv_seg;
@@ -161,8 +166,8 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     mbar_init(&bars->s_full[0], 1);
     mbar_init(&bars->s_full[1], 1);
     mbar_init(&bars->dp_full, 1);
-    mbar_init(&bars->p_full, 256);
-    mbar_init(&bars->ds_full, 256);
+    mbar_init(&bars->p_full, 8);
+    mbar_init(&bars->ds_full, 8);  // one arrival per compute warp
     mbar_init(&bars->acc_done, 1);
     mbar_fence_init();
   }
@@ -284,14 +289,16 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int q_seg = has_seg ? p.q_seg[(int64_t)batch * p.q_len + q_row] : 0;
     const int32_t* kv_seg_row = has_seg ? p.kv_seg + (int64_t)batch * p.kv_len : nullptr;
     const int64_t stat = ((int64_t)batch * p.q_heads + head) * p.q_len + q_row;
-    const float lse2 = p.lse[stat] * kLog2e;
+    const float nlse2 = p.nlse2[stat];
     const float delta = p.delta[stat];
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     const float c = p.scale_log2;
     bool ok = true;
 
+    int4 ent_next = n_ent > 0 ? p.entries[ebeg] : make_int4(0, 0, 0, 0);
     for (int n = 0; n < n_ent; ++n) {
-      const int4 ent = p.entries[ebeg + n];
+      const int4 ent = ent_next;
+      if (n + 1 < n_ent) ent_next = p.entries[ebeg + n + 1];  // fetched a step ahead of its use
       const int st = ent.y & 3;
       const int kv0 = ent.x * kTile + w * 64;
       const uint32_t t_s = tmem + lane_addr + (n & 1) * kTile;
@@ -301,13 +308,14 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tc_fence_after();
       float pr[64];
       {
-        uint32_t v[32];
+        uint32_t v0[32], v1[32];
+        tmem_ld32(t_s + w * 64, v0);
+        tmem_ld32(t_s + w * 64 + 32, v1);
+        tmem_ld_wait();
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          tmem_ld32(t_s + w * 64 + g * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) pr[g * 32 + j] = __uint_as_float(v[j]);
+        for (int j = 0; j < 32; ++j) {
+          pr[j] = __uint_as_float(v0[j]);
+          pr[32 + j] = __uint_as_float(v1[j]);
         }
       }
       if (st == 1) {
@@ -343,7 +351,7 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
 #pragma unroll
-      for (int j = 0; j < 64; ++j) pr[j] = ex2(fmaf(pr[j], c, -lse2));
+      for (int j = 0; j < 64; ++j) pr[j] = ex2(fmaf(pr[j], c, nlse2));
 
       ok = mbar_wait(&bars->dp_full, n & 1u, ab, 0x1410u);
       ok = __all_sync(0xffffffffu, ok);
@@ -351,23 +359,23 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tc_fence_after();
       uint32_t pk[32];
       {
-        uint32_t v[32];
+        uint32_t v0[32], v1[32];
+        tmem_ld32(tmem + lane_addr + 2 * kTile + w * 64, v0);
+        tmem_ld32(tmem + lane_addr + 2 * kTile + w * 64 + 32, v1);
+        tmem_ld_wait();
 #pragma unroll
-        for (int g = 0; g < 2; ++g) {
-          tmem_ld32(tmem + lane_addr + 2 * kTile + w * 64 + g * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float d0 = pr[g * 32 + 2 * j] * (__uint_as_float(v[2 * j]) - delta);
-            const float d1 = pr[g * 32 + 2 * j + 1] * (__uint_as_float(v[2 * j + 1]) - delta);
-            pk[g * 16 + j] = pack_bf16(d0, d1);
-          }
+        for (int j = 0; j < 16; ++j) {
+          pk[j] = pack_bf16(pr[2 * j] * (__uint_as_float(v0[2 * j]) - delta),
+                            pr[2 * j + 1] * (__uint_as_float(v0[2 * j + 1]) - delta));
+          pk[16 + j] = pack_bf16(pr[32 + 2 * j] * (__uint_as_float(v1[2 * j]) - delta),
+                                 pr[32 + 2 * j + 1] * (__uint_as_float(v1[2 * j + 1]) - delta));
         }
       }
       tmem_st32(t_s + packed_col(w), pk);
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars->ds_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->ds_full);
     }
 
     // epilogue
@@ -413,6 +421,9 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 //   TMEM: S^T0 [0,64) | S^T1 [64,128) | dP^T0 [128,192) | dP^T1 [192,256) | dK [256,384) | dV [384,512)
 // While the compute warps turn S^T / dP^T of half h+1 into P^T / dS^T, the tensor core runs
 // dV += P^T dO and dK += dS^T Q of half h and the score MMAs of half h+2.
+constexpr int kDkvStatsBytes = (kBwdStages / 2) * 2 * kTile * 4;
+constexpr int kDkvSmemBytes = (2 + kBwdStages) * kTileBytes + kDkvStatsBytes + 1024 + 1024;
+
 struct DkvBarriers {
   uint64_t stat_full[2];
   uint64_t ring_full[kBwdStages];
@@ -437,7 +448,9 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint8_t* k_smem = smem;
   uint8_t* v_smem = smem + kTileBytes;
   uint8_t* ring = smem + 2 * kTileBytes;
-  DkvBarriers* bars = reinterpret_cast<DkvBarriers*>(smem + (2 + kBwdStages) * kTileBytes);
+  // per-step row statistics of the q tile in flight: [slot][0: -lse*log2e | 1: di][128]
+  float* stats = reinterpret_cast<float*>(smem + (2 + kBwdStages) * kTileBytes);
+  DkvBarriers* bars = reinterpret_cast<DkvBarriers*>(smem + (2 + kBwdStages) * kTileBytes + kDkvStatsBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -497,6 +510,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       bool ok = true;
       for (int g = 0; g < group && ok; ++g) {
         const int head = kv_head * group + g;
+        const int64_t stat_base = ((int64_t)batch * p.q_heads + head) * p.q_len;
         for (int e = ebeg; e < eend && ok; ++e) {
           const int qt = p.entries[e].x;
           for (int which = 0; which < 2 && ok; ++which, ++it) {
@@ -505,9 +519,14 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (!ok) break;
             uint8_t* dst = ring + s * kTileBytes;
             const CUtensorMap* tm = which == 0 ? &tm_q : &tm_do;
-            mbar_arrive_expect_tx(&bars->ring_full[s], kTileBytes);
+            mbar_arrive_expect_tx(&bars->ring_full[s], which == 0 ? kTileBytes + 2 * kTile * 4 : kTileBytes);
             tma_load_4d(dst, tm, &bars->ring_full[s], 0, qt * kTile, head, batch);
             tma_load_4d(dst + kHalfBytes, tm, &bars->ring_full[s], 64, qt * kTile, head, batch);
+            if (which == 0) {  // the step's statistics ride on the Q slot's barrier
+              float* sdst = stats + (s / 2) * 2 * kTile;
+              bulk_load(sdst, p.nlse2 + stat_base + (int64_t)qt * kTile, kTile * 4, &bars->ring_full[s]);
+              bulk_load(sdst + kTile, p.delta + stat_base + (int64_t)qt * kTile, kTile * 4, &bars->ring_full[s]);
+            }
           }
         }
       }
@@ -600,31 +619,39 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     int h = 0;
 
     for (int g = 0; g < group && ok; ++g) {
-      const int head = kv_head * group + g;
-      const float* lse_row = p.lse + ((int64_t)batch * p.q_heads + head) * p.q_len;
-      const float* delta_row = p.delta + ((int64_t)batch * p.q_heads + head) * p.q_len;
+      int4 ent_next = n_ent > 0 ? p.entries[ebeg] : make_int4(0, 0, 0, 0);
       for (int e = ebeg; e < eend && ok; ++e) {
-        const int4 ent = p.entries[e];
+        const int4 ent = ent_next;
+        if (e + 1 < eend) ent_next = p.entries[e + 1];  // fetched a step ahead of its use
         const int st = ent.y & 3;
 #pragma unroll 1
         for (int hh = 0; hh < 2; ++hh, ++h) {
-          const uint32_t ph = (uint32_t)(h >> 1) & 1u;
+          const int n = h >> 1;
+          const uint32_t ph = (uint32_t)n & 1u;
           const int q0 = ent.x * kTile + hh * 64 + w * 32;  // first q column of this thread's 32
           const uint32_t t_st = tmem + lane_addr + hh * 64 + w * 32;
           const uint32_t t_dpt = tmem + lane_addr + kTile + hh * 64 + w * 32;
-          // per-column statistics, fetched before the waits so their latency hides there
+          // Per-column statistics of this step, staged in shared memory by the producer on the
+          // Q slot's barrier; broadcast reads, taken before the score waits.
+          {
+            const uint32_t itq = 2u * (uint32_t)n;
+            ok = mbar_wait(&bars->ring_full[itq % kBwdStages], (itq / kBwdStages) & 1u, ab, 0x2420u);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+          }
           float nlse[32], dlt[32];
           {
-            const float4* l4 = reinterpret_cast<const float4*>(lse_row + q0);
-            const float4* d4 = reinterpret_cast<const float4*>(delta_row + q0);
+            const float* sbase = stats + ((2 * n) % kBwdStages / 2) * 2 * kTile + hh * 64 + w * 32;
+            const float4* l4 = reinterpret_cast<const float4*>(sbase);
+            const float4* d4 = reinterpret_cast<const float4*>(sbase + kTile);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const float4 lv = __ldg(l4 + j);
-              const float4 dv = __ldg(d4 + j);
-              nlse[4 * j + 0] = -lv.x * kLog2e;
-              nlse[4 * j + 1] = -lv.y * kLog2e;
-              nlse[4 * j + 2] = -lv.z * kLog2e;
-              nlse[4 * j + 3] = -lv.w * kLog2e;
+              const float4 lv = l4[j];
+              const float4 dv = d4[j];
+              nlse[4 * j + 0] = lv.x;
+              nlse[4 * j + 1] = lv.y;
+              nlse[4 * j + 2] = lv.z;
+              nlse[4 * j + 3] = lv.w;
               dlt[4 * j + 0] = dv.x;
               dlt[4 * j + 1] = dv.y;
               dlt[4 * j + 2] = dv.z;
@@ -772,7 +799,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 size_t bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {
   if (batch <= 0 || q_heads <= 0 || q_len <= 0) return 0;
   const size_t n = (size_t)batch * (size_t)q_heads * (size_t)q_len * sizeof(float);
-  return (n + 255) & ~(size_t)255;
+  return 2 * ((n + 255) & ~(size_t)255);  // di, then -logsumexp * log2(e)
 }
 
 int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
@@ -814,6 +841,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
 
   const uint32_t mask = a.launch_mask == 0 ? 7u : a.launch_mask;
   float* delta = static_cast<float*>(a.workspace);
+  float* nlse2 = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + bwd_workspace_bytes(B, Hq, Sq) / 2);
   if (mask & 1u) {
     DeltaParams dp;
     dp.o = static_cast<const __nv_bfloat16*>(a.o.data);
@@ -825,6 +853,8 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     dp.do_sh = a.d_o.stride[1];
     dp.do_ss = a.d_o.stride[2];
     dp.delta = delta;
+    dp.lse = a.logsumexp;
+    dp.nlse2 = nlse2;
     dp.q_heads = (int)Hq;
     dp.q_len = (int)Sq;
     dp.n_rows = B * Hq * Sq;
@@ -838,13 +868,13 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     if (cudaFuncSetAttribute(splash_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kBwdSmemBytes) != cudaSuccess ||
         cudaFuncSetAttribute(splash_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kBwdSmemBytes) != cudaSuccess)
+                             kDkvSmemBytes) != cudaSuccess)
       return SPLASH_ERR_CUDA;
     attr_set = true;
   }
 
   BwdParams p;
-  p.lse = a.logsumexp;
+  p.nlse2 = nlse2;
   p.delta = delta;
   p.q_seg = a.q_segment_ids;
   p.kv_seg = a.kv_segment_ids;
@@ -890,7 +920,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.pm_bq = a.sched_dkv.block_q > 0 ? a.sched_dkv.block_q : kTile;
   p.pm_bkv = a.sched_dkv.block_kv > 0 ? a.sched_dkv.block_kv : kTile;
   p.n_rows = a.sched_dkv.n_rows;
-  if (mask & 4u) splash_dkv_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hkv, (unsigned)B), kBwdThreads, kBwdSmemBytes,
+  if (mask & 4u) splash_dkv_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hkv, (unsigned)B), kBwdThreads, kDkvSmemBytes,
                       stream>>>(tm_q, tm_do, tm_k, tm_v, p);
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
 }

@@ -1,10 +1,12 @@
 // Splash attention forward for sm_100a: bf16 Q/K/V, head_dim 128, fp32 accumulation.
 //
 // One CTA owns two adjacent 128-row q tiles of one (batch, q head) and walks the kv tiles its
-// schedule row lists.  Roles (320 threads):
+// schedule row lists.  Roles (384 threads):
 //   warps 0-3 / 4-7 : softmax warpgroup of q tile 0 / 1 — one thread per score row
 //   warp 8          : TMA producer (Q once, then a 4-slot ring of K and V tiles)
 //   warp 9          : tcgen05 MMA issuer (and TMEM allocator)
+//   warps 10-11     : idle; they complete the third warpgroup so registers can be handed
+//                     from it to the softmax warpgroups (setmaxnreg)
 // TMEM (512 columns): S0 | S1 | O0 | O1, 128 fp32 columns each.  P (bf16, two values per
 // column) overwrites the first 64 columns of its S tile and feeds the PV MMA straight from TMEM.
 // The two tiles ping-pong: while the softmax of tile 0 runs on the SIMT lanes, the tensor core
@@ -23,7 +25,9 @@
 namespace sb {
 
 constexpr int kFwdStages = 4;
-constexpr int kFwdThreads = 320;
+constexpr int kFwdThreads = 384;  // 3 warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
+constexpr int kSoftmaxRegs = 224;  // setmaxnreg targets: 2*128*224 + 128*56 <= 64K registers
+constexpr int kIssueRegs = 56;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
 
 struct FwdParams {
@@ -85,7 +89,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->q_full[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->p_full[i], 128);
+      mbar_init(&bars->p_full[i], 4);  // one arrival per softmax warp
       mbar_init(&bars->o_done[i], 1);
     }
     for (int s = 0; s < kFwdStages; ++s) {
@@ -107,7 +111,11 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t tmem = bars->tmem_base;
   AbortCtx ab{&bars->abort_flag, p.err};
 
-  if (warp == 8) {
+  if (warp >= 8) {
+   setmaxnreg_dec<kIssueRegs>();
+   if (warp >= 10) {
+    // idle warps: only there to complete the third warpgroup for the register hand-over
+   } else if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       tma_prefetch_desc(&tm_q);
@@ -185,10 +193,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if ((e0.y >> (2 * i)) & 3) issue_qk(i, 0);
           tc_commit(&bars->kv_empty[0]);
         }
+        int4 nxt = e0;
         for (int n = 0; n < n_ent && ok; ++n) {
-          const int4 cur = p.entries[ebeg + n];
+          const int4 cur = nxt;
           const bool has_next = n + 1 < n_ent;
-          int4 nxt = cur;
           if (has_next) nxt = p.entries[ebeg + n + 1];
           const uint32_t itv = 2 * n + 1, itk = 2 * n + 2;
           const uint32_t vslot = itv % kFwdStages, kslot = itk % kFwdStages;
@@ -215,8 +223,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tc_commit(&bars->o_done[0]);
       tc_commit(&bars->o_done[1]);
     }
+   }
   } else {
     // ------------------------------------------------------------------ softmax warpgroups
+    setmaxnreg_inc<kSoftmaxRegs>();
     const int i = warp >> 2;           // q tile within the pair
     const int wq = warp & 3;           // TMEM lane quarter this warp may touch
     const int r = wq * 32 + lane;      // row within the tile
@@ -240,8 +250,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     bool started = false;
     bool ok = true;
 
+    int4 ent_next = ebeg < eend ? p.entries[ebeg] : make_int4(0, 0, 0, 0);
     for (int e = ebeg; e < eend; ++e) {
-      const int4 ent = p.entries[e];
+      const int4 ent = ent_next;
+      if (e + 1 < eend) ent_next = p.entries[e + 1];  // fetched a step ahead of its use
       const int st = (ent.y >> (2 * i)) & 3;
       if (st == 0) continue;
       ok = mbar_wait(&bars->s_full[i], cnt & 1u, ab, 0x400u + i);
@@ -252,13 +264,18 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
       float s[kTile];
       {
-        uint32_t v[32];
+        uint32_t v0[32], v1[32], v2[32], v3[32];
+        tmem_ld32(t_s, v0);
+        tmem_ld32(t_s + 32, v1);
+        tmem_ld32(t_s + 64, v2);
+        tmem_ld32(t_s + 96, v3);
+        tmem_ld_wait();
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          tmem_ld32(t_s + g * 32, v);
-          tmem_ld_wait();
-#pragma unroll
-          for (int j = 0; j < 32; ++j) s[g * 32 + j] = __uint_as_float(v[j]);
+        for (int j = 0; j < 32; ++j) {
+          s[j] = __uint_as_float(v0[j]);
+          s[32 + j] = __uint_as_float(v1[j]);
+          s[64 + j] = __uint_as_float(v2[j]);
+          s[96 + j] = __uint_as_float(v3[j]);
         }
       }
       const int kv0 = ent.x * kTile;
@@ -343,7 +360,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       l += ls0 + ls1;
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(&bars->p_full[i]);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bars->p_full[i]);
       started = true;
     }
 
