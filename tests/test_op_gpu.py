@@ -1,0 +1,76 @@
+"""Op-level entry point (dot_product_attention, implementation="cuda_sm100") against the oracle."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention_ref
+from tokamax_b200 import op
+from tokamax_b200 import splash_attention_mask as mask_lib
+
+pytestmark = pytest.mark.gpu
+D = 128
+
+
+def _bthd(seed, b, t, n):
+  g = torch.Generator().manual_seed(seed)
+  return torch.randn(b, t, n, D, generator=g).to(torch.bfloat16)
+
+
+def _oracle(q, k, v, mask, scale):
+  outs = []
+  for b in range(q.shape[0]):
+    o, _, _ = attention_ref.attention_reference(q[b].permute(1, 0, 2), k[b].permute(1, 0, 2), v[b].permute(1, 0, 2),
+                                                mask, scale=scale)
+    outs.append(o.permute(1, 0, 2))
+  return torch.stack(outs)
+
+
+@pytest.mark.parametrize("kind", ["causal", "full", "local", "local_causal", "bool_mask"])
+def test_op_matches_oracle(kind):
+  b, t, n, kh = 2, 384, 4, 2
+  q, k, v = _bthd(1, b, t, n), _bthd(2, b, t, kh), _bthd(3, b, t, kh)
+  dev = torch.device("cuda:0")
+  kwargs, dense = {}, np.ones((t, t), bool)
+  if kind == "causal":
+    kwargs, dense = dict(is_causal=True), mask_lib.make_causal_mask((t, t))
+  elif kind == "local":
+    kwargs, dense = dict(local_window_size=(100, 28)), mask_lib.make_local_attention_mask((t, t), (100, 28))
+  elif kind == "local_causal":
+    kwargs = dict(local_window_size=150, is_causal=True)
+    dense = mask_lib.make_local_attention_mask((t, t), (150, 0))
+  elif kind == "bool_mask":
+    dense = mask_lib.make_random_mask((t, t), 0.5, 4) | np.eye(t, dtype=bool)
+    kwargs = dict(mask=torch.from_numpy(dense))
+  out = op.dot_product_attention(q.to(dev), k.to(dev), v.to(dev), implementation="cuda_sm100", **kwargs)
+  assert out.shape == (b, t, n, D)
+  ref = _oracle(q, k, v, dense, 1 / math.sqrt(D))
+  # bf16 output: half an ulp is 2^-9 relative, which alone exceeds 1e-2 once |o| >= 4 (rows with
+  # few live keys), so the bound is the reference tests' atol + rtol * |ref| form here.
+  assert ((out.float().cpu() - ref).abs() <= 1e-2 + 4e-3 * ref.abs()).all()
+
+
+def test_op_backward_and_residuals():
+  b, t, n, kh = 1, 256, 2, 1
+  dev = torch.device("cuda:0")
+  q, k, v = (x.to(dev).requires_grad_(True) for x in (_bthd(4, b, t, n), _bthd(5, b, t, kh), _bthd(6, b, t, kh)))
+  out = op.dot_product_attention(q, k, v, is_causal=True, scale=0.1)
+  out.float().square().sum().backward()
+  assert q.grad.shape == q.shape and k.grad.shape == k.shape and torch.isfinite(v.grad.float()).all()
+  o2, (mx, lse) = op.IMPLEMENTATIONS["cuda_sm100"](q.detach(), k.detach(), v.detach(), is_causal=True,
+                                                   logits_scale=0.1, return_residuals=True)
+  assert mx.shape == (b, n, t) and lse.shape == (b, n, t) and torch.equal(o2, out.detach())
+
+
+def test_op_dispatch_errors():
+  dev = torch.device("cuda:0")
+  q = torch.zeros(1, 128, 2, D, dtype=torch.bfloat16, device=dev)
+  with pytest.raises(NotImplementedError):
+    op.dot_product_attention(q, q, q, bias=torch.zeros(1, device=dev), implementation="cuda_sm100")
+  with pytest.raises(ExceptionGroup):
+    op.dot_product_attention(q, q, q, logits_soft_cap=3.0, implementation=["cuda_sm100", "cuda_sm100"])
+  with pytest.raises(ValueError):
+    op.dot_product_attention(q, q, q, implementation="nope")
+  with pytest.raises(ValueError):
+    op.dot_product_attention(q, q, q, implementation=[])

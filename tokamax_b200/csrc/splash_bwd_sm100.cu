@@ -21,7 +21,10 @@
 namespace sb {
 
 constexpr int kBwdStages = 4;
-constexpr int kBwdThreads = 320;  // 8 compute warps + TMA warp + MMA warp
+constexpr int kBwdThreads = 384;  // 8 compute warps + TMA warp + MMA warp + 2 idle warps that
+                                  // complete the third warpgroup for the register hand-over
+constexpr int kComputeRegs = 224;
+constexpr int kIssueRegs = 56;
 
 // ------------------------------------------------------------------------------------------
 // delta = rowsum(o * do)
@@ -183,7 +186,9 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const uint32_t tmem = bars->tmem_base;
   AbortCtx ab{&bars->abort_flag, p.err};
 
-  if (warp == 8) {
+  if (warp >= 8) {
+   setmaxnreg_dec<kIssueRegs>();
+   if (warp == 8) {
     if (lane == 0 && n_ent > 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_do);
@@ -232,13 +237,13 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // prologue: S_0, dP_0
       ok = ok && ring_wait(0, 0x1210u);
       if (ok) {
-        tc_fence_after();
+        mma_issue_fence();
         ss_kmajor(tmem, q_addr, ring_addr);
         tc_commit(&bars->s_full[0]);
       }
       ok = ok && ring_wait(1, 0x1211u);
       if (ok) {
-        tc_fence_after();
+        mma_issue_fence();
         ss_kmajor(t_dp, do_addr, ring_addr + kTileBytes);
         tc_commit(&bars->dp_full);
         tc_commit(&bars->ring_empty[1]);
@@ -249,13 +254,23 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (has_next) {
           ok = ring_wait(it_kn, 0x1220u);
           if (!ok) break;
-          tc_fence_after();
+          mma_issue_fence();
           ss_kmajor(tmem + ((n + 1) & 1) * kTile, q_addr, ring_addr + (it_kn % kBwdStages) * kTileBytes);
           tc_commit(&bars->s_full[(n + 1) & 1]);
         }
         ok = mbar_wait(&bars->ds_full, n & 1u, ab, 0x1230u);
         if (!ok) break;
-        tc_fence_after();
+        mma_issue_fence();
+#ifdef SPLASH_DQ_DP_FIRST
+        // dP of the next step goes first: the compute warps wait on it, while nothing waits on dQ.
+        if (has_next) {
+          ok = ring_wait(it_vn, 0x1240u);
+          if (!ok) break;
+          mma_issue_fence();
+          ss_kmajor(t_dp, do_addr, ring_addr + (it_vn % kBwdStages) * kTileBytes);
+          tc_commit(&bars->dp_full);
+          tc_commit(&bars->ring_empty[it_vn % kBwdStages]);
+        }
         {
           // dQ += dS_n K_n : A = packed dS in the S buffer, B = K tile read MN-major.
           const uint32_t a_base = tmem + (n & 1) * kTile;
@@ -266,19 +281,34 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     idesc_mn, (n > 0 || k > 0) ? 1u : 0u);
           tc_commit(&bars->ring_empty[it_k % kBwdStages]);
         }
+#else
+        {
+          // dQ += dS_n K_n : A = packed dS in the S buffer, B = K tile read MN-major.
+          const uint32_t a_base = tmem + (n & 1) * kTile;
+          const uint32_t b0 = ring_addr + (it_k % kBwdStages) * kTileBytes;
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma_ts(t_dq, a_base + packed_a_col(k), make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024),
+                    idesc_mn, (n > 0 || k > 0) ? 1u : 0u);
+          tc_commit(&bars->ring_empty[it_k % kBwdStages]);
+        }
+        // dP of the next step goes first: the compute warps wait on it, while nothing waits on dQ.
         if (has_next) {
           ok = ring_wait(it_vn, 0x1240u);
           if (!ok) break;
-          tc_fence_after();
+          mma_issue_fence();
           ss_kmajor(t_dp, do_addr, ring_addr + (it_vn % kBwdStages) * kTileBytes);
           tc_commit(&bars->dp_full);
           tc_commit(&bars->ring_empty[it_vn % kBwdStages]);
         }
+#endif
       }
       tc_commit(&bars->acc_done);
     }
+   }
   } else {
     // ------------------------------------------------------------------ compute warpgroups
+    setmaxnreg_inc<kComputeRegs>();
     const int w = warp >> 2;       // column half this warpgroup owns
     const int wq = warp & 3;
     const int r = wq * 32 + lane;  // q row within the tile
@@ -476,8 +506,8 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->st_full[i], 1);
       mbar_init(&bars->dpt_full[i], 1);
-      mbar_init(&bars->p_full[i], 8);   // one arrival per compute warp
-      mbar_init(&bars->ds_full[i], 8);
+      mbar_init(&bars->p_full[i], 4);   // one arrival per warp of the half's warpgroup
+      mbar_init(&bars->ds_full[i], 4);
     }
     mbar_init(&bars->acc_done, 1);
     mbar_fence_init();
@@ -494,7 +524,9 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t tmem = bars->tmem_base;
   AbortCtx ab{&bars->abort_flag, p.err};
 
-  if (warp == 8) {
+  if (warp >= 8) {
+   setmaxnreg_dec<kIssueRegs>();
+   if (warp == 8) {
     if (lane == 0 && n_steps > 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_do);
@@ -557,13 +589,12 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         tc_commit(&bars->dpt_full[hh]);
       };
-      // acc (+)= A_h B_h with A = packed bf16 [128 x 64] in TMEM, B = 64 rows of a q-side tile
-      // read MN-major.  K = 64 -> four K=16 slices; the two compute warpgroups wrote their 16
-      // packed columns at column offsets 0 and 32.
+      // acc (+)= A_h B_h with A = packed bf16 [128 x 64] in TMEM (32 columns at the start of the
+      // half's score buffer), B = 64 rows of a q-side tile read MN-major.  K = 64 -> four K=16 slices.
       auto issue_acc = [&](uint32_t d, uint32_t a_base, uint32_t b0, bool acc) {
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_ts(d, a_base + (k >> 1) * 32 + (k & 1) * 8,
+          umma_ts(d, a_base + k * 8,
                   make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024), idesc_acc,
                   (acc || k > 0) ? 1u : 0u);
       };
@@ -573,7 +604,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       bool ok = mbar_wait(&bars->stat_full[0], 0, ab, 0x2200u) && mbar_wait(&bars->stat_full[1], 0, ab, 0x2201u);
       ok = ok && ring_wait(0, 0x2210u) && ring_wait(1, 0x2211u);
       if (ok) {
-        tc_fence_after();
+        mma_issue_fence();
         issue_scores(0);
         issue_scores(1);
       }
@@ -584,11 +615,11 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const uint32_t do_slot = ring_addr + ((2 * n + 1) % kBwdStages) * kTileBytes + hh * 8192;
         ok = mbar_wait(&bars->p_full[hh], ph, ab, 0x2220u + hh);
         if (!ok) break;
-        tc_fence_after();
+        mma_issue_fence();
         issue_acc(t_dv, tmem + hh * 64, do_slot, h > 0);          // dV += P^T dO
         ok = mbar_wait(&bars->ds_full[hh], ph, ab, 0x2230u + hh);
         if (!ok) break;
-        tc_fence_after();
+        mma_issue_fence();
         issue_acc(t_dk, tmem + kTile + hh * 64, q_slot, h > 0);   // dK += dS^T Q
         if (hh == 1) {
           tc_commit(&bars->ring_empty[(2 * n) % kBwdStages]);
@@ -598,15 +629,19 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (hh == 0) {  // half h+2 opens step n+1: its tiles must have landed
             ok = ring_wait(2 * (n + 1), 0x2240u) && ring_wait(2 * (n + 1) + 1, 0x2241u);
             if (!ok) break;
-            tc_fence_after();
+            mma_issue_fence();
           }
           issue_scores(h + 2);
         }
       }
       tc_commit(&bars->acc_done);
     }
+   }
   } else {
-    const int w = warp >> 2;       // 32-column quarter pair: this warpgroup owns columns [32w, 32w+32) of a half
+    setmaxnreg_inc<kComputeRegs>();
+    // Warpgroup w owns half w of every q tile (64 q columns): the two warpgroups run half a
+    // step out of phase, so one computes while the other waits on TMEM or a barrier.
+    const int w = warp >> 2;
     const int wq = warp & 3;
     const int r = wq * 32 + lane;  // kv row within the tile
     const int kv_row = kv_tile * kTile + r;
@@ -614,138 +649,129 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int kv_seg = has_seg ? p.kv_seg[(int64_t)batch * p.kv_len + kv_row] : 0;
     const int32_t* q_seg_row = has_seg ? p.q_seg + (int64_t)batch * p.q_len : nullptr;
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
+    const uint32_t t_st = tmem + lane_addr + w * 64;
+    const uint32_t t_dpt = tmem + lane_addr + kTile + w * 64;
     const float c = p.scale_log2;
     bool ok = true;
-    int h = 0;
+    int n = 0;
 
     for (int g = 0; g < group && ok; ++g) {
       int4 ent_next = n_ent > 0 ? p.entries[ebeg] : make_int4(0, 0, 0, 0);
-      for (int e = ebeg; e < eend && ok; ++e) {
+      for (int e = ebeg; e < eend && ok; ++e, ++n) {
         const int4 ent = ent_next;
         if (e + 1 < eend) ent_next = p.entries[e + 1];  // fetched a step ahead of its use
         const int st = ent.y & 3;
-#pragma unroll 1
-        for (int hh = 0; hh < 2; ++hh, ++h) {
-          const int n = h >> 1;
-          const uint32_t ph = (uint32_t)n & 1u;
-          const int q0 = ent.x * kTile + hh * 64 + w * 32;  // first q column of this thread's 32
-          const uint32_t t_st = tmem + lane_addr + hh * 64 + w * 32;
-          const uint32_t t_dpt = tmem + lane_addr + kTile + hh * 64 + w * 32;
-          // Per-column statistics of this step, staged in shared memory by the producer on the
-          // Q slot's barrier; broadcast reads, taken before the score waits.
-          {
-            const uint32_t itq = 2u * (uint32_t)n;
-            ok = mbar_wait(&bars->ring_full[itq % kBwdStages], (itq / kBwdStages) & 1u, ab, 0x2420u);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-          }
-          float nlse[32], dlt[32];
-          {
-            const float* sbase = stats + ((2 * n) % kBwdStages / 2) * 2 * kTile + hh * 64 + w * 32;
-            const float4* l4 = reinterpret_cast<const float4*>(sbase);
-            const float4* d4 = reinterpret_cast<const float4*>(sbase + kTile);
+        const uint32_t ph = (uint32_t)n & 1u;
+        const int q0 = ent.x * kTile + w * 64;  // first q column of this warpgroup's half
+        // Per-column statistics of this step (-lse*log2e, di), staged in shared memory by the
+        // producer on the Q slot's barrier.
+        const uint32_t itq = 2u * (uint32_t)n;
+        ok = mbar_wait(&bars->ring_full[itq % kBwdStages], (itq / kBwdStages) & 1u, ab, 0x2420u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const float4* nl4 = reinterpret_cast<const float4*>(stats + ((itq % kBwdStages) / 2) * 2 * kTile + w * 64);
+        const float4* dl4 = nl4 + kTile / 4;
+
+        ok = mbar_wait(&bars->st_full[w], ph, ab, 0x2400u + w);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        float pr[64];
+        {
+          uint32_t v0[32], v1[32];
+          tmem_ld32(t_st, v0);
+          tmem_ld32(t_st + 32, v1);
+          tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-              const float4 lv = l4[j];
-              const float4 dv = d4[j];
-              nlse[4 * j + 0] = lv.x;
-              nlse[4 * j + 1] = lv.y;
-              nlse[4 * j + 2] = lv.z;
-              nlse[4 * j + 3] = lv.w;
-              dlt[4 * j + 0] = dv.x;
-              dlt[4 * j + 1] = dv.y;
-              dlt[4 * j + 2] = dv.z;
-              dlt[4 * j + 3] = dv.w;
-            }
+          for (int j = 0; j < 32; ++j) {
+            pr[j] = __uint_as_float(v0[j]);
+            pr[32 + j] = __uint_as_float(v1[j]);
           }
-          ok = mbar_wait(&bars->st_full[hh], ph, ab, 0x2400u + hh);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          float pr[32];
-          {
-            uint32_t v[32];
-            tmem_ld32(t_st, v);
-            tmem_ld_wait();
+        }
+        if (st == 1) {
+          if (p.fn.kind != SPLASH_MASK_TABLE) {
+            if (p.q_sequence == nullptr) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) pr[j] = __uint_as_float(v[j]);
-          }
-          if (st == 1) {
-            if (p.fn.kind != SPLASH_MASK_TABLE) {
-              if (p.q_sequence == nullptr) {
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                  const RowInterval iv = mask_fn_interval(p.fn, q0 + j);
-                  if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
-                }
-              } else {
-#pragma unroll 4
-                for (int j = 0; j < 32; ++j) {
-                  const RowInterval iv = mask_fn_interval(p.fn, __ldg(p.q_sequence + q0 + j));
-                  if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
-                }
+              for (int j = 0; j < 64; ++j) {
+                const RowInterval iv = mask_fn_interval(p.fn, q0 + j);
+                if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
               }
             } else {
-              // dkv partial blocks are stored transposed: [id, kv, q]
-              const int8_t* mrow = p.pmb + ((int64_t)ent.z * p.pm_bkv + (kv_row % p.pm_bkv)) * p.pm_bq +
-                                   (q0 % p.pm_bq);
-              const int4* m4 = reinterpret_cast<const int4*>(mrow);
 #pragma unroll
-              for (int t = 0; t < 2; ++t) {
-                const int4 mv = __ldg(m4 + t);
-                const uint32_t wd[4] = {(uint32_t)mv.x, (uint32_t)mv.y, (uint32_t)mv.z, (uint32_t)mv.w};
-#pragma unroll
-                for (int j = 0; j < 16; ++j)
-                  if (((wd[j >> 2] >> ((j & 3) * 8)) & 0xffu) == 0u) pr[t * 16 + j] = kMaskedLogit;
+              for (int j = 0; j < 64; ++j) {
+                const RowInterval iv = mask_fn_interval(p.fn, __ldg(p.q_sequence + q0 + j));
+                if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
               }
             }
-          }
-          if (has_seg) {
-            const int4* sg4 = reinterpret_cast<const int4*>(q_seg_row + q0);
+          } else {
+            // dkv partial blocks are stored transposed: [id, kv, q]
+            const int8_t* mrow = p.pmb + ((int64_t)ent.z * p.pm_bkv + (kv_row % p.pm_bkv)) * p.pm_bq +
+                                 (q0 % p.pm_bq);
+            const int4* m4 = reinterpret_cast<const int4*>(mrow);
 #pragma unroll
-            for (int t = 0; t < 8; ++t) {
-              const int4 sv = __ldg(sg4 + t);
-              if (sv.x != kv_seg) pr[t * 4 + 0] = kMaskedLogit;
-              if (sv.y != kv_seg) pr[t * 4 + 1] = kMaskedLogit;
-              if (sv.z != kv_seg) pr[t * 4 + 2] = kMaskedLogit;
-              if (sv.w != kv_seg) pr[t * 4 + 3] = kMaskedLogit;
+            for (int t = 0; t < 4; ++t) {
+              const int4 mv = __ldg(m4 + t);
+              const uint32_t wd[4] = {(uint32_t)mv.x, (uint32_t)mv.y, (uint32_t)mv.z, (uint32_t)mv.w};
+#pragma unroll
+              for (int j = 0; j < 16; ++j)
+                if (((wd[j >> 2] >> ((j & 3) * 8)) & 0xffu) == 0u) pr[t * 16 + j] = kMaskedLogit;
             }
           }
-          {
-            uint32_t pk[16];
+        }
+        if (has_seg) {
+          const int4* sg4 = reinterpret_cast<const int4*>(q_seg_row + q0);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              pr[2 * j] = ex2(fmaf(pr[2 * j], c, nlse[2 * j]));
-              pr[2 * j + 1] = ex2(fmaf(pr[2 * j + 1], c, nlse[2 * j + 1]));
-              pk[j] = pack_bf16(pr[2 * j], pr[2 * j + 1]);
-            }
-            tmem_st16(t_st, pk);
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->p_full[hh]);
+          for (int t = 0; t < 16; ++t) {
+            const int4 sv = __ldg(sg4 + t);
+            if (sv.x != kv_seg) pr[t * 4 + 0] = kMaskedLogit;
+            if (sv.y != kv_seg) pr[t * 4 + 1] = kMaskedLogit;
+            if (sv.z != kv_seg) pr[t * 4 + 2] = kMaskedLogit;
+            if (sv.w != kv_seg) pr[t * 4 + 3] = kMaskedLogit;
           }
-          ok = mbar_wait(&bars->dpt_full[hh], ph, ab, 0x2410u + hh);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-          {
-            uint32_t pk[16];
+        }
+        {
+          uint32_t pk[32];
+#pragma unroll
+          for (int t = 0; t < 16; ++t) {
+            const float4 nl = nl4[t];
+            pr[4 * t + 0] = ex2(fmaf(pr[4 * t + 0], c, nl.x));
+            pr[4 * t + 1] = ex2(fmaf(pr[4 * t + 1], c, nl.y));
+            pr[4 * t + 2] = ex2(fmaf(pr[4 * t + 2], c, nl.z));
+            pr[4 * t + 3] = ex2(fmaf(pr[4 * t + 3], c, nl.w));
+            pk[2 * t] = pack_bf16(pr[4 * t + 0], pr[4 * t + 1]);
+            pk[2 * t + 1] = pack_bf16(pr[4 * t + 2], pr[4 * t + 3]);
+          }
+          tmem_st32(t_st, pk);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->p_full[w]);
+        }
+        ok = mbar_wait(&bars->dpt_full[w], ph, ab, 0x2410u + w);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        {
+          uint32_t pk[32];
+#pragma unroll
+          for (int hf = 0; hf < 2; ++hf) {  // 32 columns at a time keeps the register count down
             uint32_t v[32];
-            tmem_ld32(t_dpt, v);
+            tmem_ld32(t_dpt + hf * 32, v);
             tmem_ld_wait();
 #pragma unroll
-            for (int j = 0; j < 16; ++j) {
-              const float a0 = pr[2 * j] * (__uint_as_float(v[2 * j]) - dlt[2 * j]);
-              const float a1 = pr[2 * j + 1] * (__uint_as_float(v[2 * j + 1]) - dlt[2 * j + 1]);
-              pk[j] = pack_bf16(a0, a1);
+            for (int t = 0; t < 8; ++t) {
+              const float4 da = dl4[hf * 8 + t];
+              pk[hf * 16 + 2 * t] = pack_bf16(pr[hf * 32 + 4 * t + 0] * (__uint_as_float(v[4 * t + 0]) - da.x),
+                                              pr[hf * 32 + 4 * t + 1] * (__uint_as_float(v[4 * t + 1]) - da.y));
+              pk[hf * 16 + 2 * t + 1] = pack_bf16(pr[hf * 32 + 4 * t + 2] * (__uint_as_float(v[4 * t + 2]) - da.z),
+                                                  pr[hf * 32 + 4 * t + 3] * (__uint_as_float(v[4 * t + 3]) - da.w));
             }
-            tmem_st16(t_dpt, pk);
-            tmem_st_wait();
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->ds_full[hh]);
           }
+          tmem_st32(t_dpt, pk);
+          tmem_st_wait();
+          tc_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&bars->ds_full[w]);
         }
       }
     }

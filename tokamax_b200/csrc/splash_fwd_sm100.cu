@@ -188,7 +188,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int4 e0 = p.entries[ebeg];
         ok = mbar_wait(&bars->kv_full[0], 0, ab, 0x300u);
         if (ok) {
-          tc_fence_after();
+          mma_issue_fence();
           for (int i = 0; i < 2; ++i)
             if ((e0.y >> (2 * i)) & 3) issue_qk(i, 0);
           tc_commit(&bars->kv_empty[0]);
@@ -204,13 +204,13 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (ok && has_next)
             ok = mbar_wait(&bars->kv_full[kslot], (itk / kFwdStages) & 1u, ab, 0x320u + kslot);
           if (!ok) break;
-          tc_fence_after();
+          mma_issue_fence();
           for (int i = 0; i < 2 && ok; ++i) {
             if ((cur.y >> (2 * i)) & 3) {
               ok = mbar_wait(&bars->p_full[i], pcnt[i] & 1u, ab, 0x330u + i);
               if (!ok) break;
               ++pcnt[i];
-              tc_fence_after();
+              mma_issue_fence();
               issue_pv(i, vslot, started[i]);
               started[i] = true;
             }

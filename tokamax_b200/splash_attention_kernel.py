@@ -232,7 +232,7 @@ class _SplashFunction(torch.autograd.Function):
     tables = kernel._tables(q.device)  # pylint: disable=protected-access
     q, k, v = _usable(q), _usable(k), _usable(v)
     b, hq, sq, d = q.shape
-    o = torch.empty((b, hq, sq, d), dtype=q.dtype, device=q.device)
+    o = torch.empty_like(q)  # keeps q's (dense) stride order, e.g. [B,T,H,D] storage stays [B,T,H,D]
     lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
     max_logits = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
     args = _native.SplashFwdArgs()
