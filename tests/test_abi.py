@@ -42,7 +42,7 @@ def test_null_and_invalid_arguments_return_status_codes():
   assert lib.splash_bwd(None, None) == -1
   assert lib.splash_read_error(None, None, None) == -1
   assert lib.splash_bwd_workspace_bytes(0, 1, 1) == 0
-  assert lib.splash_bwd_workspace_bytes(2, 8, 1024) == 2 * 8 * 1024 * 4
+  assert lib.splash_bwd_workspace_bytes(2, 8, 1024) == 2 * (2 * 8 * 1024 * 4)  # di and -lse*log2e
   assert lib.splash_bwd_workspace_bytes(1, 1, 33) % 256 == 0
   out = _native.SplashScheduleOut()
   state = np.ones((2, 2), np.int32)
