@@ -217,6 +217,31 @@ typedef struct SplashBwdArgs {
 size_t splash_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
 int splash_bwd(const SplashBwdArgs* args, void* cuda_stream);
 
+/* Backward pass for callers that cannot obtain device memory at the point of the call.
+ * (No counterpart in the reference; it exists only on this side of the boundary.)
+ *
+ * splash_bwd needs a scratch buffer for the per-row terms di and -logsumexp*log2(e).  Some
+ * callers have no way to provide one when the backward runs: a plugin or custom-call handler that
+ * is only handed its operand and result buffers by the runtime that invokes it; code that runs
+ * after the process has handed all remaining device memory to another allocator; or a caller whose
+ * allocator is not safe to enter from the thread or callback the backward is issued from.  This
+ * variant takes the same SplashBwdArgs, ignores `workspace` / `workspace_bytes`, and keeps the
+ * scratch in an array that is part of the loaded library image on every GPU: it performs no
+ * cudaMalloc / cudaFree and calls nothing that allocates.
+ *
+ * Limit: batch * q_heads * q_len <= SPLASH_STATIC_SCRATCH_MAX_ROWS (the array is
+ * 2 * 4 * SPLASH_STATIC_SCRATCH_MAX_ROWS bytes = 8 MiB, held by each GPU that loads the library
+ * until the process exits).  Larger problems return SPLASH_ERR_TOO_LARGE and launch nothing.
+ *
+ * The first call on a device looks up the array's device address (once per device, with that
+ * device current); make that first call outside any stream capture.  The array is shared by
+ * every call on the device and keeps the previous call's contents; nothing in it has to start at
+ * zero, because the di pass overwrites every row a call later reads.  Two calls whose kernels
+ * can overlap on the same GPU (different streams without an ordering between them) race on the
+ * array — order them, or use splash_bwd with separate workspaces. */
+#define SPLASH_STATIC_SCRATCH_MAX_ROWS (1 << 20)
+int splash_bwd_static_scratch(const SplashBwdArgs* args, void* cuda_stream);
+
 /* Copies the 4-word device error record to host (synchronises the stream) and maps it to a
  * status: SPLASH_OK or SPLASH_ERR_KERNEL_TIMEOUT.  record_out may be NULL. */
 int splash_read_error(const uint32_t* error_record, void* cuda_stream, uint32_t record_out[4]);

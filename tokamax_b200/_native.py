@@ -157,6 +157,7 @@ _PROTOTYPES = {
     "splash_fwd": (C.c_int, [C.POINTER(SplashFwdArgs), C.c_void_p]),
     "splash_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "splash_bwd": (C.c_int, [C.POINTER(SplashBwdArgs), C.c_void_p]),
+    "splash_bwd_static_scratch": (C.c_int, [C.POINTER(SplashBwdArgs), C.c_void_p]),
     "splash_read_error": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32 * 4)]),
     "splash_status_str": (C.c_char_p, [C.c_int]),
     "splash_version": (C.c_char_p, []),

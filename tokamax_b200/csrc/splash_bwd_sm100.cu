@@ -16,6 +16,8 @@
 // (tokamax/_src/ops/experimental/tpu/splash_attention/splash_attention_kernel.py:1234-1459 and
 // base.py:115-173): P = exp(S - logsumexp), dS = (dP - di) * P, with the softmax scale applied
 // in fp32 inside the kernels.
+#include <mutex>
+
 #include "splash_common.cuh"
 
 namespace sb {
@@ -949,6 +951,40 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   if (mask & 4u) splash_dkv_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hkv, (unsigned)B), kBwdThreads, kDkvSmemBytes,
                       stream>>>(tm_q, tm_do, tm_k, tm_v, p);
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
+}
+
+// ------------------------------------------------------------------------------------------
+// backward with the scratch held in the library image (no allocation anywhere on the path)
+// ------------------------------------------------------------------------------------------
+// di rows followed by -logsumexp*log2(e) rows, SPLASH_STATIC_SCRATCH_MAX_ROWS each.
+static __device__ __align__(256) float g_static_scratch[2 * SPLASH_STATIC_SCRATCH_MAX_ROWS];
+
+int launch_bwd_static_scratch(const SplashBwdArgs& a, cudaStream_t stream) {
+  const int64_t B = a.q.size[0], Hq = a.q.size[1], Sq = a.q.size[2];
+  if (B <= 0 || Hq <= 0 || Sq <= 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  if (B * Hq * Sq > (int64_t)SPLASH_STATIC_SCRATCH_MAX_ROWS) return SPLASH_ERR_TOO_LARGE;
+
+  // Inside host code the array's name is only a handle for the runtime, not a device address;
+  // the address is looked up once per device, with that device current.
+  constexpr int kMaxDevices = 64;
+  static float* device_ptr[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = -1;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return SPLASH_ERR_CUDA;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (device_ptr[dev] == nullptr) {
+      void* sym = nullptr;
+      if (cudaGetSymbolAddress(&sym, g_static_scratch) != cudaSuccess || sym == nullptr) return SPLASH_ERR_CUDA;
+      device_ptr[dev] = static_cast<float*>(sym);
+    }
+    scratch = device_ptr[dev];
+  }
+  SplashBwdArgs b = a;
+  b.workspace = scratch;
+  b.workspace_bytes = bwd_workspace_bytes(B, Hq, Sq);  // <= sizeof(g_static_scratch) by the row check
+  return launch_bwd(b, stream);
 }
 
 }  // namespace sb

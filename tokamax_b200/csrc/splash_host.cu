@@ -9,6 +9,7 @@ namespace sb {
 
 int launch_fwd(const SplashFwdArgs& a, cudaStream_t stream);
 int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream);
+int launch_bwd_static_scratch(const SplashBwdArgs& a, cudaStream_t stream);
 size_t bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -83,6 +84,11 @@ int splash_bwd(const SplashBwdArgs* args, void* cuda_stream) {
   return sb::launch_bwd(*args, static_cast<cudaStream_t>(cuda_stream));
 }
 
+int splash_bwd_static_scratch(const SplashBwdArgs* args, void* cuda_stream) {
+  if (args == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;
+  return sb::launch_bwd_static_scratch(*args, static_cast<cudaStream_t>(cuda_stream));
+}
+
 int splash_read_error(const uint32_t* error_record, void* cuda_stream, uint32_t record_out[4]) {
   if (error_record == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;
   uint32_t host[4] = {0, 0, 0, 0};
@@ -103,7 +109,9 @@ const char* splash_status_str(int status) {
     case SPLASH_ERR_NO_DEVICE: return "no usable sm_100 device or driver entry point";
     case SPLASH_ERR_KERNEL_TIMEOUT: return "device-side bounded wait ran out";
     case SPLASH_ERR_OUT_OF_MEMORY: return "host allocation failed";
-    case SPLASH_ERR_TOO_LARGE: return "size beyond a built-in limit";
+    case SPLASH_ERR_TOO_LARGE:
+      return "size beyond a built-in limit (grid dimension, or SPLASH_STATIC_SCRATCH_MAX_ROWS for the "
+             "static-scratch backward)";
     default: return "unknown status";
   }
 }
