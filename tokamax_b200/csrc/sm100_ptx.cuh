@@ -2,7 +2,7 @@
 // TMEM accumulators, TMEM load/store, and the shared-memory / instruction descriptors the
 // MMA consumes.  Everything here is single-CTA (cta_group::1) and uses plain TMA loads only.
 //
-// Every wait on an mbarrier is bounded: after kSpinLimit polls the waiter raises a
+// Every wait on an mbarrier is bounded: after kWaitLimitCycles the waiter raises a
 // CTA-wide abort flag plus a global error word and falls through, so a protocol bug ends
 // the kernel with a status code instead of hanging the GPU.
 #pragma once
@@ -25,7 +25,7 @@ struct AbortCtx {
   uint32_t* global_err;          // device error record (may not be null)
 };
 
-constexpr uint32_t kSpinLimit = 1u << 24;  // polls; each failed poll sleeps up to ~64 ns+
+constexpr long long kWaitLimitCycles = 1500000000ll;  // ~0.8 s at 1.9 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -71,16 +71,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait.  Returns false if the wait was abandoned (this thread timed out, or some
-// other thread of the CTA already did).
+// Bounded wait: gives up after kWaitLimitCycles (under a second), or as soon as another thread
+// of the CTA has given up.  Returns false if the wait was abandoned.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab,
                                           uint32_t tag) {
   if (mbar_try_wait(bar, parity)) return true;
-  for (uint32_t spin = 0; spin < kSpinLimit; ++spin) {
+  const long long start = clock64();
+  for (uint32_t spin = 0;; ++spin) {
     if (mbar_try_wait(bar, parity)) return true;
-    if ((spin & 63u) == 63u) {
+    if ((spin & 15u) == 15u) {
       if (*ab.cta_flag) return false;
-      __nanosleep(64);
+      if (clock64() - start > kWaitLimitCycles) break;
     }
   }
   *ab.cta_flag = 1u;

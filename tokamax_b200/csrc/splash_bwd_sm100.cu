@@ -23,6 +23,7 @@
 namespace sb {
 
 constexpr int kBwdStages = 4;
+constexpr int kDqStages = 5;  // K/V ring of the dq kernel: 2.5 steps of look-ahead
 constexpr int kBwdThreads = 384;  // 8 compute warps + TMA warp + MMA warp + 2 idle warps that
                                   // complete the third warpgroup for the register hand-over
 constexpr int kComputeRegs = 224;
@@ -97,8 +98,8 @@ struct BwdParams {
 
 struct BwdBarriers {
   uint64_t stat_full[2];              // stationary operand tiles
-  uint64_t ring_full[kBwdStages];
-  uint64_t ring_empty[kBwdStages];
+  uint64_t ring_full[kDqStages];
+  uint64_t ring_empty[kDqStages];
   uint64_t s_full[2];
   uint64_t dp_full;
   uint64_t p_full;                    // dkv: P^T ready; dq: unused
@@ -109,7 +110,7 @@ struct BwdBarriers {
   uint32_t early_exit;
 };
 
-constexpr int kBwdSmemBytes = (2 + kBwdStages) * kTileBytes + 1024 + 1024;
+constexpr int kDqSmemBytes = (2 + kDqStages) * kTileBytes + 1024 + 1024;
 
 // Column offset (32-bit TMEM columns) at which compute warpgroup w stores its 32 packed bf16
 // columns: inside the 64 fp32 columns it has itself read, so the two warpgroups never race.
@@ -147,7 +148,7 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   uint8_t* q_smem = smem;
   uint8_t* do_smem = smem + kTileBytes;
   uint8_t* ring = smem + 2 * kTileBytes;
-  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(smem + (2 + kBwdStages) * kTileBytes);
+  BwdBarriers* bars = reinterpret_cast<BwdBarriers*>(smem + (2 + kDqStages) * kTileBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -164,7 +165,7 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     bars->abort_flag = 0;
     mbar_init(&bars->stat_full[0], 1);
     mbar_init(&bars->stat_full[1], 1);
-    for (int s = 0; s < kBwdStages; ++s) {
+    for (int s = 0; s < kDqStages; ++s) {
       mbar_init(&bars->ring_full[s], 1);
       mbar_init(&bars->ring_empty[s], 1);
     }
@@ -207,8 +208,8 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       for (int e = ebeg; e < eend && ok; ++e) {
         const int col = p.entries[e].x;
         for (int kv = 0; kv < 2 && ok; ++kv, ++it) {
-          const uint32_t s = it % kBwdStages;
-          ok = mbar_wait(&bars->ring_empty[s], ((it / kBwdStages) & 1u) ^ 1u, ab, 0x1100u + s);
+          const uint32_t s = it % kDqStages;
+          ok = mbar_wait(&bars->ring_empty[s], ((it / kDqStages) & 1u) ^ 1u, ab, 0x1100u + s);
           if (!ok) break;
           uint8_t* dst = ring + s * kTileBytes;
           const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
@@ -233,7 +234,7 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       };
       auto ring_wait = [&](uint32_t it, uint32_t tag) {
-        return mbar_wait(&bars->ring_full[it % kBwdStages], (it / kBwdStages) & 1u, ab, tag);
+        return mbar_wait(&bars->ring_full[it % kDqStages], (it / kDqStages) & 1u, ab, tag);
       };
       bool ok = mbar_wait(&bars->stat_full[0], 0, ab, 0x1200u) && mbar_wait(&bars->stat_full[1], 0, ab, 0x1201u);
       // prologue: S_0, dP_0
@@ -257,7 +258,7 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ok = ring_wait(it_kn, 0x1220u);
           if (!ok) break;
           mma_issue_fence();
-          ss_kmajor(tmem + ((n + 1) & 1) * kTile, q_addr, ring_addr + (it_kn % kBwdStages) * kTileBytes);
+          ss_kmajor(tmem + ((n + 1) & 1) * kTile, q_addr, ring_addr + (it_kn % kDqStages) * kTileBytes);
           tc_commit(&bars->s_full[(n + 1) & 1]);
         }
         ok = mbar_wait(&bars->ds_full, n & 1u, ab, 0x1230u);
@@ -269,39 +270,39 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ok = ring_wait(it_vn, 0x1240u);
           if (!ok) break;
           mma_issue_fence();
-          ss_kmajor(t_dp, do_addr, ring_addr + (it_vn % kBwdStages) * kTileBytes);
+          ss_kmajor(t_dp, do_addr, ring_addr + (it_vn % kDqStages) * kTileBytes);
           tc_commit(&bars->dp_full);
-          tc_commit(&bars->ring_empty[it_vn % kBwdStages]);
+          tc_commit(&bars->ring_empty[it_vn % kDqStages]);
         }
         {
           // dQ += dS_n K_n : A = packed dS in the S buffer, B = K tile read MN-major.
           const uint32_t a_base = tmem + (n & 1) * kTile;
-          const uint32_t b0 = ring_addr + (it_k % kBwdStages) * kTileBytes;
+          const uint32_t b0 = ring_addr + (it_k % kDqStages) * kTileBytes;
 #pragma unroll
           for (int k = 0; k < 8; ++k)
             umma_ts(t_dq, a_base + packed_a_col(k), make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024),
                     idesc_mn, (n > 0 || k > 0) ? 1u : 0u);
-          tc_commit(&bars->ring_empty[it_k % kBwdStages]);
+          tc_commit(&bars->ring_empty[it_k % kDqStages]);
         }
 #else
         {
           // dQ += dS_n K_n : A = packed dS in the S buffer, B = K tile read MN-major.
           const uint32_t a_base = tmem + (n & 1) * kTile;
-          const uint32_t b0 = ring_addr + (it_k % kBwdStages) * kTileBytes;
+          const uint32_t b0 = ring_addr + (it_k % kDqStages) * kTileBytes;
 #pragma unroll
           for (int k = 0; k < 8; ++k)
             umma_ts(t_dq, a_base + packed_a_col(k), make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024),
                     idesc_mn, (n > 0 || k > 0) ? 1u : 0u);
-          tc_commit(&bars->ring_empty[it_k % kBwdStages]);
+          tc_commit(&bars->ring_empty[it_k % kDqStages]);
         }
         // dP of the next step goes first: the compute warps wait on it, while nothing waits on dQ.
         if (has_next) {
           ok = ring_wait(it_vn, 0x1240u);
           if (!ok) break;
           mma_issue_fence();
-          ss_kmajor(t_dp, do_addr, ring_addr + (it_vn % kBwdStages) * kTileBytes);
+          ss_kmajor(t_dp, do_addr, ring_addr + (it_vn % kDqStages) * kTileBytes);
           tc_commit(&bars->dp_full);
-          tc_commit(&bars->ring_empty[it_vn % kBwdStages]);
+          tc_commit(&bars->ring_empty[it_vn % kDqStages]);
         }
 #endif
       }
@@ -456,6 +457,17 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 constexpr int kDkvStatsBytes = (kBwdStages / 2) * 2 * kTile * 4;
 constexpr int kDkvSmemBytes = (2 + kBwdStages) * kTileBytes + kDkvStatsBytes + 1024 + 1024;
 
+// 16 compute warps (two groups of 8, one per q-tile half, each thread 32 score columns) keep the
+// P^T / dS^T phases short; warp 16 feeds TMA, warp 17 issues MMAs, warps 18-19 only complete the
+// fifth warpgroup so registers can be handed to the compute warpgroups.
+constexpr int kDkvThreads = 640;
+constexpr int kDkvTmaWarp = 16;
+constexpr int kDkvMmaWarp = 17;
+// setmaxnreg.inc can only take what setmaxnreg.dec of the same CTA released: at 96 registers per
+// thread at launch, 512 * (104 - 96) = 4096 <= 128 * (96 - 56) = 5120.
+constexpr int kDkvComputeRegs = 104;
+constexpr int kDkvIssueRegs = 56;
+
 struct DkvBarriers {
   uint64_t stat_full[2];
   uint64_t ring_full[kBwdStages];
@@ -470,7 +482,7 @@ struct DkvBarriers {
   uint32_t early_exit;
 };
 
-__global__ void __launch_bounds__(kBwdThreads, 1)
+__global__ void __launch_bounds__(kDkvThreads, 1)
 splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                   const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                   const BwdParams p) {
@@ -508,15 +520,15 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->st_full[i], 1);
       mbar_init(&bars->dpt_full[i], 1);
-      mbar_init(&bars->p_full[i], 4);   // one arrival per warp of the half's warpgroup
-      mbar_init(&bars->ds_full[i], 4);
+      mbar_init(&bars->p_full[i], 8);   // one arrival per warp of the half's group
+      mbar_init(&bars->ds_full[i], 8);
     }
     mbar_init(&bars->acc_done, 1);
     mbar_fence_init();
   }
   __syncthreads();
   if (bars->early_exit != 0) return;
-  if (warp == 9) {
+  if (warp == kDkvMmaWarp) {
     tmem_alloc(&bars->tmem_base, 512);
     tmem_relinquish();
   }
@@ -526,9 +538,9 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t tmem = bars->tmem_base;
   AbortCtx ab{&bars->abort_flag, p.err};
 
-  if (warp >= 8) {
-   setmaxnreg_dec<kIssueRegs>();
-   if (warp == 8) {
+  if (warp >= 16) {
+   setmaxnreg_dec<kDkvIssueRegs>();
+   if (warp == kDkvTmaWarp) {
     if (lane == 0 && n_steps > 0) {
       tma_prefetch_desc(&tm_q);
       tma_prefetch_desc(&tm_do);
@@ -565,7 +577,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
     }
-  } else if (warp == 9) {
+  } else if (warp == kDkvMmaWarp) {
     if (lane == 0 && n_steps > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kTile, 64, false, false);
       constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, kHeadDim, false, true);
@@ -591,12 +603,13 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         tc_commit(&bars->dpt_full[hh]);
       };
-      // acc (+)= A_h B_h with A = packed bf16 [128 x 64] in TMEM (32 columns at the start of the
-      // half's score buffer), B = 64 rows of a q-side tile read MN-major.  K = 64 -> four K=16 slices.
+      // acc (+)= A_h B_h with A = packed bf16 [128 x 64] in TMEM, B = 64 rows of a q-side tile read
+      // MN-major.  K = 64 -> four K=16 slices; each 32-column quarter of the score buffer holds the
+      // 16 packed columns written by the warps that own it.
       auto issue_acc = [&](uint32_t d, uint32_t a_base, uint32_t b0, bool acc) {
 #pragma unroll
         for (int k = 0; k < 4; ++k)
-          umma_ts(d, a_base + k * 8,
+          umma_ts(d, a_base + (k >> 1) * 32 + (k & 1) * 8,
                   make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024), idesc_acc,
                   (acc || k > 0) ? 1u : 0u);
       };
@@ -640,10 +653,11 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
    }
   } else {
-    setmaxnreg_inc<kComputeRegs>();
-    // Warpgroup w owns half w of every q tile (64 q columns): the two warpgroups run half a
-    // step out of phase, so one computes while the other waits on TMEM or a barrier.
-    const int w = warp >> 2;
+    setmaxnreg_inc<kDkvComputeRegs>();
+    // Group w (8 warps) owns half w of every q tile; inside it warp column c owns 32 of the 64
+    // score columns.  The two groups run half a step out of phase.
+    const int w = warp >> 3;
+    const int cq = (warp >> 2) & 1;
     const int wq = warp & 3;
     const int r = wq * 32 + lane;  // kv row within the tile
     const int kv_row = kv_tile * kTile + r;
@@ -651,8 +665,8 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const int kv_seg = has_seg ? p.kv_seg[(int64_t)batch * p.kv_len + kv_row] : 0;
     const int32_t* q_seg_row = has_seg ? p.q_seg + (int64_t)batch * p.q_len : nullptr;
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    const uint32_t t_st = tmem + lane_addr + w * 64;
-    const uint32_t t_dpt = tmem + lane_addr + kTile + w * 64;
+    const uint32_t t_st = tmem + lane_addr + w * 64 + cq * 32;
+    const uint32_t t_dpt = tmem + lane_addr + kTile + w * 64 + cq * 32;
     const float c = p.scale_log2;
     bool ok = true;
     int n = 0;
@@ -664,43 +678,40 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (e + 1 < eend) ent_next = p.entries[e + 1];  // fetched a step ahead of its use
         const int st = ent.y & 3;
         const uint32_t ph = (uint32_t)n & 1u;
-        const int q0 = ent.x * kTile + w * 64;  // first q column of this warpgroup's half
+        const int q0 = ent.x * kTile + w * 64 + cq * 32;  // first q column of this thread's 32
         // Per-column statistics of this step (-lse*log2e, di), staged in shared memory by the
         // producer on the Q slot's barrier.
         const uint32_t itq = 2u * (uint32_t)n;
         ok = mbar_wait(&bars->ring_full[itq % kBwdStages], (itq / kBwdStages) & 1u, ab, 0x2420u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const float4* nl4 = reinterpret_cast<const float4*>(stats + ((itq % kBwdStages) / 2) * 2 * kTile + w * 64);
+        const float4* nl4 =
+            reinterpret_cast<const float4*>(stats + ((itq % kBwdStages) / 2) * 2 * kTile + w * 64 + cq * 32);
         const float4* dl4 = nl4 + kTile / 4;
 
         ok = mbar_wait(&bars->st_full[w], ph, ab, 0x2400u + w);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        float pr[64];
+        float pr[32];
         {
-          uint32_t v0[32], v1[32];
-          tmem_ld32(t_st, v0);
-          tmem_ld32(t_st + 32, v1);
+          uint32_t v[32];
+          tmem_ld32(t_st, v);
           tmem_ld_wait();
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            pr[j] = __uint_as_float(v0[j]);
-            pr[32 + j] = __uint_as_float(v1[j]);
-          }
+          for (int j = 0; j < 32; ++j) pr[j] = __uint_as_float(v[j]);
         }
         if (st == 1) {
           if (p.fn.kind != SPLASH_MASK_TABLE) {
             if (p.q_sequence == nullptr) {
 #pragma unroll
-              for (int j = 0; j < 64; ++j) {
+              for (int j = 0; j < 32; ++j) {
                 const RowInterval iv = mask_fn_interval(p.fn, q0 + j);
                 if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
               }
             } else {
 #pragma unroll
-              for (int j = 0; j < 64; ++j) {
+              for (int j = 0; j < 32; ++j) {
                 const RowInterval iv = mask_fn_interval(p.fn, __ldg(p.q_sequence + q0 + j));
                 if (kv_row < iv.lo || kv_row > iv.hi) pr[j] = kMaskedLogit;
               }
@@ -711,7 +722,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                                  (q0 % p.pm_bq);
             const int4* m4 = reinterpret_cast<const int4*>(mrow);
 #pragma unroll
-            for (int t = 0; t < 4; ++t) {
+            for (int t = 0; t < 2; ++t) {
               const int4 mv = __ldg(m4 + t);
               const uint32_t wd[4] = {(uint32_t)mv.x, (uint32_t)mv.y, (uint32_t)mv.z, (uint32_t)mv.w};
 #pragma unroll
@@ -723,7 +734,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (has_seg) {
           const int4* sg4 = reinterpret_cast<const int4*>(q_seg_row + q0);
 #pragma unroll
-          for (int t = 0; t < 16; ++t) {
+          for (int t = 0; t < 8; ++t) {
             const int4 sv = __ldg(sg4 + t);
             if (sv.x != kv_seg) pr[t * 4 + 0] = kMaskedLogit;
             if (sv.y != kv_seg) pr[t * 4 + 1] = kMaskedLogit;
@@ -732,9 +743,9 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           }
         }
         {
-          uint32_t pk[32];
+          uint32_t pk[16];
 #pragma unroll
-          for (int t = 0; t < 16; ++t) {
+          for (int t = 0; t < 8; ++t) {
             const float4 nl = nl4[t];
             pr[4 * t + 0] = ex2(fmaf(pr[4 * t + 0], c, nl.x));
             pr[4 * t + 1] = ex2(fmaf(pr[4 * t + 1], c, nl.y));
@@ -743,7 +754,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             pk[2 * t] = pack_bf16(pr[4 * t + 0], pr[4 * t + 1]);
             pk[2 * t + 1] = pack_bf16(pr[4 * t + 2], pr[4 * t + 3]);
           }
-          tmem_st32(t_st, pk);
+          tmem_st16(t_st, pk);
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
@@ -754,22 +765,19 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (!ok) break;
         tc_fence_after();
         {
-          uint32_t pk[32];
+          uint32_t pk[16];
+          uint32_t v[32];
+          tmem_ld32(t_dpt, v);
+          tmem_ld_wait();
 #pragma unroll
-          for (int hf = 0; hf < 2; ++hf) {  // 32 columns at a time keeps the register count down
-            uint32_t v[32];
-            tmem_ld32(t_dpt + hf * 32, v);
-            tmem_ld_wait();
-#pragma unroll
-            for (int t = 0; t < 8; ++t) {
-              const float4 da = dl4[hf * 8 + t];
-              pk[hf * 16 + 2 * t] = pack_bf16(pr[hf * 32 + 4 * t + 0] * (__uint_as_float(v[4 * t + 0]) - da.x),
-                                              pr[hf * 32 + 4 * t + 1] * (__uint_as_float(v[4 * t + 1]) - da.y));
-              pk[hf * 16 + 2 * t + 1] = pack_bf16(pr[hf * 32 + 4 * t + 2] * (__uint_as_float(v[4 * t + 2]) - da.z),
-                                                  pr[hf * 32 + 4 * t + 3] * (__uint_as_float(v[4 * t + 3]) - da.w));
-            }
+          for (int t = 0; t < 8; ++t) {
+            const float4 da = dl4[t];
+            pk[2 * t] = pack_bf16(pr[4 * t + 0] * (__uint_as_float(v[4 * t + 0]) - da.x),
+                                  pr[4 * t + 1] * (__uint_as_float(v[4 * t + 1]) - da.y));
+            pk[2 * t + 1] = pack_bf16(pr[4 * t + 2] * (__uint_as_float(v[4 * t + 2]) - da.z),
+                                      pr[4 * t + 3] * (__uint_as_float(v[4 * t + 3]) - da.w));
           }
-          tmem_st32(t_dpt, pk);
+          tmem_st16(t_dpt, pk);
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
@@ -778,11 +786,12 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
     }
 
-    // epilogue: dK (scaled) and dV, 64 columns per warpgroup
+    // epilogue: dK (scaled) and dV, 32 columns per thread
+    const int cb = warp >> 2;  // 0..3
     __nv_bfloat16* dk = p.out0 + (int64_t)batch * p.out0_sb + (int64_t)kv_head * p.out0_sh +
-                        (int64_t)kv_row * p.out0_ss + w * 64;
+                        (int64_t)kv_row * p.out0_ss + cb * 32;
     __nv_bfloat16* dv = p.out1 + (int64_t)batch * p.out1_sb + (int64_t)kv_head * p.out1_sh +
-                        (int64_t)kv_row * p.out1_ss + w * 64;
+                        (int64_t)kv_row * p.out1_ss + cb * 32;
     if (n_steps > 0) {
       if (ok) {
         ok = mbar_wait(&bars->acc_done, 0, ab, 0x2500u);
@@ -790,31 +799,26 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       if (ok) {
         tc_fence_after();
-#pragma unroll
-        for (int t = 0; t < 2; ++t) {
-          uint32_t v[32];
-          tmem_ld32(tmem + lane_addr + 2 * kTile + w * 64 + t * 32, v);
-          tmem_ld_wait();
-          store_row_half(dk + t * 32, v, p.scale);
-          tmem_ld32(tmem + lane_addr + 3 * kTile + w * 64 + t * 32, v);
-          tmem_ld_wait();
-          store_row_half(dv + t * 32, v, 1.0f);
-        }
+        uint32_t v[32];
+        tmem_ld32(tmem + lane_addr + 2 * kTile + cb * 32, v);
+        tmem_ld_wait();
+        store_row_half(dk, v, p.scale);
+        tmem_ld32(tmem + lane_addr + 3 * kTile + cb * 32, v);
+        tmem_ld_wait();
+        store_row_half(dv, v, 1.0f);
       }
     } else {
       uint32_t v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = 0u;
       store_row_half(dk, v, 0.f);
-      store_row_half(dk + 32, v, 0.f);
       store_row_half(dv, v, 0.f);
-      store_row_half(dv + 32, v, 0.f);
     }
   }
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 9) {
+  if (warp == kDkvMmaWarp) {
     __syncwarp();
     tmem_dealloc(tmem, 512);
   }
@@ -894,7 +898,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   static bool attr_set = false;
   if (!attr_set) {
     if (cudaFuncSetAttribute(splash_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kBwdSmemBytes) != cudaSuccess ||
+                             kDqSmemBytes) != cudaSuccess ||
         cudaFuncSetAttribute(splash_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                              kDkvSmemBytes) != cudaSuccess)
       return SPLASH_ERR_CUDA;
@@ -929,7 +933,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.pm_bq = a.sched_dq.block_q > 0 ? a.sched_dq.block_q : kTile;
   p.pm_bkv = a.sched_dq.block_kv > 0 ? a.sched_dq.block_kv : kTile;
   p.n_rows = a.sched_dq.n_rows;
-  if (mask & 2u) splash_dq_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hq, (unsigned)B), kBwdThreads, kBwdSmemBytes,
+  if (mask & 2u) splash_dq_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hq, (unsigned)B), kBwdThreads, kDqSmemBytes,
                      stream>>>(tm_q, tm_do, tm_k, tm_v, p);
   if (cudaGetLastError() != cudaSuccess) return SPLASH_ERR_CUDA;
 
@@ -948,7 +952,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.pm_bq = a.sched_dkv.block_q > 0 ? a.sched_dkv.block_q : kTile;
   p.pm_bkv = a.sched_dkv.block_kv > 0 ? a.sched_dkv.block_kv : kTile;
   p.n_rows = a.sched_dkv.n_rows;
-  if (mask & 4u) splash_dkv_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hkv, (unsigned)B), kBwdThreads, kDkvSmemBytes,
+  if (mask & 4u) splash_dkv_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hkv, (unsigned)B), kDkvThreads, kDkvSmemBytes,
                       stream>>>(tm_q, tm_do, tm_k, tm_v, p);
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
 }
