@@ -1,5 +1,6 @@
 // Host side of the C ABI: argument checks, TMA tensor maps, status strings, error read-back.
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -63,6 +64,10 @@ int make_tile_tensor_map(CUtensorMap* out, const SplashTensor& t, int box_rows) 
   CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.data, dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS && std::getenv("SPLASH_DEBUG") != nullptr)
+    std::fprintf(stderr, "splash_b200: cuTensorMapEncodeTiled failed (%d): sizes %lld %lld %lld %lld strides %lld %lld %lld box rows %d\n",
+                 (int)r, (long long)t.size[0], (long long)t.size[1], (long long)t.size[2], (long long)t.size[3],
+                 (long long)t.stride[0], (long long)t.stride[1], (long long)t.stride[2], box_rows);
   return r == CUDA_SUCCESS ? SPLASH_OK : SPLASH_ERR_CUDA;
 }
 
