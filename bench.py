@@ -228,7 +228,18 @@ def per_kernel_times(kernel, q, k, v, do, seg, iters: int = 5) -> dict:
   fa.logsumexp = lse.data_ptr()
   fa.q_segment_ids = seg[0].data_ptr() if seg else None
   fa.kv_segment_ids = seg[1].data_ptr() if seg else None
-  fa.sched = tables.fwd
+  fwd_sched, dq_sched, dkv_sched, keep = tables.fwd, tables.dq, tables.dkv, []
+  if seg:
+    for kind, name in ((0, 'fwd'), (1, 'dq'), (2, 'dkv')):
+      sc, ws_ = splash._segment_schedule(getattr(tables, name), kind, seg[0], seg[1], s, k.shape[2])  # pylint: disable=protected-access
+      keep.append(ws_)
+      if kind == 0:
+        fwd_sched = sc
+      elif kind == 1:
+        dq_sched = sc
+      else:
+        dkv_sched = sc
+  fa.sched = fwd_sched
   fa.mask_fn = splash._mask_fn_struct(kernel.mask_function_rule)  # pylint: disable=protected-access
   fa.scale = SCALE
   fa.mask_value = -1e30
@@ -240,7 +251,7 @@ def per_kernel_times(kernel, q, k, v, do, seg, iters: int = 5) -> dict:
   ba.dq, ba.dk, ba.dv = map(splash._tensor_desc, (dq, dk, dv))  # pylint: disable=protected-access
   ba.logsumexp = lse.data_ptr()
   ba.q_segment_ids, ba.kv_segment_ids = fa.q_segment_ids, fa.kv_segment_ids
-  ba.sched_dq, ba.sched_dkv = tables.dq, tables.dkv
+  ba.sched_dq, ba.sched_dkv = dq_sched, dkv_sched
   ba.mask_fn = fa.mask_fn
   ba.scale = SCALE
   ba.workspace, ba.workspace_bytes = ws.data_ptr(), ws_bytes

@@ -164,7 +164,32 @@ typedef struct SplashDeviceSchedule {
   const int8_t* partial_mask_blocks; /* device, [n_partial, pm_rows, pm_cols] or NULL */
   int32_t block_q;                   /* block shape the partial blocks were cut with */
   int32_t block_kv;
+  int64_t n_entries;                 /* entries in the list (needed by splash_segment_schedule) */
+  /* Per-batch-row specialisation written by splash_segment_schedule; zero / NULL otherwise. */
+  const int32_t* row_end;            /* device, [batch, n_rows]: end of each row's entries; NULL:
+                                        row r ends at row_ptr[r + 1] */
+  int64_t entries_per_batch;         /* batch row b reads entries + b * entries_per_batch * 4 */
 } SplashDeviceSchedule;
+
+/* ------------------------------------------------------------------------------------------
+ * Segment-aware schedules (device).  With segment ids the reference masks element by element
+ * only (splash_attention_kernel.py:262-278); tiles whose q and kv segment-id ranges do not
+ * overlap contribute nothing, so they can be dropped before the kernels run.  This call filters
+ * a schedule per batch row: it computes the [min, max] segment id of every 128-token tile and
+ * writes, for each batch row, the entries that can still hold an unmasked pair (sub-tile states
+ * are lowered to 0 where they cannot).  Results are unchanged; only skipped work differs.
+ *
+ * `in` is a schedule of `kind` (0 forward, 1 dq, 2 dkv, as in splash_schedule_build) with
+ * n_entries filled in.  `out` receives device pointers into `workspace`
+ * (splash_segment_schedule_bytes bytes, 256-byte aligned) and is then passed to splash_fwd /
+ * splash_bwd in place of `in`.  Enqueued on the stream; no host synchronisation.
+ * ---------------------------------------------------------------------------------------- */
+size_t splash_segment_schedule_bytes(int64_t batch, int64_t q_len, int64_t kv_len, int32_t n_rows,
+                                     int64_t n_entries);
+int splash_segment_schedule(const SplashDeviceSchedule* in, int32_t kind, const int32_t* q_segment_ids,
+                            const int32_t* kv_segment_ids, int64_t batch, int64_t q_len, int64_t kv_len,
+                            void* workspace, size_t workspace_bytes, SplashDeviceSchedule* out,
+                            void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------------
  * Forward.  Replaces `_splash_attention_forward` + `flash_attention_kernel`

@@ -164,6 +164,54 @@ def test_segment_ids_unbatched_vector():
   assert (out.float().cpu() - ro).abs().max().item() <= O_ATOL
 
 
+@pytest.mark.parametrize("kind", [0, 1, 2])
+def test_segment_aware_schedule_matches_brute_force(kind):
+  """splash_segment_schedule keeps exactly the tiles whose segment-id ranges overlap."""
+  dev = torch.device("cuda:0")
+  s, batch = 1536, 3
+  mask = mask_lib.CausalMask((s, s))
+  kernel = splash.make_splash_mha(mask, q_seq_shards=1)
+  tables = kernel._tables(dev)  # pylint: disable=protected-access
+  sched = (tables.fwd, tables.dq, tables.dkv)[kind]
+  seg = _packed_segments(batch, s, 5, 100, 700)
+  seg_dev = seg.to(dev)
+  out, ws = splash._segment_schedule(sched, kind, seg_dev, seg_dev, s, s)  # pylint: disable=protected-access
+  torch.cuda.synchronize()
+  nt = s // 128
+  n_rows, n_ent = sched.n_rows, sched.n_entries
+  row_ptr = next(t for t in tables.keep if t.data_ptr() == sched.row_ptr).cpu().numpy()
+  entries = next(t for t in tables.keep if t.data_ptr() == sched.entries).cpu().numpy().reshape(-1, 4)
+  import ctypes as C
+  nbytes = ws.numel()
+  raw = ws.cpu().numpy()
+  row_end_off = out.row_end - ws.data_ptr()
+  ent_off = out.entries - ws.data_ptr()
+  row_end = raw[row_end_off:row_end_off + batch * n_rows * 4].view(np.int32).reshape(batch, n_rows)
+  got_entries = raw[ent_off:ent_off + batch * n_ent * 16].view(np.int32).reshape(batch, n_ent, 4)
+  tiles = seg.numpy().reshape(batch, nt, 128)
+  lo, hi = tiles.min(-1), tiles.max(-1)
+  overlap = lambda b, qt, kt: not (hi[b, qt] < lo[b, kt] or lo[b, qt] > hi[b, kt])
+  for b in range(batch):
+    for r in range(n_rows):
+      want = []
+      for e in range(row_ptr[r], row_ptr[r + 1]):
+        x, st = int(entries[e, 0]), int(entries[e, 1])
+        s0, s1 = st & 3, (st >> 2) & 3
+        if kind == 0:
+          s0 = s0 if s0 and overlap(b, 2 * r, x) else 0
+          s1 = s1 if s1 and 2 * r + 1 < nt and overlap(b, 2 * r + 1, x) else 0
+        elif kind == 1:
+          s0, s1 = (s0 if s0 and overlap(b, r, x) else 0), 0
+        else:
+          s0, s1 = (s0 if s0 and overlap(b, x, r) else 0), 0
+        if s0 or s1:
+          want.append((x, s0 | (s1 << 2)))
+      got = [(int(a[0]), int(a[1])) for a in got_entries[b, row_ptr[r]:row_end[b, r]]]
+      assert got == want, (b, r)
+  assert out.entries_per_batch == n_ent and (row_end <= row_ptr[1:][None]).all()
+  assert (row_end.astype(np.int64) - row_ptr[:-1][None]).sum() < batch * n_ent  # something was dropped
+
+
 @pytest.mark.parametrize("bq,bkv", [(256, 128), (128, 256), (512, 512)])
 def test_block_sizes(bq, bkv):
   s = 1024

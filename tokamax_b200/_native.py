@@ -23,6 +23,7 @@ SOURCES = (
     "splash_host.cu",
     "schedule_builder.cc",
     "maskinfo_builder.cc",
+    "segment_schedule.cu",
 )
 
 NVCC_FLAGS = (
@@ -106,6 +107,9 @@ class SplashDeviceSchedule(C.Structure):
       ("partial_mask_blocks", C.c_void_p),
       ("block_q", C.c_int32),
       ("block_kv", C.c_int32),
+      ("n_entries", C.c_int64),
+      ("row_end", C.c_void_p),
+      ("entries_per_batch", C.c_int64),
   ]
 
 
@@ -154,6 +158,10 @@ _PROTOTYPES = {
     "splash_schedule_build": (C.c_int, [C.c_void_p, C.c_void_p, C.c_int32, C.c_int32, C.c_int32,
                                         C.c_int32, C.c_int32, C.POINTER(SplashScheduleOut)]),
     "splash_schedule_free": (None, [C.POINTER(SplashScheduleOut)]),
+    "splash_segment_schedule_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64, C.c_int32, C.c_int64]),
+    "splash_segment_schedule": (C.c_int, [C.POINTER(SplashDeviceSchedule), C.c_int32, C.c_void_p, C.c_void_p,
+                                          C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t,
+                                          C.POINTER(SplashDeviceSchedule), C.c_void_p]),
     "splash_fwd": (C.c_int, [C.POINTER(SplashFwdArgs), C.c_void_p]),
     "splash_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "splash_bwd": (C.c_int, [C.POINTER(SplashBwdArgs), C.c_void_p]),

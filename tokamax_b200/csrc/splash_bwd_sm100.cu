@@ -88,6 +88,8 @@ struct BwdParams {
   const int32_t* q_sequence;
   const int32_t* row_ptr;
   const int4* entries;
+  const int32_t* row_end;      // per batch row [batch, n_rows] or nullptr
+  int64_t entries_per_batch;   // 0: one list shared by all batch rows
   const int8_t* pmb;
   int pm_bq, pm_bkv;
   SplashMaskFn fn;
@@ -157,7 +159,8 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
   const int batch = blockIdx.z;
   const int kv_head = head / (p.q_heads / p.kv_heads);
   const int ebeg = p.row_ptr[q_tile];
-  const int eend = p.row_ptr[q_tile + 1];
+  const int eend = p.row_end ? p.row_end[(int64_t)batch * p.n_rows + q_tile] : p.row_ptr[q_tile + 1];
+  const int4* entries = p.entries + (int64_t)batch * p.entries_per_batch;
   const int n_ent = eend - ebeg;
 
   if (threadIdx.x == 0) {
@@ -206,7 +209,7 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       uint32_t it = 0;
       bool ok = true;
       for (int e = ebeg; e < eend && ok; ++e) {
-        const int col = p.entries[e].x;
+        const int col = entries[e].x;
         for (int kv = 0; kv < 2 && ok; ++kv, ++it) {
           const uint32_t s = it % kDqStages;
           ok = mbar_wait(&bars->ring_empty[s], ((it / kDqStages) & 1u) ^ 1u, ab, 0x1100u + s);
@@ -328,10 +331,10 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float c = p.scale_log2;
     bool ok = true;
 
-    int4 ent_next = n_ent > 0 ? p.entries[ebeg] : make_int4(0, 0, 0, 0);
+    int4 ent_next = n_ent > 0 ? entries[ebeg] : make_int4(0, 0, 0, 0);
     for (int n = 0; n < n_ent; ++n) {
       const int4 ent = ent_next;
-      if (n + 1 < n_ent) ent_next = p.entries[ebeg + n + 1];  // fetched a step ahead of its use
+      if (n + 1 < n_ent) ent_next = entries[ebeg + n + 1];  // fetched a step ahead of its use
       const int st = ent.y & 3;
       const int kv0 = ent.x * kTile + w * 64;
       const uint32_t t_s = tmem + lane_addr + (n & 1) * kTile;
@@ -503,7 +506,8 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int batch = blockIdx.z;
   const int group = p.q_heads / p.kv_heads;
   const int ebeg = p.row_ptr[kv_tile];
-  const int eend = p.row_ptr[kv_tile + 1];
+  const int eend = p.row_end ? p.row_end[(int64_t)batch * p.n_rows + kv_tile] : p.row_ptr[kv_tile + 1];
+  const int4* entries = p.entries + (int64_t)batch * p.entries_per_batch;
   const int n_ent = eend - ebeg;
   const int n_steps = n_ent * group;
   const int n_half = 2 * n_steps;
@@ -558,7 +562,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const int head = kv_head * group + g;
         const int64_t stat_base = ((int64_t)batch * p.q_heads + head) * p.q_len;
         for (int e = ebeg; e < eend && ok; ++e) {
-          const int qt = p.entries[e].x;
+          const int qt = entries[e].x;
           for (int which = 0; which < 2 && ok; ++which, ++it) {
             const uint32_t s = it % kBwdStages;
             ok = mbar_wait(&bars->ring_empty[s], ((it / kBwdStages) & 1u) ^ 1u, ab, 0x2100u + s);
@@ -672,10 +676,10 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     int n = 0;
 
     for (int g = 0; g < group && ok; ++g) {
-      int4 ent_next = n_ent > 0 ? p.entries[ebeg] : make_int4(0, 0, 0, 0);
+      int4 ent_next = n_ent > 0 ? entries[ebeg] : make_int4(0, 0, 0, 0);
       for (int e = ebeg; e < eend && ok; ++e, ++n) {
         const int4 ent = ent_next;
-        if (e + 1 < eend) ent_next = p.entries[e + 1];  // fetched a step ahead of its use
+        if (e + 1 < eend) ent_next = entries[e + 1];  // fetched a step ahead of its use
         const int st = ent.y & 3;
         const uint32_t ph = (uint32_t)n & 1u;
         const int q0 = ent.x * kTile + w * 64 + cq * 32;  // first q column of this thread's 32
@@ -929,6 +933,8 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.out1_sb = p.out1_sh = p.out1_ss = 0;
   p.row_ptr = a.sched_dq.row_ptr;
   p.entries = reinterpret_cast<const int4*>(a.sched_dq.entries);
+  p.row_end = a.sched_dq.row_end;
+  p.entries_per_batch = a.sched_dq.entries_per_batch;
   p.pmb = a.sched_dq.partial_mask_blocks;
   p.pm_bq = a.sched_dq.block_q > 0 ? a.sched_dq.block_q : kTile;
   p.pm_bkv = a.sched_dq.block_kv > 0 ? a.sched_dq.block_kv : kTile;
@@ -948,6 +954,8 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.out1_ss = a.dv.stride[2];
   p.row_ptr = a.sched_dkv.row_ptr;
   p.entries = reinterpret_cast<const int4*>(a.sched_dkv.entries);
+  p.row_end = a.sched_dkv.row_end;
+  p.entries_per_batch = a.sched_dkv.entries_per_batch;
   p.pmb = a.sched_dkv.partial_mask_blocks;
   p.pm_bq = a.sched_dkv.block_q > 0 ? a.sched_dkv.block_q : kTile;
   p.pm_bkv = a.sched_dkv.block_kv > 0 ? a.sched_dkv.block_kv : kTile;

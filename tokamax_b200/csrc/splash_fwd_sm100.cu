@@ -40,6 +40,8 @@ struct FwdParams {
   const int32_t* q_sequence;
   const int32_t* row_ptr;
   const int4* entries;
+  const int32_t* row_end;      // per batch row [batch, n_rows] or nullptr
+  int64_t entries_per_batch;   // 0: one list shared by all batch rows
   const int8_t* pmb;
   int pm_bq, pm_bkv;
   SplashMaskFn fn;
@@ -80,7 +82,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int batch = blockIdx.z;
   const int kv_head = head / (p.q_heads / p.kv_heads);
   const int ebeg = p.row_ptr[row];
-  const int eend = p.row_ptr[row + 1];
+  const int eend = p.row_end ? p.row_end[(int64_t)batch * p.n_rows + row] : p.row_ptr[row + 1];
+  const int4* entries = p.entries + (int64_t)batch * p.entries_per_batch;
   const int qt0 = row * 2;
 
   if (threadIdx.x == 0) {
@@ -132,7 +135,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t it = 0;
       bool ok = true;
       for (int e = ebeg; e < eend && ok; ++e) {
-        const int col = p.entries[e].x;
+        const int col = entries[e].x;
         for (int kv = 0; kv < 2 && ok; ++kv, ++it) {
           const uint32_t s = it % kFwdStages;
           const uint32_t ph = (it / kFwdStages) & 1u;
@@ -185,7 +188,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       uint32_t pcnt[2] = {0, 0};
       bool started[2] = {false, false};
       if (n_ent > 0 && ok) {
-        const int4 e0 = p.entries[ebeg];
+        const int4 e0 = entries[ebeg];
         ok = mbar_wait(&bars->kv_full[0], 0, ab, 0x300u);
         if (ok) {
           mma_issue_fence();
@@ -197,7 +200,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         for (int n = 0; n < n_ent && ok; ++n) {
           const int4 cur = nxt;
           const bool has_next = n + 1 < n_ent;
-          if (has_next) nxt = p.entries[ebeg + n + 1];
+          if (has_next) nxt = entries[ebeg + n + 1];
           const uint32_t itv = 2 * n + 1, itk = 2 * n + 2;
           const uint32_t vslot = itv % kFwdStages, kslot = itk % kFwdStages;
           ok = mbar_wait(&bars->kv_full[vslot], (itv / kFwdStages) & 1u, ab, 0x310u + vslot);
@@ -250,10 +253,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     bool started = false;
     bool ok = true;
 
-    int4 ent_next = ebeg < eend ? p.entries[ebeg] : make_int4(0, 0, 0, 0);
+    int4 ent_next = ebeg < eend ? entries[ebeg] : make_int4(0, 0, 0, 0);
     for (int e = ebeg; e < eend; ++e) {
       const int4 ent = ent_next;
-      if (e + 1 < eend) ent_next = p.entries[e + 1];  // fetched a step ahead of its use
+      if (e + 1 < eend) ent_next = entries[e + 1];  // fetched a step ahead of its use
       const int st = (ent.y >> (2 * i)) & 3;
       if (st == 0) continue;
       ok = mbar_wait(&bars->s_full[i], cnt & 1u, ab, 0x400u + i);
@@ -456,6 +459,8 @@ int launch_fwd(const SplashFwdArgs& a, cudaStream_t stream) {
   p.q_sequence = a.q_sequence;
   p.row_ptr = a.sched.row_ptr;
   p.entries = reinterpret_cast<const int4*>(a.sched.entries);
+  p.row_end = a.sched.row_end;
+  p.entries_per_batch = a.sched.entries_per_batch;
   p.pmb = a.sched.partial_mask_blocks;
   p.pm_bq = a.sched.block_q > 0 ? a.sched.block_q : kTile;
   p.pm_bkv = a.sched.block_kv > 0 ? a.sched.block_kv : kTile;

@@ -190,6 +190,7 @@ class _DeviceTables:
     d.row_ptr = rp.data_ptr()
     d.entries = en.data_ptr()
     d.n_rows = len(row_ptr) - 1
+    d.n_entries = int(row_ptr[-1])
     d.block_q, d.block_kv = bq, bkv
     d.partial_mask_blocks = None
     if pmb is not None:
@@ -197,6 +198,28 @@ class _DeviceTables:
       self.keep.append(pm)
       d.partial_mask_blocks = pm.data_ptr()
     return d
+
+
+def _segment_schedule(sched: _native.SplashDeviceSchedule, kind: int, q_seg, kv_seg, q_len: int, kv_len: int):
+  """Per-batch-row copy of ``sched`` without the tiles the segment ids rule out (device side).
+
+  Returns ``(schedule, workspace tensor to keep alive)``; with no entries at all the input
+  schedule is returned unchanged.
+  """
+  if sched.n_entries == 0:
+    return sched, None
+  lib = _native.lib()
+  batch = q_seg.shape[0]
+  nbytes = lib.splash_segment_schedule_bytes(batch, q_len, kv_len, sched.n_rows, sched.n_entries)
+  ws = torch.empty(nbytes, dtype=torch.uint8, device=q_seg.device)
+  out = _native.SplashDeviceSchedule()
+  stream = torch.cuda.current_stream(q_seg.device).cuda_stream
+  with torch.cuda.device(q_seg.device):
+    _native.check(
+        lib.splash_segment_schedule(C.byref(sched), kind, q_seg.data_ptr(), kv_seg.data_ptr(), batch, q_len, kv_len,
+                                    ws.data_ptr(), nbytes, C.byref(out), C.c_void_p(stream)),
+        "splash_segment_schedule")
+  return out, ws
 
 
 def _tensor_desc(t: torch.Tensor) -> _native.SplashTensor:
@@ -242,7 +265,11 @@ class _SplashFunction(torch.autograd.Function):
     args.q_segment_ids = q_seg.data_ptr() if q_seg is not None else None
     args.kv_segment_ids = kv_seg.data_ptr() if kv_seg is not None else None
     args.q_sequence = tables.q_sequence.data_ptr() if tables.q_sequence is not None else None
+    keep = []
     args.sched = tables.fwd
+    if q_seg is not None:
+      args.sched, ws = _segment_schedule(tables.fwd, 0, q_seg, kv_seg, q.shape[2], k.shape[2])
+      keep.append(ws)
     args.mask_fn = _mask_fn_struct(kernel.mask_function_rule)
     args.scale = scale
     args.mask_value = max(kernel.mask_value, -3.0e38)
@@ -273,8 +300,13 @@ class _SplashFunction(torch.autograd.Function):
     args.q_segment_ids = q_seg.data_ptr() if q_seg is not None else None
     args.kv_segment_ids = kv_seg.data_ptr() if kv_seg is not None else None
     args.q_sequence = tables.q_sequence.data_ptr() if tables.q_sequence is not None else None
+    keep = []
     args.sched_dq = tables.dq
     args.sched_dkv = tables.dkv
+    if q_seg is not None:
+      args.sched_dq, ws1 = _segment_schedule(tables.dq, 1, q_seg, kv_seg, q.shape[2], k.shape[2])
+      args.sched_dkv, ws2 = _segment_schedule(tables.dkv, 2, q_seg, kv_seg, q.shape[2], k.shape[2])
+      keep += [ws1, ws2]
     args.mask_fn = _mask_fn_struct(kernel.mask_function_rule)
     args.scale = ctx.scale
     args.workspace = workspace.data_ptr()
