@@ -267,16 +267,6 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ok = mbar_wait(&bars->ds_full, n & 1u, ab, 0x1230u);
         if (!ok) break;
         mma_issue_fence();
-#ifdef SPLASH_DQ_DP_FIRST
-        // dP of the next step goes first: the compute warps wait on it, while nothing waits on dQ.
-        if (has_next) {
-          ok = ring_wait(it_vn, 0x1240u);
-          if (!ok) break;
-          mma_issue_fence();
-          ss_kmajor(t_dp, do_addr, ring_addr + (it_vn % kDqStages) * kTileBytes);
-          tc_commit(&bars->dp_full);
-          tc_commit(&bars->ring_empty[it_vn % kDqStages]);
-        }
         {
           // dQ += dS_n K_n : A = packed dS in the S buffer, B = K tile read MN-major.
           const uint32_t a_base = tmem + (n & 1) * kTile;
@@ -287,18 +277,6 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     idesc_mn, (n > 0 || k > 0) ? 1u : 0u);
           tc_commit(&bars->ring_empty[it_k % kDqStages]);
         }
-#else
-        {
-          // dQ += dS_n K_n : A = packed dS in the S buffer, B = K tile read MN-major.
-          const uint32_t a_base = tmem + (n & 1) * kTile;
-          const uint32_t b0 = ring_addr + (it_k % kDqStages) * kTileBytes;
-#pragma unroll
-          for (int k = 0; k < 8; ++k)
-            umma_ts(t_dq, a_base + packed_a_col(k), make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024),
-                    idesc_mn, (n > 0 || k > 0) ? 1u : 0u);
-          tc_commit(&bars->ring_empty[it_k % kDqStages]);
-        }
-        // dP of the next step goes first: the compute warps wait on it, while nothing waits on dQ.
         if (has_next) {
           ok = ring_wait(it_vn, 0x1240u);
           if (!ok) break;
@@ -307,7 +285,6 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           tc_commit(&bars->dp_full);
           tc_commit(&bars->ring_empty[it_vn % kDqStages]);
         }
-#endif
       }
       tc_commit(&bars->acc_done);
     }
