@@ -44,6 +44,7 @@ WORKLOADS = {
     "c2": dict(config_id=2, batch=4, q_heads=32, kv_heads=8, seq=8192, mask="causal"),
     "c3": dict(config_id=3, batch=8, q_heads=16, kv_heads=16, seq=16384, mask="local4096_causal_segments"),
     "c4": dict(config_id=4, batch=1, q_heads=64, kv_heads=8, seq=131072, mask="causal"),
+    "c5": dict(config_id=5, batch=2, q_heads=32, kv_heads=8, seq=32768, mask="causal"),  # e4m3, forward only
 }
 
 
@@ -451,6 +452,68 @@ def run_single_gpu(args, w, wname):
   print(json.dumps(line), flush=True)
 
 
+def run_fp8_prefill(args, w, wname):
+  """Forward only on block-scaled e4m3 Q/K/V (scales per 128-token tile), bf16 output."""
+  from tokamax_b200 import fp8
+
+  dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+  torch.cuda.set_device(dev)
+  kernel = make_kernel(w)
+  n_live = live_pairs(w, None)
+  flops = 4 * D * w["q_heads"] * n_live
+  q, k, v, _ = device_inputs(w, dev)
+  qq, kq, vq = (fp8.quantize_e4m3(t) for t in (q, k, v))
+
+  def step():
+    return fp8.splash_fwd_fp8(kernel, qq, kq, vq, logits_scale=SCALE)
+
+  def step_bf16():
+    with torch.no_grad():
+      return kernel(q, k, v, logits_scale=SCALE)
+
+  sampler = ClockSampler(dev.index or 0)
+  for _ in range(args.warmup):
+    step()
+  torch.cuda.synchronize()
+  sampler.start()
+  ms = timed_steps(step, args.steps, 0)
+  clocks = sampler.stop()
+  kernel.check_errors()
+  ms_bf16 = timed_steps(step_bf16, max(3, args.steps // 3), 2)
+  value = flops / ms / 1e9
+
+  e2e = None
+  if not args.no_e2e:
+    host = [t.cpu().pin_memory() for pair in (qq, kq, vq) for t in (pair.data.view(torch.uint8), pair.scale)]
+    o_host = torch.empty((w["batch"], w["q_heads"], w["seq"], D), dtype=torch.bfloat16).pin_memory()
+
+    def e2e_step():
+      d = [t.to(dev, non_blocking=True) for t in host]
+      ts = [fp8.Fp8Tensor(d[2 * i].view(torch.float8_e4m3fn), d[2 * i + 1]) for i in range(3)]
+      o_host.copy_(fp8.splash_fwd_fp8(kernel, *ts, logits_scale=SCALE), non_blocking=True)
+
+    ms_e2e = timed_steps(e2e_step, max(2, min(args.steps, 5)), 1)
+    e2e = {"value": flops / ms_e2e / 1e9, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+           "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host),
+           "d2h_bytes_per_step": o_host.numel() * 2}
+
+  peak, _, peak_src = measured_peaks()
+  line = {
+      "metric": "splash fp8 forward TFLOP/s (masked FLOPs)", "value": value, "unit": "TFLOP/s", "n_gpus": 1,
+      "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+      "vs_baseline": None, "dtype": "f8e4m3", "data": "synthetic",
+      "config": {"workload": wname, **{k_: w[k_] for k_ in ("batch", "q_heads", "kv_heads", "seq", "mask")},
+                 "head_dim": D, "n_live_pairs": n_live, "flops_per_step": flops,
+                 "l2": "inputs (168 MB of e4m3 plus a 537 MB output) are larger than the 126 MB L2"},
+      "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps,
+      "roofline": {"kernel": "splash_fwd_kernel<true>", "bound": "tensor", "achieved": value, "peak": 2 * peak,
+                   "unit": "TFLOP/s", "frac": value / (2 * peak),
+                   "peak_source": f"2 x {peak_src} bf16 burst (no fp8 GEMM peak was measured on this pool)",
+                   "traffic": None, "bf16_forward_same_shape_tflops": flops / ms_bf16 / 1e9},
+  }
+  print(json.dumps(line), flush=True)
+
+
 def run_context_parallel(args, w, wname):
   import torch.distributed as dist
   from tokamax_b200 import ulysses
@@ -544,7 +607,7 @@ def main():
   ap.add_argument("--steps", type=int, default=30)
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-  ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4"])
+  ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4", "c5"])
   ap.add_argument("--no-e2e", action="store_true")
   ap.add_argument("--no-cpu-baseline", action="store_true")
   args = ap.parse_args()
@@ -559,7 +622,11 @@ def main():
     return
   if not torch.cuda.is_available():
     raise SystemExit("bench.py needs a CUDA device (B200); there is no CPU path for the kernels")
-  if world == 1:
+  if wname == "c5":
+    if world != 1:
+      raise SystemExit("c5 (fp8 prefill) is a single-GPU workload")
+    run_fp8_prefill(args, w, wname)
+  elif world == 1:
     run_single_gpu(args, w, wname)
   else:
     run_context_parallel(args, w, wname)

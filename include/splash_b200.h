@@ -213,6 +213,23 @@ typedef struct SplashFwdArgs {
 
 int splash_fwd(const SplashFwdArgs* args, void* cuda_stream);
 
+/* Forward for e4m3 inputs (inference prefill).  No counterpart in the reference, whose splash path
+ * rejects everything but bf16 / f32 (pallas_mosaic_tpu_common.py:40-42); the contract is the bf16
+ * forward above run on the dequantised tensors.
+ * base.q / base.k / base.v are SPLASH_F8E4M3 (element strides multiples of 16), base.o is bf16.
+ * Each scale array is fp32 [batch, heads, seq / 128]: the stored values of one 128-token tile of
+ * one head times its scale are the real values.  Scales must be finite and >= 0.  Every other
+ * field means what it means for splash_fwd; logsumexp / max_logits refer to the dequantised
+ * logits. */
+typedef struct SplashFwdFp8Args {
+  SplashFwdArgs base;
+  const float* q_scale;             /* [batch, q_heads, q_len / 128] */
+  const float* k_scale;             /* [batch, kv_heads, kv_len / 128] */
+  const float* v_scale;             /* [batch, kv_heads, kv_len / 128] */
+} SplashFwdFp8Args;
+
+int splash_fwd_fp8(const SplashFwdFp8Args* args, void* cuda_stream);
+
 /* ------------------------------------------------------------------------------------------
  * Backward.  Replaces `_splash_attention_bwd` + `_splash_attention_bwd_dkv` +
  * `_flash_attention_dkv_kernel` (splash_attention_kernel.py:1871-1947, :1462-1868, :1234-1459):

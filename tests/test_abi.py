@@ -40,6 +40,7 @@ def test_null_and_invalid_arguments_return_status_codes():
   lib = _native.lib()
   assert lib.splash_fwd(None, None) == -1
   assert lib.splash_bwd(None, None) == -1
+  assert lib.splash_fwd_fp8(None, None) == -1
   assert lib.splash_read_error(None, None, None) == -1
   assert lib.splash_bwd_workspace_bytes(0, 1, 1) == 0
   assert lib.splash_bwd_workspace_bytes(2, 8, 1024) == 2 * (2 * 8 * 1024 * 4)  # di and -lse*log2e

@@ -1,0 +1,90 @@
+"""Block-scaled e4m3 forward against the oracle run on the dequantised tensors.
+
+Tolerances (this variant has no reference implementation; they are this build's contract):
+  * logsumexp / max_logits <= 1e-3 against the oracle fed the exact (fp32) dequantised values:
+    the score path is exact products of e4m3 values accumulated in fp32, so it carries the same
+    bound as the bf16 kernel.
+  * output: P is rounded to e4m3 (3 mantissa bits, relative error up to 2^-4 per weight) before
+    the PV product, so rows with few live keys see errors of a few percent of |v|.  The bound is
+    relative L2 <= 3e-2 over the tensor and max-abs <= 0.25 against the oracle fed the
+    dequantised values rounded to bf16.
+"""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import attention_ref
+from tokamax_b200 import fp8
+from tokamax_b200 import splash_attention_kernel as splash
+from tokamax_b200 import splash_attention_mask as mask_lib
+
+pytestmark = pytest.mark.gpu
+D = 128
+DEV = "cuda:0"
+
+
+def _randn(seed, *shape):
+  g = torch.Generator().manual_seed(seed)
+  return torch.randn(*shape, generator=g)
+
+
+def _check(mask, q, k, v, scale):
+  dense = np.asarray(mask[:, :]) if not isinstance(mask, np.ndarray) else mask
+  qq, kq, vq = (fp8.quantize_e4m3(x.to(DEV)) for x in (q, k, v))
+  kernel = splash.make_splash_mha_single_device(mask, save_residuals=True)
+  o, res = fp8.splash_fwd_fp8(kernel, qq, kq, vq, logits_scale=scale, save_residuals=True)
+  torch.cuda.synchronize()
+  kernel.check_errors()
+  o = o.float().cpu()
+  for b in range(q.shape[0]):
+    exact = [fp8.dequantize_e4m3(fp8.Fp8Tensor(t.data[b:b + 1], t.scale[b:b + 1]), torch.float32)[0].cpu()
+             for t in (qq, kq, vq)]
+    _, lse, mx = attention_ref.attention_reference(*exact, dense, scale=scale)
+    assert (res["logsumexp"][b].cpu() - lse).abs().max() <= 1e-3
+    assert (res["max_logits"][b].cpu() - mx).abs().max() <= 1e-3
+    rounded = [x.to(torch.bfloat16) for x in exact]
+    ref, _, _ = attention_ref.attention_reference(*rounded, dense, scale=scale)
+    err = o[b] - ref
+    assert err.norm() / ref.norm() <= 3e-2, float(err.norm() / ref.norm())
+    assert err.abs().max() <= 0.25, float(err.abs().max())
+
+
+@pytest.mark.parametrize("kind", ["causal", "full", "local"])
+def test_fp8_forward_matches_oracle_on_dequantised_inputs(kind):
+  b, hq, hkv, s = 2, 4, 2, 1024
+  q, k, v = _randn(51, b, hq, s, D), _randn(52, b, hkv, s, D), _randn(53, b, hkv, s, D)
+  if kind == "causal":
+    mask = mask_lib.CausalMask((s, s))
+  elif kind == "full":
+    mask = mask_lib.FullMask((s, s))
+  else:
+    mask = mask_lib.LocalMask((s, s), (300, 100), 0)
+  _check(mask, q, k, v, 1 / math.sqrt(D))
+
+
+def test_fp8_scales_varying_by_tile_and_zero_tiles():
+  b, hq, hkv, sq, skv = 1, 2, 1, 256, 768
+  q, k, v = _randn(61, b, hq, sq, D), _randn(62, b, hkv, skv, D), _randn(63, b, hkv, skv, D)
+  # different magnitudes per 128-token tile, one all-zero V tile, one all-zero K tile
+  v_gain = torch.tensor([1.0, 30.0, 0.0, 0.02, 5.0, 1.0])
+  k_gain = torch.tensor([1.0, 0.5, 2.0, 0.0, 1.5, 0.25])
+  q_gain = torch.tensor([0.5, 2.0])
+  v = v * v_gain.repeat_interleave(128)[None, None, :, None]
+  k = k * k_gain.repeat_interleave(128)[None, None, :, None]
+  q = q * q_gain.repeat_interleave(128)[None, None, :, None]
+  _check(mask_lib.FullMask((sq, skv)), q, k, v, 0.05)
+
+
+def test_fp8_rejects_bad_arguments():
+  s = 256
+  kernel = splash.make_splash_mha_single_device(mask_lib.CausalMask((s, s)))
+  x = fp8.quantize_e4m3(_randn(71, 1, 2, s, D).to(DEV))
+  with pytest.raises(ValueError):
+    fp8.splash_fwd_fp8(kernel, fp8.Fp8Tensor(x.data.to(torch.bfloat16), x.scale), x, x)
+  with pytest.raises(ValueError):
+    fp8.splash_fwd_fp8(kernel, x, x, fp8.Fp8Tensor(x.data, x.scale[..., :1]))
+  short = fp8.quantize_e4m3(_randn(72, 1, 2, 128, D).to(DEV))
+  with pytest.raises(ValueError):
+    fp8.splash_fwd_fp8(kernel, x, short, short)

@@ -129,6 +129,15 @@ class SplashFwdArgs(C.Structure):
   ]
 
 
+class SplashFwdFp8Args(C.Structure):
+  _fields_ = [
+      ("base", SplashFwdArgs),
+      ("q_scale", C.c_void_p),
+      ("k_scale", C.c_void_p),
+      ("v_scale", C.c_void_p),
+  ]
+
+
 class SplashBwdArgs(C.Structure):
   _fields_ = [
       ("q", SplashTensor), ("k", SplashTensor), ("v", SplashTensor), ("o", SplashTensor),
@@ -163,6 +172,7 @@ _PROTOTYPES = {
                                           C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t,
                                           C.POINTER(SplashDeviceSchedule), C.c_void_p]),
     "splash_fwd": (C.c_int, [C.POINTER(SplashFwdArgs), C.c_void_p]),
+    "splash_fwd_fp8": (C.c_int, [C.POINTER(SplashFwdFp8Args), C.c_void_p]),
     "splash_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "splash_bwd": (C.c_int, [C.POINTER(SplashBwdArgs), C.c_void_p]),
     "splash_bwd_static_scratch": (C.c_int, [C.POINTER(SplashBwdArgs), C.c_void_p]),

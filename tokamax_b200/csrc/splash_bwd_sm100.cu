@@ -68,7 +68,10 @@ __global__ void __launch_bounds__(256) splash_delta_kernel(const DeltaParams p) 
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (lane == 0) {
     p.delta[row] = acc;
-    p.nlse2[row] = -p.lse[row] * kLog2e;
+    // Rows that never met a live key carry the mask value as logsumexp; -inf keeps their
+    // probabilities at exactly zero instead of overflowing the product to +inf.
+    const float lse = p.lse[row];
+    p.nlse2[row] = lse < -1.0e20f ? -INFINITY : -lse * kLog2e;
   }
 }
 
@@ -846,6 +849,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   if (a.mask_fn.kind == SPLASH_MASK_CHUNKED && a.mask_fn.chunk <= 0)
     return SPLASH_ERR_INVALID_ARGUMENT;
   if (Hq > 65535 || B > 65535) return SPLASH_ERR_TOO_LARGE;
+  if (!(a.scale > 0.f) || !(a.scale < 1.0e30f)) return SPLASH_ERR_INVALID_ARGUMENT;
 
   CUtensorMap tm_q, tm_do, tm_k, tm_v;
   if ((st = make_tile_tensor_map(&tm_q, a.q, kTile)) || (st = make_tile_tensor_map(&tm_do, a.d_o, kTile)) ||

@@ -46,5 +46,6 @@ __device__ __forceinline__ RowInterval mask_fn_interval(const SplashMaskFn& fn, 
 // Host-side helpers (defined in splash_host.cu).
 int make_tile_tensor_map(CUtensorMap* out, const SplashTensor& t, int box_rows);
 int check_bf16_tensor(const SplashTensor& t);
+int check_e4m3_tensor(const SplashTensor& t);
 
 }  // namespace sb

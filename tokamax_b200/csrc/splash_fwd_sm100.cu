@@ -1,4 +1,5 @@
-// Splash attention forward for sm_100a: bf16 Q/K/V, head_dim 128, fp32 accumulation.
+// Splash attention forward for sm_100a: bf16 (or block-scaled e4m3) Q/K/V, head_dim 128, fp32
+// accumulation.
 //
 // One CTA owns two adjacent 128-row q tiles of one (batch, q head) and walks the kv tiles its
 // schedule row lists.  Roles (384 threads):
@@ -20,6 +21,15 @@
 // Follows the arithmetic of the reference forward kernel
 // (tokamax/_src/ops/experimental/tpu/splash_attention/splash_attention_kernel.py:299-527,
 // masking :202-296) with the softmax scale applied in fp32 inside the kernel.
+//
+// kFp8 = true is the e4m3 prefill variant: Q, K and V hold e4m3 values with one fp32 scale per
+// (batch, head, 128-token tile).  Tiles are 128 x 128 bytes (one swizzle atom wide), both MMAs run
+// as kind::f8f6f4 with K = 32 per instruction, the product of the q and k tile scales is folded
+// into the fp32 softmax scale of each score tile, and P is written back as e4m3 (four values per
+// TMEM column) after being multiplied by 2^kFp8PShift and by the V tile's scale relative to the
+// largest V scale of the (batch, kv head), so that it sits in the normal range of the format and
+// never exceeds it.  There is no counterpart of this variant in the reference, which accepts
+// bf16 / f32 only.
 #include "splash_common.cuh"
 
 namespace sb {
@@ -29,6 +39,15 @@ constexpr int kFwdThreads = 384;  // 3 warpgroups: softmax 0, softmax 1, {TMA, M
 constexpr int kSoftmaxRegs = 224;  // setmaxnreg targets: 2*128*224 + 128*56 <= 64K registers
 constexpr int kIssueRegs = 56;
 constexpr float kRescaleThreshold = 8.0f;  // log2 units
+// Lower bound of the running maximum (log2 units).  A row whose entries so far are all masked
+// would otherwise take the scaled masked logit as its maximum and turn its masked entries into
+// exp2(rounding error of a 1e29-sized product); with the floor they stay exactly zero, l stays 0,
+// and a row that never meets a live key ends as zeros with logsumexp = mask_value.
+constexpr float kLogitFloor = -1.0e6f;
+constexpr float kMinScaleLog2 = 1.0e-20f;  // keeps kMaskedLogit * scale far below kLogitFloor
+constexpr float kFp8RescaleThreshold = 2.0f;  // e4m3 P must stay below 448 = 2^8.8
+constexpr float kFp8PShift = 6.0f;            // P is stored as 2^6 * exp2(s - m) * (v scale ratio <= 1)
+constexpr int kFp8TileBytes = kTile * kHeadDim;  // 16 KiB
 
 struct FwdParams {
   __nv_bfloat16* o;
@@ -48,6 +67,11 @@ struct FwdParams {
   int q_len, kv_len, q_heads, kv_heads, n_q_tiles, n_rows;
   float scale, scale_log2, mask_value;
   uint32_t* err;
+  // e4m3 variant only: one scale per (batch, head, 128-token tile)
+  const float* q_scale;
+  const float* k_scale;
+  const float* v_scale;
+  int n_kv_tiles;
 };
 
 struct FwdBarriers {
@@ -62,18 +86,33 @@ struct FwdBarriers {
   uint32_t early_exit;
 };
 
-constexpr int kFwdSmemBytes = 2 * kTileBytes + kFwdStages * kTileBytes + 1024 /*barriers*/ +
-                              1024 /*alignment slack*/;
+constexpr int fwd_smem_bytes(bool fp8) {
+  return (2 + kFwdStages) * (fp8 ? kFp8TileBytes : kTileBytes) + 1024 /*barriers*/ +
+         1024 /*alignment slack*/;
+}
 
+__device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
+  uint32_t r;
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t}\n"
+      : "=r"(r)
+      : "f"(a), "f"(b), "f"(c), "f"(d));
+  return r;
+}
+
+template <bool kFp8>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
+  constexpr int kTB = kFp8 ? kFp8TileBytes : kTileBytes;  // bytes of one operand tile
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* q_smem = smem;                                  // 2 tiles
-  uint8_t* kv_smem = smem + 2 * kTileBytes;                // ring
-  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(smem + (2 + kFwdStages) * kTileBytes);
+  uint8_t* kv_smem = smem + 2 * kTB;                       // ring
+  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(smem + (2 + kFwdStages) * kTB);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -126,10 +165,11 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tma_prefetch_desc(&tm_v);
       for (int i = 0; i < 2; ++i) {
         if (qt0 + i < p.n_q_tiles) {
-          uint8_t* dst = q_smem + i * kTileBytes;
-          mbar_arrive_expect_tx(&bars->q_full[i], kTileBytes);
+          uint8_t* dst = q_smem + i * kTB;
+          mbar_arrive_expect_tx(&bars->q_full[i], kTB);
           tma_load_4d(dst, &tm_q, &bars->q_full[i], 0, (qt0 + i) * kTile, head, batch);
-          tma_load_4d(dst + kHalfBytes, &tm_q, &bars->q_full[i], 64, (qt0 + i) * kTile, head, batch);
+          if constexpr (!kFp8)
+            tma_load_4d(dst + kHalfBytes, &tm_q, &bars->q_full[i], 64, (qt0 + i) * kTile, head, batch);
         }
       }
       uint32_t it = 0;
@@ -141,46 +181,67 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const uint32_t ph = (it / kFwdStages) & 1u;
           ok = mbar_wait(&bars->kv_empty[s], ph ^ 1u, ab, 0x100u + s);
           if (!ok) break;
-          uint8_t* dst = kv_smem + s * kTileBytes;
+          uint8_t* dst = kv_smem + s * kTB;
           const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
-          mbar_arrive_expect_tx(&bars->kv_full[s], kTileBytes);
+          mbar_arrive_expect_tx(&bars->kv_full[s], kTB);
           tma_load_4d(dst, tm, &bars->kv_full[s], 0, col * kTile, kv_head, batch);
-          tma_load_4d(dst + kHalfBytes, tm, &bars->kv_full[s], 64, col * kTile, kv_head, batch);
+          if constexpr (!kFp8)
+            tma_load_4d(dst + kHalfBytes, tm, &bars->kv_full[s], 64, col * kTile, kv_head, batch);
         }
       }
     }
   } else if (warp == 9) {
     // ------------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      constexpr uint32_t idesc_qk = make_idesc_bf16(kTile, kTile, false, false);
-      constexpr uint32_t idesc_pv = make_idesc_bf16(kTile, kHeadDim, false, true);
+      constexpr uint32_t idesc_qk =
+          kFp8 ? make_idesc_e4m3(kTile, kTile, false, false) : make_idesc_bf16(kTile, kTile, false, false);
+      constexpr uint32_t idesc_pv = kFp8 ? make_idesc_e4m3(kTile, kHeadDim, false, true)
+                                         : make_idesc_bf16(kTile, kHeadDim, false, true);
       const uint32_t q_addr = smem_u32(q_smem);
       const uint32_t kv_addr = smem_u32(kv_smem);
       bool ok = true;
       for (int i = 0; i < 2 && ok; ++i)
         if (qt0 + i < p.n_q_tiles) ok = mbar_wait(&bars->q_full[i], 0, ab, 0x200u + i);
 
-      // S_i = Q_i K^T : both operands K-major, eight K=16 slices across two swizzle halves.
+      // S_i = Q_i K^T : both operands K-major.  bf16: eight K=16 slices across two swizzle
+      // halves; e4m3: four K=32 slices inside the single 128-byte-wide tile.
       auto issue_qk = [&](int i, uint32_t slot) {
-        const uint32_t a0 = q_addr + i * kTileBytes;
-        const uint32_t b0 = kv_addr + slot * kTileBytes;
+        const uint32_t a0 = q_addr + i * kTB;
+        const uint32_t b0 = kv_addr + slot * kTB;
+        if constexpr (kFp8) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(tmem + i * kTile, make_smem_desc_sw128(a0 + off, 16, 1024),
-                  make_smem_desc_sw128(b0 + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)
+            umma_ss_f8(tmem + i * kTile, make_smem_desc_sw128(a0 + k * 32, 16, 1024),
+                       make_smem_desc_sw128(b0 + k * 32, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+            umma_ss(tmem + i * kTile, make_smem_desc_sw128(a0 + off, 16, 1024),
+                    make_smem_desc_sw128(b0 + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+          }
         }
         tc_commit(&bars->s_full[i]);
       };
       // O_i (+)= P_i V : A from TMEM, B = V tile read MN-major (head_dim contiguous):
-      // 8 kv rows x 128 B per core group (SBO 1024), 64-column halves 16 KiB apart (LBO).
+      // 8 kv rows x 128 B per core group (SBO 1024).  bf16: 64-column halves 16 KiB apart (LBO),
+      // K=16 slices 2 KiB apart; e4m3: the 128 columns fit one 128-byte row, K=32 slices 4 KiB
+      // apart, P packed four values per TMEM column.
       auto issue_pv = [&](int i, uint32_t slot, bool acc) {
-        const uint32_t b0 = kv_addr + slot * kTileBytes;
+        const uint32_t b0 = kv_addr + slot * kTB;
+        if constexpr (kFp8) {
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          umma_ts(tmem + 2 * kTile + i * kTile, tmem + i * kTile + k * 8,
-                  make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024), idesc_pv,
-                  (acc || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k)
+            umma_ts_f8(tmem + 2 * kTile + i * kTile, tmem + i * kTile + k * 8,
+                       make_smem_desc_sw128(b0 + k * 4096, 16, 1024), idesc_pv,
+                       (acc || k > 0) ? 1u : 0u);
+        } else {
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            umma_ts(tmem + 2 * kTile + i * kTile, tmem + i * kTile + k * 8,
+                    make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024), idesc_pv,
+                    (acc || k > 0) ? 1u : 0u);
+          }
         }
       };
 
@@ -244,7 +305,24 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     const uint32_t t_s = tmem + lane_addr + i * kTile;
     const uint32_t t_o = tmem + lane_addr + 2 * kTile + i * kTile;
-    const float c = p.scale_log2;
+    // e4m3: scores carry the q tile's and the kv tile's scale; V tiles are weighted relative to
+    // the largest V scale of this (batch, kv head).
+    float cq = p.scale_log2;
+    float v_ref = 1.f;
+    const float* k_scale = nullptr;
+    const float* v_scale = nullptr;
+    if constexpr (kFp8) {
+      const int64_t kbase = ((int64_t)batch * p.kv_heads + kv_head) * p.n_kv_tiles;
+      k_scale = p.k_scale + kbase;
+      v_scale = p.v_scale + kbase;
+      if (valid) cq *= p.q_scale[((int64_t)batch * p.q_heads + head) * p.n_q_tiles + q_tile];
+      float vm = 0.f;
+      for (int t = lane; t < p.n_kv_tiles; t += 32) vm = fmaxf(vm, __ldg(v_scale + t));
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) vm = fmaxf(vm, __shfl_xor_sync(0xffffffffu, vm, off));
+      v_ref = vm > 0.f ? vm : 1.f;
+    }
+    constexpr float kThreshold = kFp8 ? kFp8RescaleThreshold : kRescaleThreshold;
 
     float m_used = -INFINITY;  // scaled (log2) units
     float m_true = kMaskedLogit;
@@ -254,9 +332,24 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     bool ok = true;
 
     int4 ent_next = ebeg < eend ? entries[ebeg] : make_int4(0, 0, 0, 0);
+    float ks_next = 1.f, vs_next = 1.f;
+    if constexpr (kFp8) {
+      if (ebeg < eend) {
+        ks_next = __ldg(k_scale + ent_next.x);
+        vs_next = __ldg(v_scale + ent_next.x);
+      }
+    }
     for (int e = ebeg; e < eend; ++e) {
       const int4 ent = ent_next;
-      if (e + 1 < eend) ent_next = entries[e + 1];  // fetched a step ahead of its use
+      const float ks = ks_next, vs = vs_next;
+      if (e + 1 < eend) {  // fetched a step ahead of its use
+        ent_next = entries[e + 1];
+        if constexpr (kFp8) {
+          ks_next = __ldg(k_scale + ent_next.x);
+          vs_next = __ldg(v_scale + ent_next.x);
+        }
+      }
+      const float c = fmaxf(kFp8 ? cq * ks : cq, kMinScaleLog2);
       const int st = (ent.y >> (2 * i)) & 3;
       if (st == 0) continue;
       ok = mbar_wait(&bars->s_full[i], cnt & 1u, ab, 0x400u + i);
@@ -325,9 +418,9 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         mx3 = fmaxf(mx3, s[j + 3]);
       }
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
-      m_true = fmaxf(m_true, mx);
-      const float m_new = mx * c;
-      const bool need = m_new > m_used + kRescaleThreshold;
+      const float m_new = fmaxf(mx * c, kLogitFloor);
+      m_true = fmaxf(m_true, kFp8 ? m_new : mx);  // e4m3: log2 units (the scale varies by tile)
+      const bool need = m_new > m_used + kThreshold;
       if (__any_sync(0xffffffffu, need)) {
         const float m_next = fmaxf(m_used, m_new);
         const float alpha = ex2(m_used - m_next);
@@ -347,20 +440,43 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
 
       float ls0 = 0.f, ls1 = 0.f;
+      if constexpr (kFp8) {
+        // P * 2^shift * r with r = v scale / largest v scale in (0, 1]; r is floored so that a
+        // tile of zeros (scale 0) still counts in l.
+        const float r = fmaxf(__fdividef(vs, v_ref), 5.9604645e-8f);
+        const float m_sub = m_used - kFp8PShift - __log2f(r);
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        uint32_t pk[16];
+        for (int g = 0; g < 2; ++g) {
+          uint32_t pk[16];
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float p0 = ex2(fmaf(s[g * 32 + 2 * j], c, -m_used));
-          const float p1 = ex2(fmaf(s[g * 32 + 2 * j + 1], c, -m_used));
-          ls0 += p0;
-          ls1 += p1;
-          pk[j] = pack_bf16(p0, p1);
+          for (int j = 0; j < 16; ++j) {
+            const float p0 = ex2(fmaf(s[g * 64 + 4 * j], c, -m_sub));
+            const float p1 = ex2(fmaf(s[g * 64 + 4 * j + 1], c, -m_sub));
+            const float p2 = ex2(fmaf(s[g * 64 + 4 * j + 2], c, -m_sub));
+            const float p3 = ex2(fmaf(s[g * 64 + 4 * j + 3], c, -m_sub));
+            ls0 += p0 + p2;
+            ls1 += p1 + p3;
+            pk[j] = pack_e4m3x4(p0, p1, p2, p3);
+          }
+          tmem_st16(t_s + g * 16, pk);
         }
-        tmem_st16(t_s + g * 16, pk);
+        l += (ls0 + ls1) * __fdividef(0.015625f, r);  // back to exp2(s - m) units (2^-6 / r)
+      } else {
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float p0 = ex2(fmaf(s[g * 32 + 2 * j], c, -m_used));
+            const float p1 = ex2(fmaf(s[g * 32 + 2 * j + 1], c, -m_used));
+            ls0 += p0;
+            ls1 += p1;
+            pk[j] = pack_bf16(p0, p1);
+          }
+          tmem_st16(t_s + g * 16, pk);
+        }
+        l += ls0 + ls1;
       }
-      l += ls0 + ls1;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
@@ -378,7 +494,9 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       __nv_bfloat16* orow = p.o + (int64_t)batch * p.o_sb + (int64_t)head * p.o_sh +
                             (int64_t)q_row * p.o_ss;
       uint4* o4 = reinterpret_cast<uint4*>(orow);
-      const float inv = started ? 1.0f / l : 0.f;
+      // e4m3: O accumulated P * 2^shift * (v scale / v_ref) times the stored V values
+      const bool live = started && l > 0.f;
+      const float inv = live ? (kFp8 ? v_ref * 0.015625f / l : 1.0f / l) : 0.f;
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
         uint32_t v[32];
@@ -400,8 +518,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
       const int64_t stat = ((int64_t)batch * p.q_heads + head) * p.q_len + q_row;
-      if (p.lse) p.lse[stat] = started ? (m_used + log2f(l)) * kLn2 : p.mask_value;
-      if (p.maxl) p.maxl[stat] = started ? m_true * p.scale : p.mask_value;
+      if (p.lse) p.lse[stat] = live ? (m_used + log2f(l)) * kLn2 : p.mask_value;
+      if (p.maxl) p.maxl[stat] = live ? (kFp8 ? m_true * kLn2 : m_true * p.scale) : p.mask_value;
     }
   }
 
@@ -417,11 +535,18 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 // ------------------------------------------------------------------------------------------
 // host launcher
 // ------------------------------------------------------------------------------------------
-int launch_fwd(const SplashFwdArgs& a, cudaStream_t stream) {
+static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const float* k_scale,
+                             const float* v_scale, bool fp8, cudaStream_t stream) {
   int st;
-  if ((st = check_bf16_tensor(a.q)) || (st = check_bf16_tensor(a.k)) ||
-      (st = check_bf16_tensor(a.v)) || (st = check_bf16_tensor(a.o)))
-    return st;
+  if (fp8) {
+    if ((st = check_e4m3_tensor(a.q)) || (st = check_e4m3_tensor(a.k)) || (st = check_e4m3_tensor(a.v)))
+      return st;
+    if (q_scale == nullptr || k_scale == nullptr || v_scale == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;
+  } else {
+    if ((st = check_bf16_tensor(a.q)) || (st = check_bf16_tensor(a.k)) || (st = check_bf16_tensor(a.v)))
+      return st;
+  }
+  if ((st = check_bf16_tensor(a.o))) return st;
   const int64_t B = a.q.size[0], Hq = a.q.size[1], Sq = a.q.size[2], D = a.q.size[3];
   const int64_t Hkv = a.k.size[1], Skv = a.k.size[2];
   if (D != kHeadDim || a.k.size[3] != kHeadDim || a.v.size[3] != kHeadDim)
@@ -441,6 +566,7 @@ int launch_fwd(const SplashFwdArgs& a, cudaStream_t stream) {
   if (a.mask_fn.kind == SPLASH_MASK_CHUNKED && a.mask_fn.chunk <= 0)
     return SPLASH_ERR_INVALID_ARGUMENT;
   if (Hq > 65535 || B > 65535) return SPLASH_ERR_TOO_LARGE;
+  if (!(a.scale > 0.f) || !(a.scale < 1.0e30f)) return SPLASH_ERR_INVALID_ARGUMENT;
 
   CUtensorMap tm_q, tm_k, tm_v;
   if ((st = make_tile_tensor_map(&tm_q, a.q, kTile)) || (st = make_tile_tensor_map(&tm_k, a.k, kTile)) ||
@@ -475,17 +601,38 @@ int launch_fwd(const SplashFwdArgs& a, cudaStream_t stream) {
   p.scale_log2 = a.scale * kLog2e;
   p.mask_value = a.mask_value;
   p.err = a.error_record;
+  p.q_scale = q_scale;
+  p.k_scale = k_scale;
+  p.v_scale = v_scale;
+  p.n_kv_tiles = (int)(Skv / kTile);
 
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(splash_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kFwdSmemBytes) != cudaSuccess)
-      return SPLASH_ERR_CUDA;
-    attr_set = true;
-  }
   dim3 grid((unsigned)p.n_rows, (unsigned)Hq, (unsigned)B);
-  splash_fwd_kernel<<<grid, kFwdThreads, kFwdSmemBytes, stream>>>(tm_q, tm_k, tm_v, p);
+  if (fp8) {
+    constexpr int smem = fwd_smem_bytes(true);
+    if (cudaFuncSetAttribute(splash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
+        cudaSuccess)
+      return SPLASH_ERR_CUDA;
+    splash_fwd_kernel<true><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
+  } else {
+    constexpr int smem = fwd_smem_bytes(false);
+    static bool attr_set = false;
+    if (!attr_set) {
+      if (cudaFuncSetAttribute(splash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               smem) != cudaSuccess)
+        return SPLASH_ERR_CUDA;
+      attr_set = true;
+    }
+    splash_fwd_kernel<false><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
+  }
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
+}
+
+int launch_fwd(const SplashFwdArgs& a, cudaStream_t stream) {
+  return launch_fwd_common(a, nullptr, nullptr, nullptr, false, stream);
+}
+
+int launch_fwd_fp8(const SplashFwdFp8Args& a, cudaStream_t stream) {
+  return launch_fwd_common(a.base, a.q_scale, a.k_scale, a.v_scale, true, stream);
 }
 
 }  // namespace sb

@@ -9,6 +9,7 @@
 namespace sb {
 
 int launch_fwd(const SplashFwdArgs& a, cudaStream_t stream);
+int launch_fwd_fp8(const SplashFwdFp8Args& a, cudaStream_t stream);
 int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream);
 int launch_bwd_static_scratch(const SplashBwdArgs& a, cudaStream_t stream);
 size_t bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
@@ -45,24 +46,38 @@ int check_bf16_tensor(const SplashTensor& t) {
   return SPLASH_OK;
 }
 
-// Tensor map over (head_dim, seq, heads, batch) with a (64 x box_rows) box and 128-byte
-// swizzle: one box is one swizzle half of an MMA operand tile.
+int check_e4m3_tensor(const SplashTensor& t) {
+  if (t.data == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;
+  if (t.dtype != SPLASH_F8E4M3) return SPLASH_ERR_UNSUPPORTED;
+  if (t.stride[3] != 1) return SPLASH_ERR_INVALID_ARGUMENT;
+  for (int i = 0; i < 4; ++i)
+    if (t.size[i] <= 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  for (int i = 0; i < 3; ++i)
+    if (t.stride[i] % 16 != 0 || t.stride[i] < 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(t.data) & 15u) != 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  return SPLASH_OK;
+}
+
+// Tensor map over (head_dim, seq, heads, batch) with a (128 bytes x box_rows) box and 128-byte
+// swizzle.  bf16: 64 columns, one swizzle half of an MMA operand tile; e4m3: all 128 columns.
 int make_tile_tensor_map(CUtensorMap* out, const SplashTensor& t, int box_rows) {
   EncodeTiledFn enc = get_encode_fn();
   if (enc == nullptr) return SPLASH_ERR_NO_DEVICE;
+  const bool fp8 = t.dtype == SPLASH_F8E4M3;
+  const cuuint64_t esize = fp8 ? 1u : 2u;
   const cuuint64_t dims[4] = {(cuuint64_t)t.size[3], (cuuint64_t)t.size[2], (cuuint64_t)t.size[1],
                               (cuuint64_t)t.size[0]};
   // A size-1 dimension may carry any stride; give it a legal one.
   auto stride_bytes = [&](int i) -> cuuint64_t {
-    cuuint64_t s = (cuuint64_t)t.stride[i] * 2u;
+    cuuint64_t s = (cuuint64_t)t.stride[i] * esize;
     if (s == 0) s = 16;
     return s;
   };
   const cuuint64_t strides[3] = {stride_bytes(2), stride_bytes(1), stride_bytes(0)};
-  const cuuint32_t box[4] = {64u, (cuuint32_t)box_rows, 1u, 1u};
+  const cuuint32_t box[4] = {fp8 ? 128u : 64u, (cuuint32_t)box_rows, 1u, 1u};
   const cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
-  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.data, dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+  CUresult r = enc(out, fp8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, t.data,
+                   dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                    CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS && std::getenv("SPLASH_DEBUG") != nullptr)
     std::fprintf(stderr, "splash_b200: cuTensorMapEncodeTiled failed (%d): sizes %lld %lld %lld %lld strides %lld %lld %lld box rows %d\n",
@@ -78,6 +93,11 @@ extern "C" {
 int splash_fwd(const SplashFwdArgs* args, void* cuda_stream) {
   if (args == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;
   return sb::launch_fwd(*args, static_cast<cudaStream_t>(cuda_stream));
+}
+
+int splash_fwd_fp8(const SplashFwdFp8Args* args, void* cuda_stream) {
+  if (args == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;
+  return sb::launch_fwd_fp8(*args, static_cast<cudaStream_t>(cuda_stream));
 }
 
 size_t splash_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {
