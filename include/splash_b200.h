@@ -149,6 +149,7 @@ typedef struct SplashScheduleOut {
   int32_t* entries;   /* [n_entries * 4] */
   int32_t n_rows;
   int64_t n_entries;
+  int32_t* row_order; /* [n_rows]: rows by decreasing entry count (ties by row index) */
 } SplashScheduleOut;
 
 int splash_schedule_build(const int32_t* block_state, const int32_t* partial_id, int32_t n_q_blocks,
@@ -169,6 +170,10 @@ typedef struct SplashDeviceSchedule {
   const int32_t* row_end;            /* device, [batch, n_rows]: end of each row's entries; NULL:
                                         row r ends at row_ptr[r + 1] */
   int64_t entries_per_batch;         /* batch row b reads entries + b * entries_per_batch * 4 */
+  /* Launch order of the rows, longest first, so that the last CTAs of a grid are the short ones
+   * (SplashScheduleOut.row_order uploaded as is).  NULL: the kernels fall back to an order that
+   * suits causal masks (forward / dq: last row first; dkv: first row first). */
+  const int32_t* row_order;          /* device, [n_rows] or NULL */
 } SplashDeviceSchedule;
 
 /* ------------------------------------------------------------------------------------------
@@ -209,6 +214,15 @@ typedef struct SplashFwdArgs {
   float scale;                      /* multiplies q k^T in fp32 */
   float mask_value;                 /* written to logsumexp / max_logits of rows with no work */
   uint32_t* error_record;           /* device, 4 words, zeroed by the caller */
+  /* Attention sinks (splash_attention_kernel.py:375-395, base.py:96-104): one extra logit per q
+   * head that joins the softmax of every row of that head without a value: the running maximum
+   * starts at it and l at 1.  Device fp32 [q_heads], in the units of scale * q k^T; NULL: none. */
+  const float* sinks;
+  /* Fixed maximum (`max_logit_const` / `max_logit_value`, splash_attention_kernel.py:363-369,
+   * :440-470): exp(logit - value) is used for every tile, no running maximum is computed and
+   * max_logits returns the value.  Device fp32 [q_heads]; NULL: running maximum.  Logits far
+   * above the value overflow, as in the reference. */
+  const float* max_logit_value;
 } SplashFwdArgs;
 
 int splash_fwd(const SplashFwdArgs* args, void* cuda_stream);

@@ -31,8 +31,8 @@ import torch
 DEFAULT_MASK_VALUE = -0.7 * float(np.finfo(np.float32).max)
 
 
-def _one_head_fwd(q, k, v, mask, seg_q, seg_kv, mask_value, soft_cap, scale):
-  """base.py:74-112 for one head: q [S,D], k [T,D], v [T,Dv], mask bool [S,T]."""
+def _one_head_fwd(q, k, v, mask, seg_q, seg_kv, mask_value, soft_cap, scale, sink=None):
+  """base.py:74-112 for one head: q [S,D], k [T,D], v [T,Dv], mask bool [S,T]; sink scalar."""
   logits = (q.float() @ k.float().T) * scale  # base.py:85
   if seg_q is not None:
     mask = mask & (seg_q[:, None] == seg_kv[None, :])  # base.py:87-90
@@ -40,16 +40,20 @@ def _one_head_fwd(q, k, v, mask, seg_q, seg_kv, mask_value, soft_cap, scale):
     logits = torch.tanh(logits / soft_cap) * soft_cap  # base.py:92-94
   logits = torch.where(mask, logits, torch.tensor(mask_value, dtype=torch.float32))  # :99
   m = logits.max(dim=-1).values  # :100
+  if sink is not None:
+    m = torch.maximum(m, sink.float())  # :101-102
   s = torch.exp(logits - m[:, None])  # :103
   l = s.sum(dim=-1)  # :104
+  if sink is not None:
+    l = l + torch.exp(sink.float() - m)  # :104
   p = s / l[:, None]  # :105
   o = p @ v.float()  # :107
   return o, m + torch.log(l), m  # :110
 
 
 def attention_reference(q, k, v, mask, segment_ids=None, *, scale=1.0, mask_value=DEFAULT_MASK_VALUE,
-                        attn_logits_soft_cap=None):
-  """fp32 forward.  q [Hq,S,D], k/v [Hkv,T,D] (or [T,D] for MQA), mask bool [S,T].
+                        attn_logits_soft_cap=None, sinks=None):
+  """fp32 forward.  q [Hq,S,D], k/v [Hkv,T,D] (or [T,D] for MQA), mask bool [S,T], sinks [Hq].
 
   Returns ``(o [Hq,S,Dv] fp32, logsumexp [Hq,S], max_logits [Hq,S])``.
   """
@@ -65,7 +69,7 @@ def attention_reference(q, k, v, mask, segment_ids=None, *, scale=1.0, mask_valu
   outs, lses, maxes = [], [], []
   for h in range(hq):
     o, lse, m = _one_head_fwd(q[h], k[h // group], v[h // group], mask, seg_q, seg_kv, mask_value,
-                              attn_logits_soft_cap, scale)
+                              attn_logits_soft_cap, scale, None if sinks is None else sinks[h])
     outs.append(o)
     lses.append(lse)
     maxes.append(m)
@@ -97,10 +101,20 @@ def _one_head_bwd(do, q, k, v, mask, seg_q, seg_kv, o, lse, mask_value, soft_cap
   return dq, dk, dv
 
 
+def sinks_vjp(do, o, logsumexp, sinks):
+  """base.py:166-172: dsinks[h] = sum over rows and columns of -exp(sink - lse) * o * do."""
+  w = -torch.exp(sinks.float()[:, None] - logsumexp.float())  # [Hq, S]
+  return (w[..., None] * o.float() * do.float()).sum(dim=(-1, -2))
+
+
 def attention_reference_vjp(do, q, k, v, mask, segment_ids, o, logsumexp, *, scale=1.0,
                             mask_value=DEFAULT_MASK_VALUE, attn_logits_soft_cap=None,
                             backward_impl="flash"):
-  """fp32 backward.  Returns ``(dq [Hq,S,D], dk [Hkv,T,D], dv [Hkv,T,Dv])`` in fp32."""
+  """fp32 backward.  Returns ``(dq [Hq,S,D], dk [Hkv,T,D], dv [Hkv,T,Dv])`` in fp32.
+
+  Sinks change nothing here beyond the logsumexp passed in (base.py:145 uses it as is); their own
+  gradient is :func:`sinks_vjp`.
+  """
   mask = torch.as_tensor(np.asarray(mask), dtype=torch.bool)
   mqa = k.dim() == 2
   if mqa:

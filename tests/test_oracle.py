@@ -90,3 +90,32 @@ def test_masked_rows_use_the_finite_mask_value():
   o, lse, mx = attention_ref.attention_reference(q, k, v, mask)
   torch.testing.assert_close(o[0, 0], v[0].mean(0))
   assert mx[0, 0].item() == pytest.approx(attention_ref.DEFAULT_MASK_VALUE)
+
+
+def test_sinks_forward_and_gradient():
+  """Sinks (base.py:96-104, :166-172): float64 definition with one extra value-less key per head,
+  and autograd of the oracle's own forward for dq / dk / dv / dsinks."""
+  g = torch.Generator().manual_seed(11)
+  hq, hkv, s, d = 4, 2, 24, 8
+  q = torch.randn(hq, s, d, generator=g, requires_grad=True)
+  k = torch.randn(hkv, s, d, generator=g, requires_grad=True)
+  v = torch.randn(hkv, s, d, generator=g, requires_grad=True)
+  sinks = (torch.randn(hq, generator=g) * 2).requires_grad_(True)
+  do = torch.randn(hq, s, d, generator=g)
+  mask = mask_lib.make_causal_mask((s, s))
+  o, lse, mx = attention_ref.attention_reference(q, k, v, mask, scale=0.4, sinks=sinks)
+  # definition: softmax over the live keys plus the sink, whose value is zero
+  for h in range(hq):
+    logits = (q[h].detach().double() @ k[h // 2].detach().double().T) * 0.4
+    logits = torch.where(torch.from_numpy(mask), logits, torch.tensor(-math.inf, dtype=torch.float64))
+    full = torch.cat([logits, sinks[h].detach().double().expand(s, 1)], dim=1)
+    p = torch.softmax(full, dim=-1)[:, :-1]
+    np.testing.assert_allclose(o[h].detach().numpy(), (p @ v[h // 2].detach().double()).numpy(), rtol=2e-5, atol=2e-6)
+    np.testing.assert_allclose(lse[h].detach().numpy(), torch.logsumexp(full, dim=-1).numpy(), rtol=2e-6, atol=2e-6)
+    assert torch.all(mx[h] >= sinks[h] - 1e-6)
+  o.backward(do)
+  dq, dk, dv = attention_ref.attention_reference_vjp(do, q.detach(), k.detach(), v.detach(), mask, None,
+                                                     o.detach(), lse.detach(), scale=0.4)
+  dsinks = attention_ref.sinks_vjp(do, o.detach(), lse.detach(), sinks.detach())
+  for got, ref in ((dq, q.grad), (dk, k.grad), (dv, v.grad), (dsinks, sinks.grad)):
+    np.testing.assert_allclose(got.numpy(), ref.numpy(), rtol=2e-4, atol=2e-5)

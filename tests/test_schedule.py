@@ -18,7 +18,11 @@ def _build(state, pid, bq, bkv, kind):
                                           bq, bkv, kind, C.byref(out)), "schedule")
   rp = np.ctypeslib.as_array(out.row_ptr, shape=(out.n_rows + 1,)).copy()
   en = np.ctypeslib.as_array(out.entries, shape=(max(out.n_entries, 1), 4)).copy()[:out.n_entries]
+  order = np.ctypeslib.as_array(out.row_order, shape=(out.n_rows,)).copy()
   lib.splash_schedule_free(C.byref(out))
+  # launch order: a permutation of the rows, longest first, ties by row index
+  counts = np.diff(rp)
+  np.testing.assert_array_equal(order, np.argsort(-counts, kind="stable"))
   return rp, en
 
 

@@ -302,8 +302,6 @@ def test_unsupported_and_invalid_arguments():
   kernel = splash.make_splash_mha(mask, q_seq_shards=1)
   q = torch.zeros(2, s, D, dtype=torch.bfloat16, device=dev)
   with pytest.raises(NotImplementedError):
-    kernel(q, q, q, sinks=torch.zeros(2, device=dev))
-  with pytest.raises(NotImplementedError):
     kernel(q.float(), q.float(), q.float())
   with pytest.raises(NotImplementedError):
     kernel(q[..., :64], q[..., :64], q[..., :64])

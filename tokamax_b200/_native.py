@@ -96,6 +96,7 @@ class SplashScheduleOut(C.Structure):
       ("entries", C.POINTER(C.c_int32)),
       ("n_rows", C.c_int32),
       ("n_entries", C.c_int64),
+      ("row_order", C.POINTER(C.c_int32)),
   ]
 
 
@@ -110,6 +111,7 @@ class SplashDeviceSchedule(C.Structure):
       ("n_entries", C.c_int64),
       ("row_end", C.c_void_p),
       ("entries_per_batch", C.c_int64),
+      ("row_order", C.c_void_p),
   ]
 
 
@@ -126,6 +128,8 @@ class SplashFwdArgs(C.Structure):
       ("scale", C.c_float),
       ("mask_value", C.c_float),
       ("error_record", C.c_void_p),
+      ("sinks", C.c_void_p),
+      ("max_logit_value", C.c_void_p),
   ]
 
 

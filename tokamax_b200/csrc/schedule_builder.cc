@@ -1,8 +1,10 @@
 // Expands a block-level mask classification (what MaskInfo encodes) into the per-CTA work
 // lists the 128x128-tile kernels walk.  Host only, no CUDA.
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <new>
+#include <numeric>
 #include <vector>
 
 #include "../../include/splash_b200.h"
@@ -94,11 +96,17 @@ int splash_schedule_build(const int32_t* block_state, const int32_t* partial_id,
   out->n_entries = (int64_t)entries.size();
   out->row_ptr = static_cast<int32_t*>(std::malloc(row_ptr.size() * sizeof(int32_t)));
   out->entries = static_cast<int32_t*>(std::malloc((entries.size() + 1) * sizeof(Entry)));
-  if (out->row_ptr == nullptr || out->entries == nullptr) {
+  out->row_order = static_cast<int32_t*>(std::malloc((size_t)out->n_rows * sizeof(int32_t)));
+  if (out->row_ptr == nullptr || out->entries == nullptr || out->row_order == nullptr) {
     splash_schedule_free(out);
     return SPLASH_ERR_OUT_OF_MEMORY;
   }
   std::memcpy(out->row_ptr, row_ptr.data(), row_ptr.size() * sizeof(int32_t));
+  // Longest rows first: a grid launched in this order ends on its shortest CTAs.
+  std::iota(out->row_order, out->row_order + out->n_rows, 0);
+  std::stable_sort(out->row_order, out->row_order + out->n_rows, [&](int32_t a, int32_t b) {
+    return row_ptr[a + 1] - row_ptr[a] > row_ptr[b + 1] - row_ptr[b];
+  });
   if (!entries.empty()) std::memcpy(out->entries, entries.data(), entries.size() * sizeof(Entry));
   return SPLASH_OK;
 }
@@ -107,6 +115,7 @@ void splash_schedule_free(SplashScheduleOut* out) {
   if (out == nullptr) return;
   std::free(out->row_ptr);
   std::free(out->entries);
+  std::free(out->row_order);
   std::memset(out, 0, sizeof(*out));
 }
 

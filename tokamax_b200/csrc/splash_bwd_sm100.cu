@@ -91,12 +91,14 @@ struct BwdParams {
   const int32_t* q_sequence;
   const int32_t* row_ptr;
   const int4* entries;
+  const int32_t* row_order;    // launch order of the rows (longest first) or nullptr
   const int32_t* row_end;      // per batch row [batch, n_rows] or nullptr
   int64_t entries_per_batch;   // 0: one list shared by all batch rows
   const int8_t* pmb;
   int pm_bq, pm_bkv;
   SplashMaskFn fn;
   int q_len, kv_len, q_heads, kv_heads, n_rows;
+  int n_groups, chunk_groups;  // (batch, head) pairs of the grid; how many share a launch chunk
   float scale, scale_log2;
   uint32_t* err;
 };
@@ -157,9 +159,10 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int q_tile = p.n_rows - 1 - (int)blockIdx.x;
-  const int head = blockIdx.y;
-  const int batch = blockIdx.z;
+  const CtaWork work = cta_work(p.row_order, p.n_rows, p.n_groups, p.chunk_groups, true);
+  const int q_tile = work.row;
+  const int head = work.group % p.q_heads;
+  const int batch = work.group / p.q_heads;
   const int kv_head = head / (p.q_heads / p.kv_heads);
   const int ebeg = p.row_ptr[q_tile];
   const int eend = p.row_end ? p.row_end[(int64_t)batch * p.n_rows + q_tile] : p.row_ptr[q_tile + 1];
@@ -481,9 +484,10 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int kv_tile = blockIdx.x;  // for causal masks low kv tiles carry the most work
-  const int kv_head = blockIdx.y;
-  const int batch = blockIdx.z;
+  const CtaWork work = cta_work(p.row_order, p.n_rows, p.n_groups, p.chunk_groups, false);
+  const int kv_tile = work.row;
+  const int kv_head = work.group % p.kv_heads;
+  const int batch = work.group / p.kv_heads;
   const int group = p.q_heads / p.kv_heads;
   const int ebeg = p.row_ptr[kv_tile];
   const int eend = p.row_end ? p.row_end[(int64_t)batch * p.n_rows + kv_tile] : p.row_ptr[kv_tile + 1];
@@ -848,7 +852,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     return SPLASH_ERR_INVALID_ARGUMENT;
   if (a.mask_fn.kind == SPLASH_MASK_CHUNKED && a.mask_fn.chunk <= 0)
     return SPLASH_ERR_INVALID_ARGUMENT;
-  if (Hq > 65535 || B > 65535) return SPLASH_ERR_TOO_LARGE;
+  if (Hq > 65535 || B > 65535 || Sq / kTile > 65535 || Skv / kTile > 65535) return SPLASH_ERR_TOO_LARGE;
   if (!(a.scale > 0.f) || !(a.scale < 1.0e30f)) return SPLASH_ERR_INVALID_ARGUMENT;
 
   CUtensorMap tm_q, tm_do, tm_k, tm_v;
@@ -914,13 +918,18 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.out1_sb = p.out1_sh = p.out1_ss = 0;
   p.row_ptr = a.sched_dq.row_ptr;
   p.entries = reinterpret_cast<const int4*>(a.sched_dq.entries);
+  p.row_order = a.sched_dq.row_order;
   p.row_end = a.sched_dq.row_end;
   p.entries_per_batch = a.sched_dq.entries_per_batch;
   p.pmb = a.sched_dq.partial_mask_blocks;
   p.pm_bq = a.sched_dq.block_q > 0 ? a.sched_dq.block_q : kTile;
   p.pm_bkv = a.sched_dq.block_kv > 0 ? a.sched_dq.block_kv : kTile;
   p.n_rows = a.sched_dq.n_rows;
-  if (mask & 2u) splash_dq_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hq, (unsigned)B), kBwdThreads, kDqSmemBytes,
+  // dq: the q heads of one kv head stream the same K / V
+  p.n_groups = (int)(Hq * B);
+  p.chunk_groups = chunk_groups_for(2 * Skv * kHeadDim * 2 / (Hq / Hkv), p.n_groups, Hq / Hkv);
+  if ((int64_t)p.n_rows * p.n_groups > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
+  if (mask & 2u) splash_dq_kernel<<<dim3((unsigned)(p.n_rows * p.n_groups), 1u, 1u), kBwdThreads, kDqSmemBytes,
                      stream>>>(tm_q, tm_do, tm_k, tm_v, p);
   if (cudaGetLastError() != cudaSuccess) return SPLASH_ERR_CUDA;
 
@@ -935,13 +944,18 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.out1_ss = a.dv.stride[2];
   p.row_ptr = a.sched_dkv.row_ptr;
   p.entries = reinterpret_cast<const int4*>(a.sched_dkv.entries);
+  p.row_order = a.sched_dkv.row_order;
   p.row_end = a.sched_dkv.row_end;
   p.entries_per_batch = a.sched_dkv.entries_per_batch;
   p.pmb = a.sched_dkv.partial_mask_blocks;
   p.pm_bq = a.sched_dkv.block_q > 0 ? a.sched_dkv.block_q : kTile;
   p.pm_bkv = a.sched_dkv.block_kv > 0 ? a.sched_dkv.block_kv : kTile;
   p.n_rows = a.sched_dkv.n_rows;
-  if (mask & 4u) splash_dkv_kernel<<<dim3((unsigned)p.n_rows, (unsigned)Hkv, (unsigned)B), kDkvThreads, kDkvSmemBytes,
+  // dkv: the kv tiles of one (batch, kv head) stream the same Q / dO of its q-head group
+  p.n_groups = (int)(Hkv * B);
+  p.chunk_groups = chunk_groups_for(2 * (Hq / Hkv) * Sq * kHeadDim * 2, p.n_groups, 1);
+  if ((int64_t)p.n_rows * p.n_groups > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
+  if (mask & 4u) splash_dkv_kernel<<<dim3((unsigned)(p.n_rows * p.n_groups), 1u, 1u), kDkvThreads, kDkvSmemBytes,
                       stream>>>(tm_q, tm_do, tm_k, tm_v, p);
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
 }

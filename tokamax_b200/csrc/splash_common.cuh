@@ -43,6 +43,37 @@ __device__ __forceinline__ RowInterval mask_fn_interval(const SplashMaskFn& fn, 
 // Same mask function seen from a key: the queries i that keep key j form an interval too, but
 // the dkv kernel simply evaluates lo(i) <= j <= hi(i) per element, so no inverse is needed.
 
+// Which (row, group) a CTA of a 1-D grid of n_rows * n_groups blocks works on.  A group is a
+// (batch, head) pair.  Groups are taken chunk_groups at a time; inside a chunk the launch order
+// runs through the rows longest first (row_order, or `fallback_reversed` index order), all groups
+// of the chunk side by side.  A chunk small enough for its streamed operands to stay in L2 keeps
+// DRAM traffic near the compulsory minimum, while the grid still drains on short CTAs.
+struct CtaWork {
+  int row, group;
+};
+__device__ __forceinline__ CtaWork cta_work(const int32_t* row_order, int n_rows, int n_groups,
+                                            int chunk_groups, bool fallback_reversed) {
+  const unsigned per_chunk = (unsigned)n_rows * (unsigned)chunk_groups;
+  const unsigned chunk = blockIdx.x / per_chunk;
+  const unsigned rem = blockIdx.x - chunk * per_chunk;
+  const unsigned first = chunk * (unsigned)chunk_groups;
+  const unsigned here = min((unsigned)chunk_groups, (unsigned)n_groups - first);
+  const unsigned pos = rem / here;
+  CtaWork w;
+  w.group = (int)(first + (rem - pos * here));
+  w.row = row_order ? row_order[pos] : (fallback_reversed ? n_rows - 1 - (int)pos : (int)pos);
+  return w;
+}
+// Groups per chunk so that `bytes_per_group` of streamed operands of one chunk fill about half
+// of a 126 MB L2, in whole multiples of `align` (heads sharing a kv head stay together).
+inline int chunk_groups_for(int64_t bytes_per_group, int64_t n_groups, int64_t align) {
+  int64_t g = (int64_t)(64ll << 20) / (bytes_per_group > 0 ? bytes_per_group : 1);
+  g = g / align * align;
+  if (g < align) g = align;
+  if (g > n_groups) g = n_groups;
+  return (int)g;
+}
+
 // Host-side helpers (defined in splash_host.cu).
 int make_tile_tensor_map(CUtensorMap* out, const SplashTensor& t, int box_rows);
 int check_bf16_tensor(const SplashTensor& t);

@@ -59,12 +59,14 @@ struct FwdParams {
   const int32_t* q_sequence;
   const int32_t* row_ptr;
   const int4* entries;
+  const int32_t* row_order;    // launch order of the rows (longest first) or nullptr
   const int32_t* row_end;      // per batch row [batch, n_rows] or nullptr
   int64_t entries_per_batch;   // 0: one list shared by all batch rows
   const int8_t* pmb;
   int pm_bq, pm_bkv;
   SplashMaskFn fn;
   int q_len, kv_len, q_heads, kv_heads, n_q_tiles, n_rows;
+  int n_groups, chunk_groups;  // (batch, q head) pairs; how many of them share a launch chunk
   float scale, scale_log2, mask_value;
   uint32_t* err;
   // e4m3 variant only: one scale per (batch, head, 128-token tile)
@@ -72,6 +74,8 @@ struct FwdParams {
   const float* k_scale;
   const float* v_scale;
   int n_kv_tiles;
+  const float* sinks;            // [q_heads] or nullptr
+  const float* max_logit_value;  // [q_heads] or nullptr
 };
 
 struct FwdBarriers {
@@ -116,9 +120,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int row = p.n_rows - 1 - (int)blockIdx.x;  // long causal rows first
-  const int head = blockIdx.y;
-  const int batch = blockIdx.z;
+  const CtaWork work = cta_work(p.row_order, p.n_rows, p.n_groups, p.chunk_groups, true);
+  const int row = work.row;
+  const int head = work.group % p.q_heads;
+  const int batch = work.group / p.q_heads;
   const int kv_head = head / (p.q_heads / p.kv_heads);
   const int ebeg = p.row_ptr[row];
   const int eend = p.row_end ? p.row_end[(int64_t)batch * p.n_rows + row] : p.row_ptr[row + 1];
@@ -327,6 +332,18 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     float m_used = -INFINITY;  // scaled (log2) units
     float m_true = kMaskedLogit;
     float l = 0.f;
+    // A sink starts the row as one extra key of weight 1 at the sink logit; a fixed maximum
+    // replaces the running one for the whole row (and a sink is then weighed against it).
+    const bool fixed_max = p.max_logit_value != nullptr;
+    float sink2 = -INFINITY;  // sink logit in log2 units
+    if (p.sinks != nullptr) sink2 = p.sinks[head] * kLog2e;
+    if (fixed_max) {
+      m_used = p.max_logit_value[head] * kLog2e;
+      if (p.sinks != nullptr) l = ex2(sink2 - m_used);
+    } else if (p.sinks != nullptr) {
+      m_used = sink2;
+      l = 1.f;
+    }
     uint32_t cnt = 0;
     bool started = false;
     bool ok = true;
@@ -420,7 +437,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = fmaxf(mx * c, kLogitFloor);
       m_true = fmaxf(m_true, kFp8 ? m_new : mx);  // e4m3: log2 units (the scale varies by tile)
-      const bool need = m_new > m_used + kThreshold;
+      const bool need = !fixed_max && m_new > m_used + kThreshold;
       if (__any_sync(0xffffffffu, need)) {
         const float m_next = fmaxf(m_used, m_new);
         const float alpha = ex2(m_used - m_next);
@@ -495,7 +512,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
                             (int64_t)q_row * p.o_ss;
       uint4* o4 = reinterpret_cast<uint4*>(orow);
       // e4m3: O accumulated P * 2^shift * (v scale / v_ref) times the stored V values
-      const bool live = started && l > 0.f;
+      const bool live = l > 0.f;  // a row that met a live key, or has a sink
       const float inv = live ? (kFp8 ? v_ref * 0.015625f / l : 1.0f / l) : 0.f;
 #pragma unroll
       for (int g = 0; g < 4; ++g) {
@@ -519,7 +536,12 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
       const int64_t stat = ((int64_t)batch * p.q_heads + head) * p.q_len + q_row;
       if (p.lse) p.lse[stat] = live ? (m_used + log2f(l)) * kLn2 : p.mask_value;
-      if (p.maxl) p.maxl[stat] = live ? (kFp8 ? m_true * kLn2 : m_true * p.scale) : p.mask_value;
+      if (p.maxl) {
+        float mv = kFp8 ? m_true * kLn2 : m_true * p.scale;
+        if (p.sinks != nullptr) mv = fmaxf(mv, sink2 * kLn2);
+        if (fixed_max) mv = m_used * kLn2;
+        p.maxl[stat] = live ? mv : p.mask_value;
+      }
     }
   }
 
@@ -565,7 +587,7 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   if (a.sched.n_rows != (n_q_tiles + 1) / 2) return SPLASH_ERR_INVALID_ARGUMENT;
   if (a.mask_fn.kind == SPLASH_MASK_CHUNKED && a.mask_fn.chunk <= 0)
     return SPLASH_ERR_INVALID_ARGUMENT;
-  if (Hq > 65535 || B > 65535) return SPLASH_ERR_TOO_LARGE;
+  if (Hq > 65535 || B > 65535 || n_q_tiles > 2 * 65535) return SPLASH_ERR_TOO_LARGE;
   if (!(a.scale > 0.f) || !(a.scale < 1.0e30f)) return SPLASH_ERR_INVALID_ARGUMENT;
 
   CUtensorMap tm_q, tm_k, tm_v;
@@ -585,6 +607,7 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   p.q_sequence = a.q_sequence;
   p.row_ptr = a.sched.row_ptr;
   p.entries = reinterpret_cast<const int4*>(a.sched.entries);
+  p.row_order = a.sched.row_order;
   p.row_end = a.sched.row_end;
   p.entries_per_batch = a.sched.entries_per_batch;
   p.pmb = a.sched.partial_mask_blocks;
@@ -605,8 +628,14 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   p.k_scale = k_scale;
   p.v_scale = v_scale;
   p.n_kv_tiles = (int)(Skv / kTile);
+  p.sinks = a.sinks;
+  p.max_logit_value = a.max_logit_value;
 
-  dim3 grid((unsigned)p.n_rows, (unsigned)Hq, (unsigned)B);
+  // The q heads of one kv head stream the same K / V (2 tensors of Skv x 128 elements).
+  p.n_groups = (int)(Hq * B);
+  p.chunk_groups = chunk_groups_for(2 * Skv * kHeadDim * (fp8 ? 1 : 2) / (Hq / Hkv), p.n_groups, Hq / Hkv);
+  if ((int64_t)p.n_rows * p.n_groups > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
+  dim3 grid((unsigned)(p.n_rows * p.n_groups), 1u, 1u);
   if (fp8) {
     constexpr int smem = fwd_smem_bytes(true);
     if (cudaFuncSetAttribute(splash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=

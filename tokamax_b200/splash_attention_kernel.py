@@ -143,9 +143,10 @@ def _build_schedule(state: np.ndarray, pid: np.ndarray, block_q: int, block_kv: 
     entries = np.ctypeslib.as_array(out.entries, shape=(n * 4,)).copy()
     if out.n_entries == 0:
       entries[:] = 0
+    row_order = np.ctypeslib.as_array(out.row_order, shape=(out.n_rows,)).copy()
   finally:
     lib.splash_schedule_free(C.byref(out))
-  return row_ptr, entries
+  return row_ptr, entries, row_order
 
 
 class _DeviceTables:
@@ -182,13 +183,15 @@ class _DeviceTables:
       self.q_sequence = torch.from_numpy(np.ascontiguousarray(q_seq, dtype=np.int32)).to(device)
 
   def _upload(self, state, pid, bq, bkv, kind, pmb, device) -> _native.SplashDeviceSchedule:
-    row_ptr, entries = _build_schedule(state, pid, bq, bkv, kind)
+    row_ptr, entries, row_order = _build_schedule(state, pid, bq, bkv, kind)
     rp = torch.from_numpy(row_ptr).to(device)
     en = torch.from_numpy(entries).to(device)
-    self.keep += [rp, en]
+    ro = torch.from_numpy(row_order).to(device)
+    self.keep += [rp, en, ro]
     d = _native.SplashDeviceSchedule()
     d.row_ptr = rp.data_ptr()
     d.entries = en.data_ptr()
+    d.row_order = ro.data_ptr()
     d.n_rows = len(row_ptr) - 1
     d.n_entries = int(row_ptr[-1])
     d.block_q, d.block_kv = bq, bkv
@@ -250,7 +253,7 @@ class _SplashFunction(torch.autograd.Function):
   """forward = splash_fwd, backward = splash_bwd (reference custom_vjp: kernel.py:998-1108)."""
 
   @staticmethod
-  def forward(ctx, q, k, v, q_seg, kv_seg, kernel, scale):
+  def forward(ctx, q, k, v, q_seg, kv_seg, kernel, scale, sinks, max_logit):
     _require_cuda(q)
     tables = kernel._tables(q.device)  # pylint: disable=protected-access
     q, k, v = _usable(q), _usable(k), _usable(v)
@@ -274,10 +277,14 @@ class _SplashFunction(torch.autograd.Function):
     args.scale = scale
     args.mask_value = max(kernel.mask_value, -3.0e38)
     args.error_record = tables.error_record.data_ptr()
+    sinks_f32 = None if sinks is None else sinks.detach().to(torch.float32).contiguous()
+    args.sinks = None if sinks_f32 is None else sinks_f32.data_ptr()
+    args.max_logit_value = None if max_logit is None else max_logit.data_ptr()
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
       _native.check(_native.lib().splash_fwd(C.byref(args), C.c_void_p(stream)), "splash_fwd")
-    ctx.save_for_backward(q, k, v, o, lse, q_seg, kv_seg)
+    ctx.save_for_backward(q, k, v, o, lse, q_seg, kv_seg, sinks_f32)
+    ctx.sinks_dtype = None if sinks is None else sinks.dtype
     ctx.kernel = kernel
     ctx.scale = scale
     ctx.mark_non_differentiable(lse, max_logits)
@@ -285,7 +292,7 @@ class _SplashFunction(torch.autograd.Function):
 
   @staticmethod
   def backward(ctx, d_o, _dlse, _dmax):
-    q, k, v, o, lse, q_seg, kv_seg = ctx.saved_tensors
+    q, k, v, o, lse, q_seg, kv_seg, sinks = ctx.saved_tensors
     kernel = ctx.kernel
     tables = kernel._tables(q.device)  # pylint: disable=protected-access
     d_o = _usable(d_o)
@@ -315,7 +322,14 @@ class _SplashFunction(torch.autograd.Function):
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
       _native.check(lib.splash_bwd(C.byref(args), C.c_void_p(stream)), "splash_bwd")
-    return dq, dk, dv, None, None, None, None
+    dsinks = None
+    if sinks is not None:
+      # reference kernel.py:1928-1935: dsinks[h] = -sum_rows exp(sink - lse) * sum_d(o * do); the
+      # row sums di are the first array of the backward workspace.
+      n = q.shape[0] * q.shape[1] * q.shape[2]
+      di = workspace[:4 * n].view(torch.float32).view(q.shape[0], q.shape[1], q.shape[2])
+      dsinks = -(torch.exp(sinks[None, :, None] - lse) * di).sum(dim=(0, 2)).to(ctx.sinks_dtype)
+    return dq, dk, dv, None, None, None, None, dsinks, None
 
 
 class SplashAttentionKernel:
@@ -364,10 +378,8 @@ class SplashAttentionKernel:
 
   def _reject_unsupported(self, q, k, sinks, max_logit_value):
     cfg = self.config
-    if sinks is not None:
-      raise NotImplementedError("attention sinks are not built on B200 yet")
-    if max_logit_value is not None or cfg.max_logit_const is not None:
-      raise NotImplementedError("max_logit_value / max_logit_const are not built on B200 yet")
+    if cfg.max_logit_const is not None and max_logit_value is not None:
+      raise ValueError(f"Only one of max_logit_const={cfg.max_logit_const} and {max_logit_value=} can be set.")
     if cfg.attn_logits_soft_cap is not None:
       raise NotImplementedError("attn_logits_soft_cap is not built on B200 yet")
     if any(l != QKVLayout.HEAD_DIM_MINOR for l in (cfg.q_layout, cfg.k_layout, cfg.v_layout)):
@@ -410,7 +422,20 @@ class SplashAttentionKernel:
       if q_seg.shape != (q.shape[0], q_len) or kv_seg.shape != (q.shape[0], kv_len):
         raise ValueError(f"segment id shapes {tuple(q_seg.shape)}, {tuple(kv_seg.shape)} do not match q/kv")
       q_seg, kv_seg = q_seg.contiguous(), kv_seg.contiguous()
-    o, lse, max_logits = _SplashFunction.apply(q, k, v, q_seg, kv_seg, self, float(logits_scale))
+    hq = q.shape[1]
+    if sinks is not None:
+      sinks = torch.as_tensor(sinks, device=q.device)
+      if sinks.shape != (hq,):
+        raise ValueError(f"sinks.shape={tuple(sinks.shape)} != num_q_heads={hq}")
+    max_logit = None
+    if max_logit_value is not None or self.config.max_logit_const is not None:
+      value = max_logit_value if max_logit_value is not None else self.config.max_logit_const
+      value = torch.as_tensor(value, dtype=torch.float32, device=q.device)
+      if tuple(value.shape) not in ((), (1,), (hq,)):
+        raise ValueError(f"max_logit_value should have shape (), (1,) or ({hq},), got {tuple(value.shape)}")
+      max_logit = value.reshape(-1).expand(hq).contiguous()
+    o, lse, max_logits = _SplashFunction.apply(q, k, v, q_seg, kv_seg, self, float(logits_scale), sinks,
+                                               max_logit)
     if not batched:
       o, lse, max_logits = o[0], lse[0], max_logits[0]
     if save_residuals:
