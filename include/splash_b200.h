@@ -223,6 +223,9 @@ typedef struct SplashFwdArgs {
    * max_logits returns the value.  Device fp32 [q_heads]; NULL: running maximum.  Logits far
    * above the value overflow, as in the reference. */
   const float* max_logit_value;
+  /* attn_logits_soft_cap (splash_attention_kernel.py:202-296, base.py:92-94): logits become
+   * cap * tanh(scale * q k^T / cap) before masking.  0 = off.  bf16 inputs only. */
+  float soft_cap;
 } SplashFwdArgs;
 
 int splash_fwd(const SplashFwdArgs* args, void* cuda_stream);
@@ -268,6 +271,8 @@ typedef struct SplashBwdArgs {
   uint32_t launch_mask;             /* 0 = everything; else bit 0 di pass, bit 1 dq kernel, bit 2
                                        dkv kernel (for timing / profiling one kernel alone; the di
                                        pass must have run on this workspace before bits 1 or 2) */
+  float soft_cap;                   /* as in SplashFwdArgs; dS gains the factor 1 - tanh^2
+                                       (base.py:159-163).  0 = off */
 } SplashBwdArgs;
 
 size_t splash_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);

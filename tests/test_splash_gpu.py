@@ -309,9 +309,6 @@ def test_unsupported_and_invalid_arguments():
     kernel(q[:, :128], q, q)
   with pytest.raises(RuntimeError):
     kernel(q.cpu(), q.cpu(), q.cpu())
-  cfg = splash.SplashConfig(block_q=128, block_kv=128, attn_logits_soft_cap=30.0)
-  with pytest.raises(NotImplementedError):
-    splash.make_splash_mha(mask, config=cfg, q_seq_shards=1)(q, q, q)
   with pytest.raises(NotImplementedError):
     splash.make_splash_mha(mask_lib.CausalMask((64, 64)), q_seq_shards=1,
                            config=splash.SplashConfig(block_q=16, block_kv=16))(

@@ -130,6 +130,7 @@ class SplashFwdArgs(C.Structure):
       ("error_record", C.c_void_p),
       ("sinks", C.c_void_p),
       ("max_logit_value", C.c_void_p),
+      ("soft_cap", C.c_float),
   ]
 
 
@@ -159,6 +160,7 @@ class SplashBwdArgs(C.Structure):
       ("workspace_bytes", C.c_size_t),
       ("error_record", C.c_void_p),
       ("launch_mask", C.c_uint32),
+      ("soft_cap", C.c_float),
   ]
 
 

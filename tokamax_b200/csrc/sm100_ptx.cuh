@@ -320,6 +320,13 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// tanh to ~1e-6 absolute: (e - 1) / (e + 1) with e = 2^(2 log2(e) y).  tanh.approx.f32 (relative
+// error 2^-11) is too coarse for logits that must hold 1e-3 after being multiplied by a cap of
+// tens.  Saturates cleanly: e = inf -> 1, e = 0 -> -1.
+__device__ __forceinline__ float tanh_ex2(float y) {
+  const float e = ex2(y * 2.8853900817779268f);
+  return 1.0f - __fdividef(2.0f, e + 1.0f);
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

@@ -99,6 +99,8 @@ struct BwdParams {
   SplashMaskFn fn;
   int q_len, kv_len, q_heads, kv_heads, n_rows;
   int n_groups, chunk_groups;  // (batch, head) pairs of the grid; how many share a launch chunk
+  // soft-cap variants: logits = cap * tanh(scale * q k^T / cap); dS gains the factor 1 - tanh^2
+  float soft_cap, softcap_a;   // cap; scale / cap
   float scale, scale_log2;
   uint32_t* err;
 };
@@ -145,6 +147,7 @@ __device__ __forceinline__ void store_row_half(__nv_bfloat16* dst, const uint32_
 // dq kernel
 // ------------------------------------------------------------------------------------------
 // TMEM: S0 [0,128) | S1 [128,256) | dP [256,384) | dQ [384,512)
+template <bool kSoftCap>
 __global__ void __launch_bounds__(kBwdThreads, 1)
 splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -311,7 +314,7 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const float nlse2 = p.nlse2[stat];
     const float delta = p.delta[stat];
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    const float c = p.scale_log2;
+    const float c = kSoftCap ? p.soft_cap * kLog2e : p.scale_log2;
     bool ok = true;
 
     int4 ent_next = n_ent > 0 ? entries[ebeg] : make_int4(0, 0, 0, 0);
@@ -336,6 +339,10 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           pr[j] = __uint_as_float(v0[j]);
           pr[32 + j] = __uint_as_float(v1[j]);
         }
+      }
+      if constexpr (kSoftCap) {  // pr <- tanh(scale * s / cap), capped before it is masked
+#pragma unroll
+        for (int j = 0; j < 64; ++j) pr[j] = tanh_ex2(pr[j] * p.softcap_a);
       }
       if (st == 1) {
         if (p.fn.kind != SPLASH_MASK_TABLE) {
@@ -369,8 +376,18 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (sv.w != q_seg) pr[g * 4 + 3] = kMaskedLogit;
         }
       }
+      if constexpr (kSoftCap) {
+        // p * (1 - tanh^2): the chain factor of the cap rides on p (masked entries hold -1e30
+        // in place of tanh; the clamp keeps their factor finite, their p is 0)
 #pragma unroll
-      for (int j = 0; j < 64; ++j) pr[j] = ex2(fmaf(pr[j], c, nlse2));
+        for (int j = 0; j < 64; ++j) {
+          const float t = fmaxf(pr[j], -1.0f);
+          pr[j] = ex2(fmaf(pr[j], c, nlse2)) * fmaf(-t, t, 1.0f);
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 64; ++j) pr[j] = ex2(fmaf(pr[j], c, nlse2));
+      }
 
       ok = mbar_wait(&bars->dp_full, n & 1u, ab, 0x1410u);
       ok = __all_sync(0xffffffffu, ok);
@@ -468,6 +485,7 @@ struct DkvBarriers {
   uint32_t early_exit;
 };
 
+template <bool kSoftCap>
 __global__ void __launch_bounds__(kDkvThreads, 1)
 splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                   const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
@@ -655,7 +673,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     const uint32_t t_st = tmem + lane_addr + w * 64 + cq * 32;
     const uint32_t t_dpt = tmem + lane_addr + kTile + w * 64 + cq * 32;
-    const float c = p.scale_log2;
+    const float c = kSoftCap ? p.soft_cap * kLog2e : p.scale_log2;
     bool ok = true;
     int n = 0;
 
@@ -688,6 +706,10 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) pr[j] = __uint_as_float(v[j]);
+        }
+        if constexpr (kSoftCap) {  // pr <- tanh(scale * s / cap), capped before it is masked
+#pragma unroll
+          for (int j = 0; j < 32; ++j) pr[j] = tanh_ex2(pr[j] * p.softcap_a);
         }
         if (st == 1) {
           if (p.fn.kind != SPLASH_MASK_TABLE) {
@@ -735,12 +757,21 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
           for (int t = 0; t < 8; ++t) {
             const float4 nl = nl4[t];
+            float th[4];
+            if constexpr (kSoftCap) {
+#pragma unroll
+              for (int u = 0; u < 4; ++u) th[u] = fmaxf(pr[4 * t + u], -1.0f);
+            }
             pr[4 * t + 0] = ex2(fmaf(pr[4 * t + 0], c, nl.x));
             pr[4 * t + 1] = ex2(fmaf(pr[4 * t + 1], c, nl.y));
             pr[4 * t + 2] = ex2(fmaf(pr[4 * t + 2], c, nl.z));
             pr[4 * t + 3] = ex2(fmaf(pr[4 * t + 3], c, nl.w));
             pk[2 * t] = pack_bf16(pr[4 * t + 0], pr[4 * t + 1]);
             pk[2 * t + 1] = pack_bf16(pr[4 * t + 2], pr[4 * t + 3]);
+            if constexpr (kSoftCap) {  // dS = (p * (1 - tanh^2)) * (dP - di): fold the factor into p
+#pragma unroll
+              for (int u = 0; u < 4; ++u) pr[4 * t + u] *= fmaf(-th[u], th[u], 1.0f);
+            }
           }
           tmem_st16(t_st, pk);
           tmem_st_wait();
@@ -884,14 +915,18 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     if (cudaGetLastError() != cudaSuccess) return SPLASH_ERR_CUDA;
   }
 
-  static bool attr_set = false;
-  if (!attr_set) {
-    if (cudaFuncSetAttribute(splash_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kDqSmemBytes) != cudaSuccess ||
-        cudaFuncSetAttribute(splash_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             kDkvSmemBytes) != cudaSuccess)
+  const bool soft_cap = a.soft_cap != 0.f;
+  if (soft_cap && !(a.soft_cap > 0.f)) return SPLASH_ERR_INVALID_ARGUMENT;
+  auto* dq_kernel = soft_cap ? splash_dq_kernel<true> : splash_dq_kernel<false>;
+  auto* dkv_kernel = soft_cap ? splash_dkv_kernel<true> : splash_dkv_kernel<false>;
+  static bool attr_set[2] = {false, false};
+  if (!attr_set[soft_cap]) {
+    if (cudaFuncSetAttribute(dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmemBytes) !=
+            cudaSuccess ||
+        cudaFuncSetAttribute(dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmemBytes) !=
+            cudaSuccess)
       return SPLASH_ERR_CUDA;
-    attr_set = true;
+    attr_set[soft_cap] = true;
   }
 
   BwdParams p;
@@ -908,6 +943,8 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.scale = a.scale;
   p.scale_log2 = a.scale * kLog2e;
   p.err = a.error_record;
+  p.soft_cap = a.soft_cap;
+  p.softcap_a = soft_cap ? a.scale / a.soft_cap : 0.f;
 
   // dq
   p.out0 = static_cast<__nv_bfloat16*>(a.dq.data);
@@ -929,8 +966,9 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.n_groups = (int)(Hq * B);
   p.chunk_groups = chunk_groups_for(2 * Skv * kHeadDim * 2 / (Hq / Hkv), p.n_groups, Hq / Hkv);
   if ((int64_t)p.n_rows * p.n_groups > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
-  if (mask & 2u) splash_dq_kernel<<<dim3((unsigned)(p.n_rows * p.n_groups), 1u, 1u), kBwdThreads, kDqSmemBytes,
-                     stream>>>(tm_q, tm_do, tm_k, tm_v, p);
+  if (mask & 2u)
+    dq_kernel<<<dim3((unsigned)(p.n_rows * p.n_groups), 1u, 1u), kBwdThreads, kDqSmemBytes, stream>>>(
+        tm_q, tm_do, tm_k, tm_v, p);
   if (cudaGetLastError() != cudaSuccess) return SPLASH_ERR_CUDA;
 
   // dkv
@@ -955,8 +993,9 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.n_groups = (int)(Hkv * B);
   p.chunk_groups = chunk_groups_for(2 * (Hq / Hkv) * Sq * kHeadDim * 2, p.n_groups, 1);
   if ((int64_t)p.n_rows * p.n_groups > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
-  if (mask & 4u) splash_dkv_kernel<<<dim3((unsigned)(p.n_rows * p.n_groups), 1u, 1u), kDkvThreads, kDkvSmemBytes,
-                      stream>>>(tm_q, tm_do, tm_k, tm_v, p);
+  if (mask & 4u)
+    dkv_kernel<<<dim3((unsigned)(p.n_rows * p.n_groups), 1u, 1u), kDkvThreads, kDkvSmemBytes, stream>>>(
+        tm_q, tm_do, tm_k, tm_v, p);
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
 }
 

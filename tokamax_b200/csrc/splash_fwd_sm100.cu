@@ -76,6 +76,8 @@ struct FwdParams {
   int n_kv_tiles;
   const float* sinks;            // [q_heads] or nullptr
   const float* max_logit_value;  // [q_heads] or nullptr
+  // soft-cap variant: logits = cap * tanh(scale * q k^T / cap)
+  float soft_cap, softcap_a;     // cap; scale / cap
 };
 
 struct FwdBarriers {
@@ -106,7 +108,7 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
   return r;
 }
 
-template <bool kFp8>
+template <bool kFp8, bool kSoftCap>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
@@ -312,7 +314,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     const uint32_t t_o = tmem + lane_addr + 2 * kTile + i * kTile;
     // e4m3: scores carry the q tile's and the kv tile's scale; V tiles are weighted relative to
     // the largest V scale of this (batch, kv head).
-    float cq = p.scale_log2;
+    float cq = kSoftCap ? p.soft_cap * kLog2e : p.scale_log2;  // score -> log2 units
     float v_ref = 1.f;
     const float* k_scale = nullptr;
     const float* v_scale = nullptr;
@@ -390,6 +392,12 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           s[64 + j] = __uint_as_float(v2[j]);
           s[96 + j] = __uint_as_float(v3[j]);
         }
+      }
+      if constexpr (kSoftCap) {
+        // s <- tanh(scale * s / cap) before masking (reference :202-296 caps, then masks); the
+        // factor cap * log2(e) that follows is `c`.
+#pragma unroll
+        for (int j = 0; j < kTile; ++j) s[j] = tanh_ex2(s[j] * p.softcap_a);
       }
       const int kv0 = ent.x * kTile;
       if (st == 1) {
@@ -537,7 +545,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const int64_t stat = ((int64_t)batch * p.q_heads + head) * p.q_len + q_row;
       if (p.lse) p.lse[stat] = live ? (m_used + log2f(l)) * kLn2 : p.mask_value;
       if (p.maxl) {
-        float mv = kFp8 ? m_true * kLn2 : m_true * p.scale;
+        float mv = kFp8 ? m_true * kLn2 : m_true * (kSoftCap ? p.soft_cap : p.scale);
         if (p.sinks != nullptr) mv = fmaxf(mv, sink2 * kLn2);
         if (fixed_max) mv = m_used * kLn2;
         p.maxl[stat] = live ? mv : p.mask_value;
@@ -560,6 +568,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const float* k_scale,
                              const float* v_scale, bool fp8, cudaStream_t stream) {
   int st;
+  const bool soft_cap = a.soft_cap != 0.f;
+  if (soft_cap && (fp8 || !(a.soft_cap > 0.f))) return fp8 ? SPLASH_ERR_UNSUPPORTED : SPLASH_ERR_INVALID_ARGUMENT;
   if (fp8) {
     if ((st = check_e4m3_tensor(a.q)) || (st = check_e4m3_tensor(a.k)) || (st = check_e4m3_tensor(a.v)))
       return st;
@@ -630,6 +640,8 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   p.n_kv_tiles = (int)(Skv / kTile);
   p.sinks = a.sinks;
   p.max_logit_value = a.max_logit_value;
+  p.soft_cap = a.soft_cap;
+  p.softcap_a = soft_cap ? a.scale / a.soft_cap : 0.f;
 
   // The q heads of one kv head stream the same K / V (2 tensors of Skv x 128 elements).
   p.n_groups = (int)(Hq * B);
@@ -638,20 +650,26 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   dim3 grid((unsigned)(p.n_rows * p.n_groups), 1u, 1u);
   if (fp8) {
     constexpr int smem = fwd_smem_bytes(true);
-    if (cudaFuncSetAttribute(splash_fwd_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) !=
-        cudaSuccess)
+    if (cudaFuncSetAttribute(splash_fwd_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem) != cudaSuccess)
       return SPLASH_ERR_CUDA;
-    splash_fwd_kernel<true><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
+    splash_fwd_kernel<true, false><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
+  } else if (soft_cap) {
+    constexpr int smem = fwd_smem_bytes(false);
+    if (cudaFuncSetAttribute(splash_fwd_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             smem) != cudaSuccess)
+      return SPLASH_ERR_CUDA;
+    splash_fwd_kernel<false, true><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
   } else {
     constexpr int smem = fwd_smem_bytes(false);
     static bool attr_set = false;
     if (!attr_set) {
-      if (cudaFuncSetAttribute(splash_fwd_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+      if (cudaFuncSetAttribute(splash_fwd_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                smem) != cudaSuccess)
         return SPLASH_ERR_CUDA;
       attr_set = true;
     }
-    splash_fwd_kernel<false><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
+    splash_fwd_kernel<false, false><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
   }
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
 }

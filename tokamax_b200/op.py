@@ -15,6 +15,7 @@ strides — the reference's four layout transposes (``pallas_mosaic_tpu.py:121-1
 
 from __future__ import annotations
 
+import dataclasses
 import functools
 from typing import Any, Callable, Sequence
 
@@ -28,7 +29,8 @@ AUTO = "auto"
 
 
 @functools.lru_cache(maxsize=32)
-def _kernel_for(kind: str, t: int, s: int, window: tuple | None, dense_key: bytes | None):
+def _kernel_for(kind: str, t: int, s: int, window: tuple | None, dense_key: bytes | None,
+                soft_cap: float | None = None):
   if kind == "dense":
     dense = np.frombuffer(dense_key, dtype=np.bool_).reshape(t, s)
     mask = mask_lib.NumpyMask(dense.copy())
@@ -40,7 +42,10 @@ def _kernel_for(kind: str, t: int, s: int, window: tuple | None, dense_key: byte
     mask = mask_lib.LocalMask((t, s), window, 0)
   else:
     raise ValueError(kind)
-  return splash.make_splash_mha(mask, q_seq_shards=1, save_residuals=True,
+  config = None
+  if soft_cap is not None:
+    config = dataclasses.replace(splash.SplashConfig.get_default(), attn_logits_soft_cap=soft_cap)
+  return splash.make_splash_mha(mask, q_seq_shards=1, save_residuals=True, config=config,
                                 mask_value=float(np.finfo(np.float32).min), downcast_smem_data=False)
 
 
@@ -56,8 +61,6 @@ class CudaSm100SplashAttention:
                precision=None, q_sharding=None):
     if bias is not None:
       raise NotImplementedError("Bias is not supported.")
-    if logits_soft_cap is not None:
-      raise NotImplementedError("logits_soft_cap is not built on B200 yet")
     if dropout_rate != 0.0:
       raise NotImplementedError("dropout is not supported.")
     if query_seq_lengths is not None or key_value_seq_lengths is not None:
@@ -79,6 +82,7 @@ class CudaSm100SplashAttention:
     if t % 128 or s % 128:
       raise NotImplementedError("sequence lengths must be multiples of 128")
     scale = h ** -0.5 if logits_scale == AUTO else float(logits_scale)
+    cap = None if logits_soft_cap is None else float(logits_soft_cap)
 
     if mask is not None:
       m = np.asarray(mask.detach().cpu() if hasattr(mask, "detach") else mask).astype(np.bool_)
@@ -92,16 +96,16 @@ class CudaSm100SplashAttention:
       if local_window_size is not None:
         w = (local_window_size, local_window_size) if isinstance(local_window_size, int) else tuple(local_window_size)
         m = m & mask_lib.make_local_attention_mask((t, s), w)
-      kernel = _kernel_for("dense", t, s, None, np.ascontiguousarray(m).tobytes())
+      kernel = _kernel_for("dense", t, s, None, np.ascontiguousarray(m).tobytes(), cap)
     elif local_window_size is not None:
       w = (local_window_size, local_window_size) if isinstance(local_window_size, int) else tuple(local_window_size)
       if is_causal:
         w = (w[0], min(w[1], 0) if w[1] is not None else 0)
-      kernel = _kernel_for("local", t, s, w, None)
+      kernel = _kernel_for("local", t, s, w, None, cap)
     elif is_causal:
-      kernel = _kernel_for("causal", t, s, None, None)
+      kernel = _kernel_for("causal", t, s, None, None, cap)
     else:
-      kernel = _kernel_for("full", t, s, None, None)
+      kernel = _kernel_for("full", t, s, None, None, cap)
 
     def bhtd(x):  # [*B, L, N, H] -> [B', N, L, H] view, no copy for a single batch axis
       x = x.reshape((-1,) + tuple(x.shape[-3:])) if len(batch) != 1 else x

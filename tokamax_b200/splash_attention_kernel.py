@@ -279,6 +279,7 @@ class _SplashFunction(torch.autograd.Function):
     args.error_record = tables.error_record.data_ptr()
     sinks_f32 = None if sinks is None else sinks.detach().to(torch.float32).contiguous()
     args.sinks = None if sinks_f32 is None else sinks_f32.data_ptr()
+    args.soft_cap = float(kernel.config.attn_logits_soft_cap or 0.0)
     args.max_logit_value = None if max_logit is None else max_logit.data_ptr()
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
@@ -318,6 +319,7 @@ class _SplashFunction(torch.autograd.Function):
     args.scale = ctx.scale
     args.workspace = workspace.data_ptr()
     args.workspace_bytes = ws_bytes
+    args.soft_cap = float(kernel.config.attn_logits_soft_cap or 0.0)
     args.error_record = tables.error_record.data_ptr()
     stream = torch.cuda.current_stream(q.device).cuda_stream
     with torch.cuda.device(q.device):
@@ -380,8 +382,8 @@ class SplashAttentionKernel:
     cfg = self.config
     if cfg.max_logit_const is not None and max_logit_value is not None:
       raise ValueError(f"Only one of max_logit_const={cfg.max_logit_const} and {max_logit_value=} can be set.")
-    if cfg.attn_logits_soft_cap is not None:
-      raise NotImplementedError("attn_logits_soft_cap is not built on B200 yet")
+    if cfg.attn_logits_soft_cap is not None and not cfg.attn_logits_soft_cap > 0:
+      raise ValueError(f"attn_logits_soft_cap must be positive, got {cfg.attn_logits_soft_cap}")
     if any(l != QKVLayout.HEAD_DIM_MINOR for l in (cfg.q_layout, cfg.k_layout, cfg.v_layout)):
       raise NotImplementedError("only HEAD_DIM_MINOR layouts are built on B200")
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16:
