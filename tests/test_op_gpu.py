@@ -69,7 +69,8 @@ def test_op_dispatch_errors():
   with pytest.raises(NotImplementedError):
     op.dot_product_attention(q, q, q, bias=torch.zeros(1, device=dev), implementation="cuda_sm100")
   with pytest.raises(ExceptionGroup):
-    op.dot_product_attention(q, q, q, dropout_rate=0.1, implementation=["cuda_sm100", "cuda_sm100"])
+    op.dot_product_attention(q, q, q, query_seq_lengths=torch.tensor([64]),
+                             implementation=["cuda_sm100", "cuda_sm100"])
   with pytest.raises(ValueError):
     op.dot_product_attention(q, q, q, implementation="nope")
   with pytest.raises(ValueError):
@@ -80,7 +81,7 @@ def test_op_soft_cap_matches_oracle():
   b, t, n, kh = 1, 256, 4, 2
   q, k, v = _bthd(21, b, t, n), _bthd(22, b, t, kh), _bthd(23, b, t, kh)
   dev = torch.device("cuda:0")
-  out = op.dot_product_attention(q.to(dev), k.to(dev), v.to(dev), is_causal=True, logits_scale=0.3,
+  out = op.dot_product_attention(q.to(dev), k.to(dev), v.to(dev), is_causal=True, scale=0.3,
                                  logits_soft_cap=5.0, implementation="cuda_sm100")
   o, _, _ = attention_ref.attention_reference(q[0].permute(1, 0, 2), k[0].permute(1, 0, 2), v[0].permute(1, 0, 2),
                                               mask_lib.make_causal_mask((t, t)), scale=0.3, attn_logits_soft_cap=5.0)
