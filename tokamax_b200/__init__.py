@@ -37,7 +37,7 @@ __all__ = [
 
 def __getattr__(name):
   # The kernel module imports torch; keep `import tokamax_b200` light for table-only users.
-  if name in ("splash_attention_kernel", "ulysses", "op", "fp8"):
+  if name in ("splash_attention_kernel", "ulysses", "ring_attention", "op", "fp8"):
     import importlib
 
     return importlib.import_module(f"tokamax_b200.{name}")

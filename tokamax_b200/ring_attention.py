@@ -1,0 +1,287 @@
+"""Ring attention: context parallelism with the keys and values sharded along the sequence.
+
+Counterpart of the reference's ring wrapper
+(tokamax/_src/ops/experimental/tpu/splash_attention/ring_attention_kernel.py:68-293, factory
+:617-705).  Rank ``r`` of ``P`` keeps its query shard for the whole call and starts with key /
+value shard ``r``; at step ``i`` it attends to shard ``(r - i) mod P`` and passes the shard it
+holds on to rank ``r + 1`` (:98-113).  Per step the unsharded splash kernels run on the
+(query shard, key shard) sub-mask; the forward merges the partial outputs through their
+logsumexp in fp32 (:150-158), the backward calls the backward kernels with the merged output and
+logsumexp, accumulates dq in place and sends the dk / dv accumulators round the ring with their
+shard, so that they are back home after ``P`` steps (:228-262).
+
+Unlike Ulysses (``tokamax_b200.ulysses``) this does not need ``P`` to divide the head counts and
+never materialises the whole sequence on one GPU; it pays for that with ``P`` kernel launches per
+pass and with merging in HBM.  The transfer of step ``i + 1``'s shard is posted before the kernels
+of step ``i`` are launched, so it runs under them.
+
+Differences from the reference: sub-masks are built per (query shard, key shard) pair from the
+mask object itself (any mask, not only ``NumpyMask`` / ``FullMask``, :647-650), pairs whose
+sub-mask is empty launch nothing, and tensors are batched ``[B, H, S / P, D]``.
+"""
+
+from __future__ import annotations
+
+from typing import Any, Callable, Protocol
+
+import numpy as np
+import torch
+import torch.distributed as dist
+
+from tokamax_b200 import base
+from tokamax_b200 import splash_attention_mask as mask_lib
+
+DEFAULT_MASK_VALUE = base.DEFAULT_MASK_VALUE
+
+
+# ----------------------------------------------------------------------------------------------
+# sub-masks
+# ----------------------------------------------------------------------------------------------
+def shard_mask(mask: mask_lib.Mask, q_shard: int, kv_shard: int, q_shards: int, kv_shards: int) -> mask_lib.Mask:
+  """The (q_shard, kv_shard) window of ``mask`` as a mask object of its own.
+
+  Lazy masks stay lazy: a causal or local mask seen from a window is the same rule with its offset
+  moved by ``q_start - kv_start``; a chunked-causal window is chunked-causal again on the diagonal
+  when the shard length is a multiple of the chunk.  Anything else is materialised for the window.
+  """
+  q_len, kv_len = mask.shape
+  if q_len % q_shards or kv_len % kv_shards:
+    raise ValueError(f"mask {mask.shape} does not split into {q_shards} x {kv_shards} shards")
+  sq, skv = q_len // q_shards, kv_len // kv_shards
+  q0, k0 = q_shard * sq, kv_shard * skv
+  shape = (sq, skv)
+  if isinstance(mask, mask_lib.FullMask):
+    return mask_lib.FullMask(shape)
+  if isinstance(mask, mask_lib.CausalMask):
+    return mask_lib.CausalMask(shape, offset=mask.offset + q0 - k0)
+  if isinstance(mask, mask_lib.LocalMask):
+    return mask_lib.LocalMask(shape, mask.window_size, mask.offset + q0 - k0)
+  if isinstance(mask, mask_lib.ChunkedCausalMask) and q0 == k0 and q0 % mask.chunk_size == 0:
+    return mask_lib.ChunkedCausalMask(shape, mask.chunk_size)
+  if isinstance(mask, (mask_lib.LogicalAnd, mask_lib.LogicalOr)):
+    return type(mask)(shard_mask(mask.left, q_shard, kv_shard, q_shards, kv_shards),
+                      shard_mask(mask.right, q_shard, kv_shard, q_shards, kv_shards))
+  window = np.ascontiguousarray(mask[q0:q0 + sq, k0:k0 + skv]).astype(np.bool_)
+  return mask_lib.NumpyMask(window)
+
+
+# ----------------------------------------------------------------------------------------------
+# what the ring needs from the per-pair attention
+# ----------------------------------------------------------------------------------------------
+class ShardAttention(Protocol):
+  """Attention of one query shard against one key shard."""
+
+  empty: bool  # the sub-mask has no live block: both calls may be skipped
+
+  def forward(self, q, k, v, q_seg, kv_seg, scale: float) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(o [B, Hq, Sq, D], logsumexp fp32 [B, Hq, Sq])``; rows without a live key: lse <= -1e37."""
+
+  def backward(self, q, k, v, o, lse, d_o, q_seg, kv_seg, scale: float):
+    """``(dq, dk, dv)`` of this key shard given the merged ``o`` / ``lse``."""
+
+
+class SplashShardAttention:
+  """`ShardAttention` on the CUDA kernels."""
+
+  def __init__(self, sub_mask: mask_lib.Mask, **kernel_kwargs):
+    from tokamax_b200 import splash_attention_kernel as splash  # needs torch + the native library
+
+    self._splash = splash
+    self.kernel = splash.make_splash_mha(sub_mask, q_seq_shards=1, save_residuals=True, **kernel_kwargs)
+    info = self.kernel.fwd_mask_info
+    self.empty = info.num_active_blocks is not None and int(np.sum(info.num_active_blocks)) == 0
+    if info.block_mask is not None and not self.empty:
+      self.empty = not bool(np.any(np.asarray(info.block_mask) > 0))
+
+  def forward(self, q, k, v, q_seg, kv_seg, scale):
+    seg = None if q_seg is None else base.SegmentIds(q_seg, kv_seg)
+    with torch.no_grad():
+      o, res = self.kernel(q, k, v, seg, logits_scale=scale)
+    return o, res["logsumexp"]
+
+  def backward(self, q, k, v, o, lse, d_o, q_seg, kv_seg, scale):
+    dq, dk, dv, _ = self._splash.splash_backward(self.kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, scale)
+    return dq, dk, dv
+
+
+# ----------------------------------------------------------------------------------------------
+# merge of partial softmaxes
+# ----------------------------------------------------------------------------------------------
+def merge_partial(o_acc: torch.Tensor, lse_acc: torch.Tensor, o_i: torch.Tensor, lse_i: torch.Tensor):
+  """Folds one partial (normalised output, logsumexp) into the fp32 running pair, in place.
+
+  Same arithmetic as the reference's (m, l, o) carry (:150-158) written on logsumexp: the merged
+  output is the logsumexp-weighted mean of the partial outputs.
+  """
+  lse_new = torch.logaddexp(lse_acc, lse_i)
+  w_acc = torch.exp(lse_acc - lse_new).unsqueeze(-1)
+  w_i = torch.exp(lse_i - lse_new).unsqueeze(-1)
+  o_acc.mul_(w_acc).addcmul_(o_i.float(), w_i)
+  lse_acc.copy_(lse_new)
+
+
+# ----------------------------------------------------------------------------------------------
+# the ring
+# ----------------------------------------------------------------------------------------------
+def _ring_peers(group) -> tuple[int, int, int, int]:
+  rank, world = dist.get_rank(group), dist.get_world_size(group)
+  to_global = (lambda r: dist.get_global_rank(group, r)) if group is not None else (lambda r: r)
+  return rank, world, to_global((rank + 1) % world), to_global((rank - 1) % world)
+
+
+def _post_shift(tensors, group, nxt: int, prv: int):
+  """Sends each tensor to the next rank and receives the previous rank's; returns (works, received)."""
+  if nxt == prv == dist.get_rank():  # a ring of one: nothing moves
+    return [], list(tensors)
+  recv = [torch.empty_like(t) for t in tensors]
+  ops = []
+  for t, r in zip(tensors, recv):
+    ops.append(dist.P2POp(dist.isend, t.contiguous(), nxt, group))
+    ops.append(dist.P2POp(dist.irecv, r, prv, group))
+  return dist.batch_isend_irecv(ops), recv
+
+
+def _wait(works):
+  for w in works:
+    w.wait()
+
+
+class _RingFunction(torch.autograd.Function):
+
+  @staticmethod
+  def forward(ctx, q, k, v, q_seg, kv_seg, ring, scale):
+    rank, world, nxt, prv = _ring_peers(ring.group)
+    b, hq, sq, d = q.shape
+    o_acc = torch.zeros((b, hq, sq, d), dtype=torch.float32, device=q.device)
+    lse_acc = torch.full((b, hq, sq), -float("inf"), dtype=torch.float32, device=q.device)
+    k_cur, v_cur, seg_cur = k.contiguous(), v.contiguous(), kv_seg
+    for i in range(world):
+      shard = (rank - i) % world
+      works = None
+      if i + 1 < world:  # the next step's shard travels under this step's kernels
+        moving = [k_cur, v_cur] + ([seg_cur] if seg_cur is not None else [])
+        works, received = _post_shift(moving, ring.group, nxt, prv)
+      attn = ring.shard_attention(rank, shard)
+      if not attn.empty:
+        o_i, lse_i = attn.forward(q, k_cur, v_cur, q_seg, seg_cur, scale)
+        merge_partial(o_acc, lse_acc, o_i, lse_i)
+      if works is not None:
+        _wait(works)
+        k_cur, v_cur = received[0], received[1]
+        seg_cur = received[2] if seg_cur is not None else None
+    dead = lse_acc < -1.0e37  # no live key on any shard (or no shard visited at all)
+    o = torch.where(dead.unsqueeze(-1), torch.zeros_like(o_acc), o_acc).to(q.dtype)
+    lse = torch.where(dead, torch.full_like(lse_acc, ring.mask_value), lse_acc)
+    ctx.save_for_backward(q, k, v, o, lse, q_seg, kv_seg)
+    ctx.ring, ctx.scale = ring, scale
+    ctx.mark_non_differentiable(lse)
+    return o, lse
+
+  @staticmethod
+  def backward(ctx, d_o, _dlse):
+    q, k, v, o, lse, q_seg, kv_seg = ctx.saved_tensors
+    ring, scale = ctx.ring, ctx.scale
+    rank, world, nxt, prv = _ring_peers(ring.group)
+    d_o = d_o.contiguous()
+    dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    k_cur, v_cur, seg_cur = k.contiguous(), v.contiguous(), kv_seg
+    acc_in_flight = None  # (works, [dk_acc, dv_acc]) on their way here from the previous rank
+    for i in range(world):
+      shard = (rank - i) % world
+      works = None
+      if i + 1 < world:
+        moving = [k_cur, v_cur] + ([seg_cur] if seg_cur is not None else [])
+        works, received = _post_shift(moving, ring.group, nxt, prv)
+      attn = ring.shard_attention(rank, shard)
+      dk_i = dv_i = None
+      if not attn.empty:
+        dq_i, dk_i, dv_i = attn.backward(q, k_cur, v_cur, o, lse, d_o, q_seg, seg_cur, scale)
+        dq += dq_i.float()
+      # The accumulators follow their shard: what the previous rank held for the shard now here
+      # arrives while this step's kernels run, gets this step's share, and moves on.  After the
+      # last step's shift they are home again (reference :255-262).
+      if acc_in_flight is None:
+        dk_acc = torch.zeros(k.shape, dtype=torch.float32, device=k.device)
+        dv_acc = torch.zeros(v.shape, dtype=torch.float32, device=v.device)
+      else:
+        _wait(acc_in_flight[0])
+        dk_acc, dv_acc = acc_in_flight[1]
+      if dk_i is not None:
+        dk_acc += dk_i.float()
+        dv_acc += dv_i.float()
+      acc_in_flight = _post_shift([dk_acc, dv_acc], ring.group, nxt, prv)
+      if works is not None:
+        _wait(works)
+        k_cur, v_cur = received[0], received[1]
+        seg_cur = received[2] if seg_cur is not None else None
+    _wait(acc_in_flight[0])
+    dk_acc, dv_acc = acc_in_flight[1]
+    return dq.to(q.dtype), dk_acc.to(k.dtype), dv_acc.to(v.dtype), None, None, None, None
+
+
+class RingSplashAttention:
+  """Sequence-sharded splash attention over a ring of ranks (reference :520-615).
+
+  Call with the local shards ``q [B, Hq, S/P, D]``, ``k, v [B, Hkv, S/P, D]`` (rank ``r`` holds
+  tokens ``[r S/P, (r+1) S/P)`` of both) and optional ``SegmentIds`` shards ``[B, S/P]``.  Returns
+  the local shard of the output, or ``(out, {"logsumexp"})`` with ``save_residuals=True``.
+  """
+
+  def __init__(self, mask: mask_lib.Mask, *, group=None, save_residuals: bool = False,
+               mask_value: float = DEFAULT_MASK_VALUE,
+               shard_attention_factory: Callable[[mask_lib.Mask], ShardAttention] | None = None,
+               **kernel_kwargs: Any):
+    self.mask = mask
+    self.group = group
+    self.save_residuals = save_residuals
+    self.mask_value = max(float(mask_value), -3.0e38)
+    self._factory = shard_attention_factory or (
+        lambda sub: SplashShardAttention(sub, mask_value=mask_value, **kernel_kwargs))
+    self._cache: dict[tuple[int, int, int], ShardAttention] = {}
+
+  def shard_attention(self, q_shard: int, kv_shard: int) -> ShardAttention:
+    world = dist.get_world_size(self.group)
+    key = (world, q_shard, kv_shard)
+    if key not in self._cache:
+      self._cache[key] = self._factory(shard_mask(self.mask, q_shard, kv_shard, world, world))
+    return self._cache[key]
+
+  def __call__(self, q, k, v, segment_ids: base.SegmentIds | None = None, sinks=None, *,
+               logits_scale: float = 1.0):
+    if sinks is not None:
+      raise NotImplementedError("Sinks aren't supported yet.")  # as the reference, :91-92
+    world = dist.get_world_size(self.group)
+    q_len, kv_len = self.mask.shape
+    if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
+      raise ValueError(f"expected [B, H, S/P, D] shards, got {tuple(q.shape)}, {tuple(k.shape)}")
+    if q.shape[2] * world != q_len or k.shape[2] * world != kv_len or v.shape[2] != k.shape[2]:
+      raise ValueError(f"shards of length {q.shape[2]} / {k.shape[2]} on {world} ranks do not tile the "
+                       f"mask {self.mask.shape}")
+    if q.shape[-1] != k.shape[-1]:
+      raise NotImplementedError("Queries and keys must have the same head dimension.")
+    q_seg = kv_seg = None
+    if segment_ids is not None:
+      q_seg = torch.as_tensor(segment_ids.q, device=q.device).to(torch.int32).contiguous()
+      kv_seg = torch.as_tensor(segment_ids.kv, device=q.device).to(torch.int32).contiguous()
+    out, lse = _RingFunction.apply(q, k, v, q_seg, kv_seg, self, float(logits_scale))
+    if self.save_residuals:
+      return out, {"logsumexp": lse}
+    return out
+
+
+def make_ring_attention(mask: np.ndarray | mask_lib.Mask, *, config=None, is_mqa: bool = False,
+                        save_residuals: bool = False, mask_value: float = DEFAULT_MASK_VALUE,
+                        downcast_smem_data: bool = True, partial_mask_blocks_dtype: Any = np.int8,
+                        ring_axis=None, q_seq_shards: int = 1, kv_seq_shards: int = 1) -> RingSplashAttention:
+  """Reference factory (:617-705).  ``ring_axis`` is the process group of the ring (default: the world)."""
+  del q_seq_shards, kv_seq_shards  # the ring size is the group's size; sub-masks are cut per pair
+  if len(mask.shape) != 2:
+    raise ValueError(f"Unexpected mask shape: {mask.shape}")
+  if isinstance(mask, np.ndarray):
+    mask = mask_lib.NumpyMask(mask)
+  if is_mqa:
+    raise NotImplementedError("pass MQA keys / values with a kv-head axis of 1")
+  kwargs = dict(downcast_smem_data=downcast_smem_data, partial_mask_blocks_dtype=partial_mask_blocks_dtype)
+  if config is not None:
+    kwargs["config"] = config
+  return RingSplashAttention(mask, group=ring_axis, save_residuals=save_residuals, mask_value=mask_value, **kwargs)

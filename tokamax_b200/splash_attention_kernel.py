@@ -294,44 +294,55 @@ class _SplashFunction(torch.autograd.Function):
   @staticmethod
   def backward(ctx, d_o, _dlse, _dmax):
     q, k, v, o, lse, q_seg, kv_seg, sinks = ctx.saved_tensors
-    kernel = ctx.kernel
-    tables = kernel._tables(q.device)  # pylint: disable=protected-access
-    d_o = _usable(d_o)
-    dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-    lib = _native.lib()
-    ws_bytes = lib.splash_bwd_workspace_bytes(q.shape[0], q.shape[1], q.shape[2])
-    workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
-    args = _native.SplashBwdArgs()
-    args.q, args.k, args.v, args.o, args.d_o = map(_tensor_desc, (q, k, v, o, d_o))
-    args.dq, args.dk, args.dv = map(_tensor_desc, (dq, dk, dv))
-    args.logsumexp = lse.data_ptr()
-    args.q_segment_ids = q_seg.data_ptr() if q_seg is not None else None
-    args.kv_segment_ids = kv_seg.data_ptr() if kv_seg is not None else None
-    args.q_sequence = tables.q_sequence.data_ptr() if tables.q_sequence is not None else None
-    keep = []
-    args.sched_dq = tables.dq
-    args.sched_dkv = tables.dkv
-    if q_seg is not None:
-      args.sched_dq, ws1 = _segment_schedule(tables.dq, 1, q_seg, kv_seg, q.shape[2], k.shape[2])
-      args.sched_dkv, ws2 = _segment_schedule(tables.dkv, 2, q_seg, kv_seg, q.shape[2], k.shape[2])
-      keep += [ws1, ws2]
-    args.mask_fn = _mask_fn_struct(kernel.mask_function_rule)
-    args.scale = ctx.scale
-    args.workspace = workspace.data_ptr()
-    args.workspace_bytes = ws_bytes
-    args.soft_cap = float(kernel.config.attn_logits_soft_cap or 0.0)
-    args.error_record = tables.error_record.data_ptr()
-    stream = torch.cuda.current_stream(q.device).cuda_stream
-    with torch.cuda.device(q.device):
-      _native.check(lib.splash_bwd(C.byref(args), C.c_void_p(stream)), "splash_bwd")
+    dq, dk, dv, di = splash_backward(ctx.kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale)
     dsinks = None
     if sinks is not None:
-      # reference kernel.py:1928-1935: dsinks[h] = -sum_rows exp(sink - lse) * sum_d(o * do); the
-      # row sums di are the first array of the backward workspace.
-      n = q.shape[0] * q.shape[1] * q.shape[2]
-      di = workspace[:4 * n].view(torch.float32).view(q.shape[0], q.shape[1], q.shape[2])
+      # reference kernel.py:1928-1935: dsinks[h] = -sum_rows exp(sink - lse) * sum_d(o * do)
       dsinks = -(torch.exp(sinks[None, :, None] - lse) * di).sum(dim=(0, 2)).to(ctx.sinks_dtype)
     return dq, dk, dv, None, None, None, None, dsinks, None
+
+
+def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg=None, kv_seg=None,
+                    scale: float = 1.0):
+  """One `splash_bwd` call: ``(dq, dk, dv, di)`` for batched ``[B, H, S, 128]`` bf16 tensors.
+
+  ``o`` and ``lse`` are the forward's output and logsumexp for these q rows; they may come from a
+  softmax over more keys than ``k`` holds (ring attention passes the merged values, reference
+  ring_attention_kernel.py:228-262), in which case dq / dk / dv are this key shard's share.
+  ``di`` is the fp32 row sum ``sum_d(o * do)`` ``[B, Hq, Sq]`` the backward leaves in its workspace.
+  """
+  tables = kernel._tables(q.device)  # pylint: disable=protected-access
+  d_o = _usable(d_o)
+  dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+  lib = _native.lib()
+  ws_bytes = lib.splash_bwd_workspace_bytes(q.shape[0], q.shape[1], q.shape[2])
+  workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
+  args = _native.SplashBwdArgs()
+  args.q, args.k, args.v, args.o, args.d_o = map(_tensor_desc, (q, k, v, o, d_o))
+  args.dq, args.dk, args.dv = map(_tensor_desc, (dq, dk, dv))
+  args.logsumexp = lse.data_ptr()
+  args.q_segment_ids = q_seg.data_ptr() if q_seg is not None else None
+  args.kv_segment_ids = kv_seg.data_ptr() if kv_seg is not None else None
+  args.q_sequence = tables.q_sequence.data_ptr() if tables.q_sequence is not None else None
+  keep = []
+  args.sched_dq = tables.dq
+  args.sched_dkv = tables.dkv
+  if q_seg is not None:
+    args.sched_dq, ws1 = _segment_schedule(tables.dq, 1, q_seg, kv_seg, q.shape[2], k.shape[2])
+    args.sched_dkv, ws2 = _segment_schedule(tables.dkv, 2, q_seg, kv_seg, q.shape[2], k.shape[2])
+    keep += [ws1, ws2]
+  args.mask_fn = _mask_fn_struct(kernel.mask_function_rule)
+  args.scale = scale
+  args.workspace = workspace.data_ptr()
+  args.workspace_bytes = ws_bytes
+  args.soft_cap = float(kernel.config.attn_logits_soft_cap or 0.0)
+  args.error_record = tables.error_record.data_ptr()
+  stream = torch.cuda.current_stream(q.device).cuda_stream
+  with torch.cuda.device(q.device):
+    _native.check(lib.splash_bwd(C.byref(args), C.c_void_p(stream)), "splash_bwd")
+  n = q.shape[0] * q.shape[1] * q.shape[2]
+  di = workspace[:4 * n].view(torch.float32).view(q.shape[0], q.shape[1], q.shape[2])
+  return dq, dk, dv, di
 
 
 class SplashAttentionKernel:
@@ -464,6 +475,12 @@ class SplashAttentionKernel:
 # ----------------------------------------------------------------------------------------------
 # factories
 # ----------------------------------------------------------------------------------------------
+def _live_fraction(block_mask) -> float:
+  """Share of non-empty blocks in a block_mask table (0 for a mask with no live block)."""
+  block_mask = np.asarray(block_mask)
+  return float(np.mean(block_mask != 0)) if block_mask.size else 0.0
+
+
 def _make_splash_attention(
     mask: np.ndarray | mask_lib.Mask,
     *,
@@ -494,7 +511,7 @@ def _make_splash_attention(
   )
   fwd_mask_info, mask_function_fwd = process_fn(mask, (config.block_q, config.block_kv))
   fwd_mask_sparsity = (
-      float(np.mean(fwd_mask_info.block_mask != 0)) if fwd_mask_info.block_mask is not None else 1.0
+      _live_fraction(fwd_mask_info.block_mask) if fwd_mask_info.block_mask is not None else 1.0
   )
   dkv_mask_info = None
   dkv_mask_sparsity = 1.0
@@ -507,7 +524,7 @@ def _make_splash_attention(
     )
     assert (mask_function_fwd is None) == (mask_function_dkv is None)
     if dkv_mask_info.block_mask is not None:
-      dkv_mask_sparsity = float(np.mean(dkv_mask_info.block_mask != 0))
+      dkv_mask_sparsity = _live_fraction(dkv_mask_info.block_mask)
   rule = mask.interval_rule if mask_function_fwd is not None else None
   return SplashAttentionKernel(
       fwd_mask_info,
