@@ -197,6 +197,30 @@ int splash_segment_schedule(const SplashDeviceSchedule* in, int32_t kind, const 
                             void* cuda_stream);
 
 /* ------------------------------------------------------------------------------------------
+ * Schedules for a mask that is data on the device (device).  Replaces `_process_dynamic_mask`
+ * (splash_attention_mask_info.py:231-350; factories splash_attention_kernel.py:2134-2226) for the
+ * kernels' purposes: nothing goes through the host, so a mask may change every call.
+ *
+ * splash_mask_tile_states: `mask` is [q_len, kv_len] bytes (0 = masked, anything else = keep; a
+ * bool or int8 array), 16-byte aligned rows (`row_stride_bytes` a multiple of 16); writes the state
+ * of every 128x128 tile (0 empty, 1 partial, 2 full) to `states` [q_len / 128, kv_len / 128].
+ *
+ * splash_dynamic_schedule: turns `states` into a schedule of `kind` (as in splash_schedule_build)
+ * inside `workspace` (splash_dynamic_schedule_bytes bytes, 256-byte aligned): rows at a fixed
+ * stride with `row_end` replicated for `batch` rows.  `partial_blocks` is what the attention
+ * kernels read for partial tiles — the mask itself [q_len, kv_len] for kinds 0 and 1, its
+ * transpose [kv_len, q_len] for kind 2 — registered as one partial block covering the whole mask.
+ * The result cannot be passed to splash_segment_schedule (segment ids are still applied
+ * element by element by the kernels).
+ * ---------------------------------------------------------------------------------------- */
+int splash_mask_tile_states(const void* mask, int64_t row_stride_bytes, int64_t q_len, int64_t kv_len,
+                            int32_t* states, void* cuda_stream);
+size_t splash_dynamic_schedule_bytes(int64_t q_len, int64_t kv_len, int32_t kind, int64_t batch);
+int splash_dynamic_schedule(const int32_t* states, int64_t q_len, int64_t kv_len, int32_t kind, int64_t batch,
+                            const void* partial_blocks, void* workspace, size_t workspace_bytes,
+                            SplashDeviceSchedule* out, void* cuda_stream);
+
+/* ------------------------------------------------------------------------------------------
  * Forward.  Replaces `_splash_attention_forward` + `flash_attention_kernel`
  * (splash_attention_kernel.py:550-995, :299-527): o = softmax(mask(scale * q k^T)) v with fp32
  * accumulation, plus logsumexp and max_logits (natural log, fp32 [batch, q_heads, q_len]).

@@ -24,6 +24,7 @@ SOURCES = (
     "schedule_builder.cc",
     "maskinfo_builder.cc",
     "segment_schedule.cu",
+    "dynamic_schedule.cu",
 )
 
 NVCC_FLAGS = (
@@ -177,6 +178,10 @@ _PROTOTYPES = {
     "splash_segment_schedule": (C.c_int, [C.POINTER(SplashDeviceSchedule), C.c_int32, C.c_void_p, C.c_void_p,
                                           C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t,
                                           C.POINTER(SplashDeviceSchedule), C.c_void_p]),
+    "splash_mask_tile_states": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]),
+    "splash_dynamic_schedule_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int32, C.c_int64]),
+    "splash_dynamic_schedule": (C.c_int, [C.c_void_p, C.c_int64, C.c_int64, C.c_int32, C.c_int64, C.c_void_p,
+                                          C.c_void_p, C.c_size_t, C.POINTER(SplashDeviceSchedule), C.c_void_p]),
     "splash_fwd": (C.c_int, [C.POINTER(SplashFwdArgs), C.c_void_p]),
     "splash_fwd_fp8": (C.c_int, [C.POINTER(SplashFwdFp8Args), C.c_void_p]),
     "splash_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),

@@ -203,6 +203,47 @@ class _DeviceTables:
     return d
 
 
+class _DynamicDeviceTables:
+  """Schedules built on the device from a mask tensor (no host round trip; one per batch size).
+
+  The 128x128 tile states come from one pass over the mask, the three schedules from one small
+  kernel each, and partial tiles are read from the mask itself (its transpose for dkv).
+  """
+
+  def __init__(self, mask: torch.Tensor, batch: int):
+    lib = _native.lib()
+    device = mask.device
+    if mask.dim() != 2 or mask.dtype not in (torch.bool, torch.int8, torch.uint8):
+      raise ValueError(f"expected a 2-dim bool / int8 mask tensor, got {mask.dtype} {tuple(mask.shape)}")
+    q_len, kv_len = mask.shape
+    if q_len % _TILE or kv_len % _TILE:
+      raise NotImplementedError(f"mask sides must be multiples of {_TILE} on B200, got {tuple(mask.shape)}")
+    m = mask.contiguous().view(torch.uint8)
+    mt = m.t().contiguous()
+    if m.data_ptr() % 16 or mt.data_ptr() % 16:
+      m, mt = m.clone(), mt.clone()
+    states = torch.empty((q_len // _TILE, kv_len // _TILE), dtype=torch.int32, device=device)
+    stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
+    self.keep = [m, mt, states]
+    with torch.cuda.device(device):
+      _native.check(lib.splash_mask_tile_states(m.data_ptr(), m.stride(0), q_len, kv_len, states.data_ptr(), stream),
+                    "splash_mask_tile_states")
+      scheds = []
+      for kind, blocks in ((0, m), (1, m), (2, mt)):
+        nbytes = lib.splash_dynamic_schedule_bytes(q_len, kv_len, kind, batch)
+        ws = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        out = _native.SplashDeviceSchedule()
+        _native.check(lib.splash_dynamic_schedule(states.data_ptr(), q_len, kv_len, kind, batch, blocks.data_ptr(),
+                                                  ws.data_ptr(), nbytes, C.byref(out), stream),
+                      "splash_dynamic_schedule")
+        self.keep.append(ws)
+        scheds.append(out)
+    self.fwd, self.dq, self.dkv = scheds
+    self.tile_states = states
+    self.error_record = torch.zeros(4, dtype=torch.int32, device=device)
+    self.q_sequence = None
+
+
 def _segment_schedule(sched: _native.SplashDeviceSchedule, kind: int, q_seg, kv_seg, q_len: int, kv_len: int):
   """Per-batch-row copy of ``sched`` without the tiles the segment ids rule out (device side).
 
@@ -255,7 +296,7 @@ class _SplashFunction(torch.autograd.Function):
   @staticmethod
   def forward(ctx, q, k, v, q_seg, kv_seg, kernel, scale, sinks, max_logit):
     _require_cuda(q)
-    tables = kernel._tables(q.device)  # pylint: disable=protected-access
+    tables = kernel._tables(q.device, q.shape[0])  # pylint: disable=protected-access
     q, k, v = _usable(q), _usable(k), _usable(v)
     b, hq, sq, d = q.shape
     o = torch.empty_like(q)  # keeps q's (dense) stride order, e.g. [B,T,H,D] storage stays [B,T,H,D]
@@ -270,7 +311,7 @@ class _SplashFunction(torch.autograd.Function):
     args.q_sequence = tables.q_sequence.data_ptr() if tables.q_sequence is not None else None
     keep = []
     args.sched = tables.fwd
-    if q_seg is not None:
+    if q_seg is not None and not tables.fwd.row_end:  # device-built schedules are not filtered further
       args.sched, ws = _segment_schedule(tables.fwd, 0, q_seg, kv_seg, q.shape[2], k.shape[2])
       keep.append(ws)
     args.mask_fn = _mask_fn_struct(kernel.mask_function_rule)
@@ -311,7 +352,7 @@ def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg
   ring_attention_kernel.py:228-262), in which case dq / dk / dv are this key shard's share.
   ``di`` is the fp32 row sum ``sum_d(o * do)`` ``[B, Hq, Sq]`` the backward leaves in its workspace.
   """
-  tables = kernel._tables(q.device)  # pylint: disable=protected-access
+  tables = kernel._tables(q.device, q.shape[0])  # pylint: disable=protected-access
   d_o = _usable(d_o)
   dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
   lib = _native.lib()
@@ -327,7 +368,7 @@ def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg
   keep = []
   args.sched_dq = tables.dq
   args.sched_dkv = tables.dkv
-  if q_seg is not None:
+  if q_seg is not None and not tables.dq.row_end:
     args.sched_dq, ws1 = _segment_schedule(tables.dq, 1, q_seg, kv_seg, q.shape[2], k.shape[2])
     args.sched_dkv, ws2 = _segment_schedule(tables.dkv, 2, q_seg, kv_seg, q.shape[2], k.shape[2])
     keep += [ws1, ws2]
@@ -356,11 +397,32 @@ class SplashAttentionKernel:
   the caller's ``q * scale`` into the kernel in fp32).  Differentiable through torch autograd.
   """
 
-  def __init__(self, fwd_mask_info: MaskInfo, dkv_mask_info: MaskInfo | None, **kwargs):
+  def __init__(self, fwd_mask_info: MaskInfo | None, dkv_mask_info: MaskInfo | None, *,
+               dynamic_mask: torch.Tensor | None = None, **kwargs):
     self.kwargs = kwargs
-    self.fwd_mask_info = fwd_mask_info
-    self.dkv_mask_info = dkv_mask_info
+    self._fwd_mask_info = fwd_mask_info
+    self._dkv_mask_info = dkv_mask_info
+    # A mask tensor on a CUDA device: schedules are built there at call time, and the MaskInfo
+    # tables (host arrays, for inspection / pytree parity) only if somebody asks for them.
+    self._dynamic_mask = dynamic_mask
     self._device_tables: dict = {}
+
+  def _dynamic_info(self, is_dkv: bool) -> MaskInfo:
+    cfg = self.config
+    block = (cfg.block_q_dkv, cfg.block_kv_dkv) if is_dkv else (cfg.block_q, cfg.block_kv)
+    return mask_info_lib._process_dynamic_mask(self._dynamic_mask, block, is_dkv=is_dkv)  # pylint: disable=protected-access
+
+  @property
+  def fwd_mask_info(self) -> MaskInfo:
+    if self._fwd_mask_info is None and self._dynamic_mask is not None:
+      self._fwd_mask_info = self._dynamic_info(False)
+    return self._fwd_mask_info
+
+  @property
+  def dkv_mask_info(self) -> MaskInfo | None:
+    if self._dkv_mask_info is None and self._dynamic_mask is not None and self.config.has_backward_blocks:
+      self._dkv_mask_info = self._dynamic_info(True)
+    return self._dkv_mask_info
 
   # attribute views of kwargs
   config = property(lambda self: self.kwargs["config"])
@@ -371,7 +433,14 @@ class SplashAttentionKernel:
   mask_function_rule = property(lambda self: self.kwargs.get("mask_function_rule"))
   mask_shape = property(lambda self: self.kwargs["mask_shape"])
 
-  def _tables(self, device: torch.device) -> _DeviceTables:
+  def _tables(self, device: torch.device, batch: int = 1):
+    if self._dynamic_mask is not None:
+      if self._dynamic_mask.device != device:
+        raise ValueError(f"the mask lives on {self._dynamic_mask.device}, the inputs on {device}")
+      key = (device.type, device.index, int(batch))
+      if key not in self._device_tables:
+        self._device_tables[key] = _DynamicDeviceTables(self._dynamic_mask, int(batch))
+      return self._device_tables[key]
     key = (device.type, device.index)
     if key not in self._device_tables:
       self._device_tables[key] = _DeviceTables(self, device)
@@ -563,6 +632,13 @@ def _make_dynamic_splash_attention(
   if config is None:
     config = SplashConfig.get_default()
   config = dataclasses.replace(config, dq_reduction_steps=3)
+  if isinstance(mask, torch.Tensor) and mask.is_cuda:
+    # Device path: nothing of the mask goes through the host (the kernel object snapshots the
+    # tensor it is given; build a new one, which is cheap, when the mask changes).
+    return SplashAttentionKernel(
+        None, None, dynamic_mask=mask, config=config, is_mqa=is_mqa, save_residuals=save_residuals,
+        mask_value=mask_value, mask_function=None, mask_function_rule=None, mask_shape=tuple(mask.shape),
+        fwd_mask_sparsity=1.0, dkv_mask_sparsity=1.0)
   process = partial(
       mask_info_lib._process_dynamic_mask,  # pylint: disable=protected-access
       downcast_smem_data=downcast_smem_data,
