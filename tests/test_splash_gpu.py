@@ -3,6 +3,7 @@
 Tolerances are the ones the task states: forward output max-abs <= 1e-2, logsumexp <= 1e-3
 against the fp32 oracle; dQ / dK / dV relative L2 <= 1e-2.
 """
+import dataclasses
 import math
 
 import numpy as np
@@ -303,8 +304,9 @@ def test_unsupported_and_invalid_arguments():
   q = torch.zeros(2, s, D, dtype=torch.bfloat16, device=dev)
   with pytest.raises(NotImplementedError):
     kernel(q.float(), q.float(), q.float())
+  wide = torch.zeros(2, s, 256, dtype=torch.bfloat16, device=dev)
   with pytest.raises(NotImplementedError):
-    kernel(q[..., :64], q[..., :64], q[..., :64])
+    kernel(wide, wide, wide)
   with pytest.raises(ValueError):
     kernel(q[:, :128], q, q)
   with pytest.raises(RuntimeError):
@@ -313,3 +315,46 @@ def test_unsupported_and_invalid_arguments():
     splash.make_splash_mha(mask_lib.CausalMask((64, 64)), q_seq_shards=1,
                            config=splash.SplashConfig(block_q=16, block_kv=16))(
                                q[:, :64], q[:, :64], q[:, :64])
+
+
+@pytest.mark.parametrize("d_qk,d_v", [(64, 64), (96, 128), (128, 32)])
+def test_head_dims_below_128_run_zero_padded(d_qk, d_v):
+  """Reference head-dim cases (splash_attention_kernel_test.py:233-237) that fit one MMA tile."""
+  b, hq, hkv, s = 1, 4, 2, 384
+  g = torch.Generator().manual_seed(d_qk + d_v)
+  mk = lambda h, d: torch.randn(b, h, s, d, generator=g).to(torch.bfloat16)
+  q, k, v, do = mk(hq, d_qk), mk(hkv, d_qk), mk(hkv, d_v), mk(hq, d_v)
+  mask = mask_lib.CausalMask((s, s))
+  kernel = splash.make_splash_mha(mask, q_seq_shards=1, save_residuals=True)
+  dev = torch.device("cuda:0")
+  qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+  scale = 1 / math.sqrt(d_qk)
+  out, res = kernel(qd, kd, vd, logits_scale=scale)
+  assert out.shape == (b, hq, s, d_v)
+  out.backward(do.to(dev))
+  kernel.check_errors()
+  ro, rlse, _, rdq, rdk, rdv = attention_ref.fwd_bwd(q, k, v, do, _dense(mask), None, scale=scale)
+  assert ((out.float().cpu() - ro).abs() <= 1e-2 + 4e-3 * ro.abs()).all()
+  assert (res["logsumexp"].cpu() - rlse).abs().max().item() <= LSE_ATOL
+  assert qd.grad.shape == q.shape and kd.grad.shape == k.shape and vd.grad.shape == v.shape
+  assert _rel(qd.grad, rdq) <= GRAD_REL and _rel(kd.grad, rdk) <= GRAD_REL and _rel(vd.grad, rdv) <= GRAD_REL
+
+
+def test_seq_minor_layouts_give_the_head_dim_minor_result():
+  b, hq, hkv, s = 1, 4, 2, 256
+  q, k, v, do = _inputs(41, b, hq, hkv, s, s)
+  mask = mask_lib.CausalMask((s, s))
+  dev = torch.device("cuda:0")
+  plain = splash.make_splash_mha(mask, q_seq_shards=1)
+  cfg = dataclasses.replace(splash.SplashConfig.get_default(), q_layout=splash.QKVLayout.SEQ_MINOR,
+                            k_layout=splash.QKVLayout.SEQ_MINOR, v_layout=splash.QKVLayout.SEQ_MINOR)
+  minor = splash.make_splash_mha(mask, q_seq_shards=1, config=cfg)
+  qa, ka, va = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+  ref = plain(qa, ka, va, logits_scale=0.1)
+  ref.backward(do.to(dev))
+  qb, kb, vb = (t.to(dev).transpose(-1, -2).contiguous().requires_grad_(True) for t in (q, k, v))  # [B, H, D, S]
+  out = minor(qb, kb, vb, logits_scale=0.1)
+  out.backward(do.to(dev))
+  assert torch.equal(out, ref)
+  for got, want in ((qb.grad, qa.grad), (kb.grad, ka.grad), (vb.grad, va.grad)):
+    assert got.shape == want.transpose(-1, -2).shape and torch.equal(got.transpose(-1, -2), want)

@@ -77,8 +77,8 @@ class CudaSm100SplashAttention:
     s, k_heads = key.shape[-3], key.shape[-2]
     if list(key.shape[:-3]) != batch or list(value.shape[:-3]) != batch:
       raise ValueError("batch dimensions of query, key and value differ")
-    if h != 128 or value.shape[-1] != 128:
-      raise NotImplementedError(f"only head_dim 128 is built on B200, got {h}")
+    if h > 128 or value.shape[-1] > 128:
+      raise NotImplementedError(f"head dims above 128 are not built on B200, got {h} / {value.shape[-1]}")
     if t % 128 or s % 128:
       raise NotImplementedError("sequence lengths must be multiples of 128")
     scale = h ** -0.5 if logits_scale == AUTO else float(logits_scale)
@@ -112,7 +112,7 @@ class CudaSm100SplashAttention:
       return x.permute(0, 2, 1, 3)
 
     out, res = kernel(bhtd(query), bhtd(key), bhtd(value), logits_scale=scale)
-    out = out.permute(0, 2, 1, 3).reshape(tuple(batch) + (t, n, h))
+    out = out.permute(0, 2, 1, 3).reshape(tuple(batch) + (t, n, value.shape[-1]))
     if return_residuals:
       shape = tuple(batch) + (n, t)
       return out, (res["max_logits"].reshape(shape), res["logsumexp"].reshape(shape))

@@ -464,18 +464,23 @@ class SplashAttentionKernel:
       raise ValueError(f"Only one of max_logit_const={cfg.max_logit_const} and {max_logit_value=} can be set.")
     if cfg.attn_logits_soft_cap is not None and not cfg.attn_logits_soft_cap > 0:
       raise ValueError(f"attn_logits_soft_cap must be positive, got {cfg.attn_logits_soft_cap}")
-    if any(l != QKVLayout.HEAD_DIM_MINOR for l in (cfg.q_layout, cfg.k_layout, cfg.v_layout)):
-      raise NotImplementedError("only HEAD_DIM_MINOR layouts are built on B200")
     if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16:
       raise NotImplementedError(f"only bfloat16 inputs are built on B200, got {q.dtype}")
-    if q.shape[-1] != _HEAD_DIM:
-      raise NotImplementedError(f"only head_dim {_HEAD_DIM} is built on B200, got {q.shape[-1]}")
 
   def __call__(self, q, k, v, segment_ids: SegmentIds | None = None, sinks=None, *,
                max_logit_value=None, logits_scale: float = 1.0, **overrides):
     kw = dict(self.kwargs, **overrides)
     save_residuals = kw.get("save_residuals", False)
     self._reject_unsupported(q, k, sinks, max_logit_value)
+    # SEQ_MINOR operands ([..., head_dim, seq], reference kernel.py:51-54) are viewed head-dim-minor;
+    # the kernels take head_dim-contiguous tiles, so such an operand is copied once on the way in.
+    cfg = self.config
+    if cfg.q_layout == QKVLayout.SEQ_MINOR:
+      q = q.transpose(-1, -2)
+    if cfg.k_layout == QKVLayout.SEQ_MINOR:
+      k = k.transpose(-1, -2)
+    if cfg.v_layout == QKVLayout.SEQ_MINOR:
+      v = v.transpose(-1, -2)
     batched = q.dim() == 4
     is_mqa = self.is_mqa
     if not batched:
@@ -492,8 +497,19 @@ class SplashAttentionKernel:
       raise ValueError(f"Sequence lengths {q.shape[2]}, {k.shape[2]} do not match the mask {self.mask_shape}")
     if k.shape[1] == 0 or q.shape[1] % k.shape[1] != 0:
       raise ValueError(f"q heads ({q.shape[1]}) must be a multiple of kv heads ({k.shape[1]})")
-    if v.shape[-1] != q.shape[-1]:
-      raise NotImplementedError("head_dim_v != head_dim_qk is not built on B200 yet")
+    # The MMA tiles are 128 wide.  Smaller head dims run zero-padded (q k^T and p v are unchanged
+    # by zero columns; the padding of the output and of the gradients is sliced off again), at
+    # the cost of the padded work; larger ones are not built.
+    d_qk, d_v = q.shape[-1], v.shape[-1]
+    if k.shape[-1] != d_qk:
+      raise ValueError(f"q and k head dims differ: {d_qk} vs {k.shape[-1]}")
+    if d_qk > _HEAD_DIM or d_v > _HEAD_DIM:
+      raise NotImplementedError(f"head dims above {_HEAD_DIM} are not built on B200, got {d_qk} / {d_v}")
+    if d_qk < _HEAD_DIM:
+      q = torch.nn.functional.pad(q, (0, _HEAD_DIM - d_qk))
+      k = torch.nn.functional.pad(k, (0, _HEAD_DIM - d_qk))
+    if d_v < _HEAD_DIM:
+      v = torch.nn.functional.pad(v, (0, _HEAD_DIM - d_v))
     q_seg = kv_seg = None
     if segment_ids is not None:
       q_seg = torch.as_tensor(segment_ids.q, device=q.device).to(torch.int32)
@@ -518,6 +534,8 @@ class SplashAttentionKernel:
       max_logit = value.reshape(-1).expand(hq).contiguous()
     o, lse, max_logits = _SplashFunction.apply(q, k, v, q_seg, kv_seg, self, float(logits_scale), sinks,
                                                max_logit)
+    if d_v < _HEAD_DIM:
+      o = o[..., :d_v]
     if not batched:
       o, lse, max_logits = o[0], lse[0], max_logits[0]
     if save_residuals:
