@@ -311,7 +311,31 @@ def cpu_baseline(w: dict, seconds_budget: float = 20.0) -> dict:
       "kind": "port",
       "sample": (f"1 batch row x 1 kv head ({group} q heads) of {w['mask']} seq {s}, fwd+bwd, {reps} reps in "
                  f"{dt:.1f} s; torch-CPU fp32 restatement of the reference's attention_reference[_vjp]"),
+      "maskinfo_build_ms": maskinfo_build_times(w),
   }
+
+
+def maskinfo_build_times(w: dict) -> dict:
+  """Host time to build the forward MaskInfo of the workload's mask: the native builder against the
+  numpy restatement of the reference's block-by-block `_process_mask` (capped at 16384 tokens for the
+  restatement, whose cost grows with the number of blocks times the block area)."""
+  from oracle import maskinfo_ref
+  from tokamax_b200 import splash_attention_mask as mask_lib
+  from tokamax_b200 import splash_attention_mask_info as mask_info_lib
+
+  def build(s):
+    return mask_lib.CausalMask((s, s)) if w["mask"] == "causal" else mask_lib.LocalMask((s, s), (4096, 0), 0)
+
+  s = w["seq"]
+  mask_info_lib._process_mask.cache_clear()  # pylint: disable=protected-access
+  t0 = time.perf_counter()
+  mask_info_lib.process_mask(build(s), (128, 128))
+  native_ms = (time.perf_counter() - t0) * 1e3
+  s_ref = min(s, 16384)
+  t0 = time.perf_counter()
+  maskinfo_ref.process_mask(build(s_ref), (128, 128), False)
+  port_ms = (time.perf_counter() - t0) * 1e3
+  return {"native": native_ms, "native_seq": s, "port": port_ms, "port_seq": s_ref}
 
 
 # ----------------------------------------------------------------------------------------------

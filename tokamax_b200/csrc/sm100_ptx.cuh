@@ -327,6 +327,12 @@ __device__ __forceinline__ float tanh_ex2(float y) {
   const float e = ex2(y * 2.8853900817779268f);
   return 1.0f - __fdividef(2.0f, e + 1.0f);
 }
+// Three-input maximum (one instruction on sm_100).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));

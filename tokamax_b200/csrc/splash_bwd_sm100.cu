@@ -1,7 +1,8 @@
 // Splash attention backward for sm_100a: bf16 inputs, head_dim 128, fp32 accumulation.
 //
 // Three kernels, all atomic-free and bitwise repeatable:
-//   1. delta      : di[b,h,q] = sum_d o * do                      (HBM-bound elementwise pass)
+//   1. delta      : -di[b,h,q] = -sum_d o * do  (stored negated: dP + (-di) is an add, which has a
+//                   two-wide form)                                   (HBM-bound elementwise pass)
 //   2. dq kernel  : one CTA per (q tile, q head).  Per kv tile: S = Q K^T, dP = dO V^T,
 //                   dS = P o (dP - di), dQ += dS K.
 //   3. dkv kernel : one CTA per (kv tile, kv head).  Loops over the q heads that share the kv
@@ -36,7 +37,7 @@ struct DeltaParams {
   const __nv_bfloat16* o;
   const __nv_bfloat16* d_o;
   int64_t o_sb, o_sh, o_ss, do_sb, do_sh, do_ss;
-  float* delta;      // [B, Hq, Sq]
+  float* delta;      // [B, Hq, Sq]  -sum_d(o * do)
   const float* lse;  // [B, Hq, Sq] natural log
   float* nlse2;      // [B, Hq, Sq]  -lse * log2(e): the exponent offset the MMA kernels subtract
   int q_heads, q_len;
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(256) splash_delta_kernel(const DeltaParams p) 
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
   if (lane == 0) {
-    p.delta[row] = acc;
+    p.delta[row] = -acc;
     // Rows that never met a live key carry the mask value as logsumexp; -inf keeps their
     // probabilities at exactly zero instead of overflowing the product to +inf.
     const float lse = p.lse[row];
@@ -85,7 +86,7 @@ struct BwdParams {
   __nv_bfloat16* out1;
   int64_t out1_sb, out1_sh, out1_ss;
   const float* nlse2;  // [B, Hq, Sq]  -logsumexp * log2(e)
-  const float* delta;  // [B, Hq, Sq]
+  const float* delta;  // [B, Hq, Sq]  -sum_d(o * do)
   const int32_t* q_seg;
   const int32_t* kv_seg;
   const int32_t* q_sequence;
@@ -312,7 +313,7 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int32_t* kv_seg_row = has_seg ? p.kv_seg + (int64_t)batch * p.kv_len : nullptr;
     const int64_t stat = ((int64_t)batch * p.q_heads + head) * p.q_len + q_row;
     const float nlse2 = p.nlse2[stat];
-    const float delta = p.delta[stat];
+    const float ndelta = p.delta[stat];  // -di
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
     const float c = kSoftCap ? p.soft_cap * kLog2e : p.scale_log2;
     bool ok = true;
@@ -385,8 +386,14 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           pr[j] = ex2(fmaf(pr[j], c, nlse2)) * fmaf(-t, t, 1.0f);
         }
       } else {
+        // issue-bound: two-wide fp32 fma for the exponent arguments
+        const float2 c2 = make_float2(c, c), nl2 = make_float2(nlse2, nlse2);
 #pragma unroll
-        for (int j = 0; j < 64; ++j) pr[j] = ex2(fmaf(pr[j], c, nlse2));
+        for (int j = 0; j < 64; j += 2) {
+          const float2 x = __ffma2_rn(make_float2(pr[j], pr[j + 1]), c2, nl2);
+          pr[j] = ex2(x.x);
+          pr[j + 1] = ex2(x.y);
+        }
       }
 
       ok = mbar_wait(&bars->dp_full, n & 1u, ab, 0x1410u);
@@ -399,12 +406,15 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         tmem_ld32(tmem + lane_addr + 2 * kTile + w * 64, v0);
         tmem_ld32(tmem + lane_addr + 2 * kTile + w * 64 + 32, v1);
         tmem_ld_wait();
+        const float2 nd2 = make_float2(ndelta, ndelta);
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          pk[j] = pack_bf16(pr[2 * j] * (__uint_as_float(v0[2 * j]) - delta),
-                            pr[2 * j + 1] * (__uint_as_float(v0[2 * j + 1]) - delta));
-          pk[16 + j] = pack_bf16(pr[32 + 2 * j] * (__uint_as_float(v1[2 * j]) - delta),
-                                 pr[32 + 2 * j + 1] * (__uint_as_float(v1[2 * j + 1]) - delta));
+        for (int j = 0; j < 16; ++j) {  // dS = p * (dP - di), two elements per instruction
+          const float2 a = __fmul2_rn(make_float2(pr[2 * j], pr[2 * j + 1]),
+                                      __fadd2_rn(make_float2(__uint_as_float(v0[2 * j]), __uint_as_float(v0[2 * j + 1])), nd2));
+          const float2 b = __fmul2_rn(make_float2(pr[32 + 2 * j], pr[32 + 2 * j + 1]),
+                                      __fadd2_rn(make_float2(__uint_as_float(v1[2 * j]), __uint_as_float(v1[2 * j + 1])), nd2));
+          pk[j] = pack_bf16(a.x, a.y);
+          pk[16 + j] = pack_bf16(b.x, b.y);
         }
       }
       tmem_st32(t_s + packed_col(w), pk);
@@ -762,10 +772,14 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
               for (int u = 0; u < 4; ++u) th[u] = fmaxf(pr[4 * t + u], -1.0f);
             }
-            pr[4 * t + 0] = ex2(fmaf(pr[4 * t + 0], c, nl.x));
-            pr[4 * t + 1] = ex2(fmaf(pr[4 * t + 1], c, nl.y));
-            pr[4 * t + 2] = ex2(fmaf(pr[4 * t + 2], c, nl.z));
-            pr[4 * t + 3] = ex2(fmaf(pr[4 * t + 3], c, nl.w));
+            const float2 xa = __ffma2_rn(make_float2(pr[4 * t + 0], pr[4 * t + 1]), make_float2(c, c),
+                                         make_float2(nl.x, nl.y));
+            const float2 xb = __ffma2_rn(make_float2(pr[4 * t + 2], pr[4 * t + 3]), make_float2(c, c),
+                                         make_float2(nl.z, nl.w));
+            pr[4 * t + 0] = ex2(xa.x);
+            pr[4 * t + 1] = ex2(xa.y);
+            pr[4 * t + 2] = ex2(xb.x);
+            pr[4 * t + 3] = ex2(xb.y);
             pk[2 * t] = pack_bf16(pr[4 * t + 0], pr[4 * t + 1]);
             pk[2 * t + 1] = pack_bf16(pr[4 * t + 2], pr[4 * t + 3]);
             if constexpr (kSoftCap) {  // dS = (p * (1 - tanh^2)) * (dP - di): fold the factor into p
@@ -790,11 +804,15 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           tmem_ld_wait();
 #pragma unroll
           for (int t = 0; t < 8; ++t) {
-            const float4 da = dl4[t];
-            pk[2 * t] = pack_bf16(pr[4 * t + 0] * (__uint_as_float(v[4 * t + 0]) - da.x),
-                                  pr[4 * t + 1] * (__uint_as_float(v[4 * t + 1]) - da.y));
-            pk[2 * t + 1] = pack_bf16(pr[4 * t + 2] * (__uint_as_float(v[4 * t + 2]) - da.z),
-                                      pr[4 * t + 3] * (__uint_as_float(v[4 * t + 3]) - da.w));
+            const float4 nd = dl4[t];  // -di of the four query columns
+            const float2 a = __fmul2_rn(make_float2(pr[4 * t + 0], pr[4 * t + 1]),
+                                        __fadd2_rn(make_float2(__uint_as_float(v[4 * t + 0]), __uint_as_float(v[4 * t + 1])),
+                                                   make_float2(nd.x, nd.y)));
+            const float2 b = __fmul2_rn(make_float2(pr[4 * t + 2], pr[4 * t + 3]),
+                                        __fadd2_rn(make_float2(__uint_as_float(v[4 * t + 2]), __uint_as_float(v[4 * t + 3])),
+                                                   make_float2(nd.z, nd.w)));
+            pk[2 * t] = pack_bf16(a.x, a.y);
+            pk[2 * t + 1] = pack_bf16(b.x, b.y);
           }
           tmem_st16(t_dpt, pk);
           tmem_st_wait();

@@ -434,14 +434,19 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
       }
 
-      float mx0 = s[0], mx1 = s[1], mx2 = s[2], mx3 = s[3];
+      // The softmax warps are bound by instruction issue, so the per-element work uses the
+      // two-wide fp32 instructions of sm_100 (fma / add on register pairs) and three-input max.
+      float mx0 = max3(s[0], s[1], s[2]), mx1 = max3(s[3], s[4], s[5]);
+      float mx2 = max3(s[6], s[7], s[8]), mx3 = max3(s[9], s[10], s[11]);
 #pragma unroll
-      for (int j = 4; j < kTile; j += 4) {
-        mx0 = fmaxf(mx0, s[j]);
-        mx1 = fmaxf(mx1, s[j + 1]);
-        mx2 = fmaxf(mx2, s[j + 2]);
-        mx3 = fmaxf(mx3, s[j + 3]);
+      for (int j = 12; j < kTile - 4; j += 8) {
+        mx0 = max3(mx0, s[j], s[j + 1]);
+        mx1 = max3(mx1, s[j + 2], s[j + 3]);
+        mx2 = max3(mx2, s[j + 4], s[j + 5]);
+        mx3 = max3(mx3, s[j + 6], s[j + 7]);
       }
+      mx0 = max3(mx0, s[kTile - 4], s[kTile - 3]);
+      mx1 = max3(mx1, s[kTile - 2], s[kTile - 1]);
       const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3));
       const float m_new = fmaxf(mx * c, kLogitFloor);
       m_true = fmaxf(m_true, kFp8 ? m_new : mx);  // e4m3: log2 units (the scale varies by tile)
@@ -487,19 +492,26 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         l += (ls0 + ls1) * __fdividef(0.015625f, r);  // back to exp2(s - m) units (2^-6 / r)
       } else {
+        const float2 c2 = make_float2(c, c), nm2 = make_float2(-m_used, -m_used);
+        float2 lsa = make_float2(0.f, 0.f), lsb = make_float2(0.f, 0.f);
 #pragma unroll
         for (int g = 0; g < 4; ++g) {
           uint32_t pk[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float p0 = ex2(fmaf(s[g * 32 + 2 * j], c, -m_used));
-            const float p1 = ex2(fmaf(s[g * 32 + 2 * j + 1], c, -m_used));
-            ls0 += p0;
-            ls1 += p1;
-            pk[j] = pack_bf16(p0, p1);
+          for (int j = 0; j < 16; j += 2) {
+            const float2 xa = __ffma2_rn(make_float2(s[g * 32 + 2 * j], s[g * 32 + 2 * j + 1]), c2, nm2);
+            const float2 xb = __ffma2_rn(make_float2(s[g * 32 + 2 * j + 2], s[g * 32 + 2 * j + 3]), c2, nm2);
+            const float2 pa = make_float2(ex2(xa.x), ex2(xa.y));
+            const float2 pb = make_float2(ex2(xb.x), ex2(xb.y));
+            lsa = __fadd2_rn(lsa, pa);
+            lsb = __fadd2_rn(lsb, pb);
+            pk[j] = pack_bf16(pa.x, pa.y);
+            pk[j + 1] = pack_bf16(pb.x, pb.y);
           }
           tmem_st16(t_s + g * 16, pk);
         }
+        ls0 = lsa.x + lsb.x;
+        ls1 = lsa.y + lsb.y;
         l += ls0 + ls1;
       }
       tmem_st_wait();

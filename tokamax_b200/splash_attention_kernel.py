@@ -382,7 +382,7 @@ def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg
   with torch.cuda.device(q.device):
     _native.check(lib.splash_bwd(C.byref(args), C.c_void_p(stream)), "splash_bwd")
   n = q.shape[0] * q.shape[1] * q.shape[2]
-  di = workspace[:4 * n].view(torch.float32).view(q.shape[0], q.shape[1], q.shape[2])
+  di = -workspace[:4 * n].view(torch.float32).view(q.shape[0], q.shape[1], q.shape[2])  # stored negated
   return dq, dk, dv, di
 
 
