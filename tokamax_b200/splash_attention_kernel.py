@@ -335,22 +335,23 @@ class _SplashFunction(torch.autograd.Function):
   @staticmethod
   def backward(ctx, d_o, _dlse, _dmax):
     q, k, v, o, lse, q_seg, kv_seg, sinks = ctx.saved_tensors
-    dq, dk, dv, di = splash_backward(ctx.kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale)
+    dq, dk, dv, neg_di = splash_backward(ctx.kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale)
     dsinks = None
     if sinks is not None:
       # reference kernel.py:1928-1935: dsinks[h] = -sum_rows exp(sink - lse) * sum_d(o * do)
-      dsinks = -(torch.exp(sinks[None, :, None] - lse) * di).sum(dim=(0, 2)).to(ctx.sinks_dtype)
+      dsinks = (torch.exp(sinks[None, :, None] - lse) * neg_di).sum(dim=(0, 2)).to(ctx.sinks_dtype)
     return dq, dk, dv, None, None, None, None, dsinks, None
 
 
 def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg=None, kv_seg=None,
                     scale: float = 1.0):
-  """One `splash_bwd` call: ``(dq, dk, dv, di)`` for batched ``[B, H, S, 128]`` bf16 tensors.
+  """One `splash_bwd` call: ``(dq, dk, dv, neg_di)`` for batched ``[B, H, S, 128]`` bf16 tensors.
 
   ``o`` and ``lse`` are the forward's output and logsumexp for these q rows; they may come from a
   softmax over more keys than ``k`` holds (ring attention passes the merged values, reference
   ring_attention_kernel.py:228-262), in which case dq / dk / dv are this key shard's share.
-  ``di`` is the fp32 row sum ``sum_d(o * do)`` ``[B, Hq, Sq]`` the backward leaves in its workspace.
+  ``neg_di`` is ``-sum_d(o * do)`` (fp32 ``[B, Hq, Sq]``), a view of the backward's workspace, which
+  keeps the row sums negated.
   """
   tables = kernel._tables(q.device, q.shape[0])  # pylint: disable=protected-access
   d_o = _usable(d_o)
@@ -382,8 +383,8 @@ def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg
   with torch.cuda.device(q.device):
     _native.check(lib.splash_bwd(C.byref(args), C.c_void_p(stream)), "splash_bwd")
   n = q.shape[0] * q.shape[1] * q.shape[2]
-  di = -workspace[:4 * n].view(torch.float32).view(q.shape[0], q.shape[1], q.shape[2])  # stored negated
-  return dq, dk, dv, di
+  neg_di = workspace[:4 * n].view(torch.float32).view(q.shape[0], q.shape[1], q.shape[2])
+  return dq, dk, dv, neg_di
 
 
 class SplashAttentionKernel:
