@@ -302,6 +302,13 @@ typedef struct SplashBwdArgs {
 size_t splash_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
 int splash_bwd(const SplashBwdArgs* args, void* cuda_stream);
 
+/* Ring attention (ring_attention_kernel.py:150-158): folds one ring step's partial result
+ * (o_i bf16 [n_rows, 128], its logsumexp lse_i [n_rows]) into the running fp32 pair in place:
+ * lse_acc <- log(exp(lse_acc) + exp(lse_i)), o_acc <- the logsumexp-weighted mean.  Start with
+ * o_acc = 0, lse_acc = -inf.  n_rows = batch * q_heads * q_len of contiguous rows. */
+int splash_ring_merge(float* o_acc, float* lse_acc, const void* o_i, const float* lse_i, int64_t n_rows,
+                      int64_t head_dim, void* cuda_stream);
+
 /* Backward pass for callers that cannot obtain device memory at the point of the call.
  * (No counterpart in the reference; it exists only on this side of the boundary.)
  *

@@ -157,3 +157,26 @@ def test_ring_matches_single_gpu_on_two_gpus():
   for p in procs:
     p.join(timeout=60)
   assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+def test_fused_merge_matches_the_torch_formula():
+  g = torch.Generator().manual_seed(9)
+  b, h, s = 2, 3, 200
+  o_acc = torch.randn(b, h, s, D, generator=g)
+  lse_acc = torch.randn(b, h, s, generator=g) * 3
+  o_i = torch.randn(b, h, s, D, generator=g).to(torch.bfloat16)
+  lse_i = torch.randn(b, h, s, generator=g) * 3
+  lse_acc[0, 0, :5] = -float("inf")      # nothing merged yet
+  lse_i[0, 1, :5] = -2.0e38              # no live key on this shard
+  lse_acc[1, 2, :3] = -2.0e38
+  lse_i[1, 2, :3] = -2.0e38              # dead on both
+  want_o, want_l = o_acc.clone(), lse_acc.clone()
+  ring.merge_partial(want_o, want_l, o_i, lse_i)  # host tensors: the torch form
+  got_o, got_l = o_acc.to(DEV), lse_acc.to(DEV)
+  ring.merge_partial(got_o, got_l, o_i.to(DEV), lse_i.to(DEV))
+  torch.testing.assert_close(got_o.cpu(), want_o, rtol=2e-5, atol=2e-5)
+  finite = torch.isfinite(want_l)
+  torch.testing.assert_close(got_l.cpu()[finite], want_l[finite], rtol=2e-6, atol=2e-5)
+  assert torch.equal(got_o.cpu()[0, 0, :5], o_i[0, 0, :5].float())
+  with pytest.raises(ValueError):
+    ring.merge_partial(got_o, got_l, o_i.float().to(DEV), lse_i.to(DEV))

@@ -25,6 +25,7 @@ SOURCES = (
     "maskinfo_builder.cc",
     "segment_schedule.cu",
     "dynamic_schedule.cu",
+    "ring_merge.cu",
 )
 
 NVCC_FLAGS = (
@@ -184,6 +185,7 @@ _PROTOTYPES = {
                                           C.c_void_p, C.c_size_t, C.POINTER(SplashDeviceSchedule), C.c_void_p]),
     "splash_fwd": (C.c_int, [C.POINTER(SplashFwdArgs), C.c_void_p]),
     "splash_fwd_fp8": (C.c_int, [C.POINTER(SplashFwdFp8Args), C.c_void_p]),
+    "splash_ring_merge": (C.c_int, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]),
     "splash_bwd_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "splash_bwd": (C.c_int, [C.POINTER(SplashBwdArgs), C.c_void_p]),
     "splash_bwd_static_scratch": (C.c_int, [C.POINTER(SplashBwdArgs), C.c_void_p]),

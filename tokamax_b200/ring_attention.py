@@ -113,11 +113,28 @@ def merge_partial(o_acc: torch.Tensor, lse_acc: torch.Tensor, o_i: torch.Tensor,
   Same arithmetic as the reference's (m, l, o) carry (:150-158) written on logsumexp: the merged
   output is the logsumexp-weighted mean of the partial outputs.
   """
-  lse_new = torch.logaddexp(lse_acc, lse_i)
-  w_acc = torch.exp(lse_acc - lse_new).unsqueeze(-1)
-  w_i = torch.exp(lse_i - lse_new).unsqueeze(-1)
-  o_acc.mul_(w_acc).addcmul_(o_i.float(), w_i)
-  lse_acc.copy_(lse_new)
+  if o_acc.is_cuda:  # one fused pass (splash_ring_merge); the torch form below serves host tensors only
+    if not (o_i.dtype == torch.bfloat16 and o_acc.shape[-1] == 128 and o_acc.is_contiguous()
+            and o_i.is_contiguous() and lse_acc.is_contiguous() and lse_i.is_contiguous()):
+      raise ValueError("merge_partial on a CUDA device takes contiguous fp32 / bf16 tensors with head_dim 128")
+    import ctypes as C
+    from tokamax_b200 import _native
+
+    stream = C.c_void_p(torch.cuda.current_stream(o_acc.device).cuda_stream)
+    with torch.cuda.device(o_acc.device):
+      _native.check(_native.lib().splash_ring_merge(o_acc.data_ptr(), lse_acc.data_ptr(), o_i.data_ptr(),
+                                                    lse_i.data_ptr(), lse_acc.numel(), 128, stream),
+                    "splash_ring_merge")
+    return
+  # Weights from the larger of the two logsumexps, as in the kernel: exact also where both are the
+  # (huge, finite) mask value, which `logaddexp` cannot move by log 2 in fp32.
+  m = torch.maximum(lse_acc, lse_i)
+  m_safe = torch.where(torch.isinf(m), torch.zeros_like(m), m)
+  e_acc, e_i = torch.exp(lse_acc - m_safe), torch.exp(lse_i - m_safe)
+  total = e_acc + e_i
+  inv = torch.where(total > 0, 1.0 / total, torch.zeros_like(total))
+  o_acc.mul_((e_acc * inv).unsqueeze(-1)).addcmul_(o_i.float(), (e_i * inv).unsqueeze(-1))
+  lse_acc.copy_(torch.where(total > 0, m_safe + torch.log(total), m))
 
 
 # ----------------------------------------------------------------------------------------------
