@@ -9,8 +9,9 @@
 //                   head and their active q tiles: S^T = K Q^T, dP^T = V dO^T, dV += P^T dO,
 //                   dK += dS^T Q.  The whole GQA group is summed in the CTA's fp32 TMEM
 //                   accumulators, so dK/dV need no atomics and no second pass.
-// In both MMA kernels P / dS are written back to TMEM as bf16 and consumed as the A operand of
-// the next MMA; K, V, Q and dO tiles are each staged once by TMA and read both K-major and
+// P (and dS in the dq kernel) is written back to TMEM as bf16 and consumed as the A operand of the
+// next MMA; the dkv kernel's dS^T goes through shared memory instead, which frees its TMEM columns
+// a step earlier.  K, V, Q and dO tiles are each staged once by TMA and read both K-major and
 // MN-major from the same 128-byte-swizzled shared-memory image.
 //
 // Arithmetic follows the reference backward
@@ -462,17 +463,9 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // ------------------------------------------------------------------------------------------
 // dkv kernel
 // ------------------------------------------------------------------------------------------
-// The q tile of a step is processed as two 64-column halves so that the score tiles can be
-// double-buffered next to the two 128-column accumulators:
-//   TMEM: S^T0 [0,64) | S^T1 [64,128) | dP^T0 [128,192) | dP^T1 [192,256) | dK [256,384) | dV [384,512)
-// While the compute warps turn S^T / dP^T of half h+1 into P^T / dS^T, the tensor core runs
-// dV += P^T dO and dK += dS^T Q of half h and the score MMAs of half h+2.
-constexpr int kDkvStatsBytes = (kBwdStages / 2) * 2 * kTile * 4;
-constexpr int kDkvSmemBytes = (2 + kBwdStages) * kTileBytes + kDkvStatsBytes + 1024 + 1024;
-
-// 16 compute warps (two groups of 8, one per q-tile half, each thread 32 score columns) keep the
-// P^T / dS^T phases short; warp 16 feeds TMA, warp 17 issues MMAs, warps 18-19 only complete the
-// fifth warpgroup so registers can be handed to the compute warpgroups.
+// 16 compute warps (thread = kv row x one 32-column quarter of the q tile) keep the P^T / dS^T
+// phases short; warp 16 feeds TMA, warp 17 issues MMAs, warps 18-19 only complete the fifth
+// warpgroup so registers can be handed to the compute warpgroups.
 constexpr int kDkvThreads = 640;
 constexpr int kDkvTmaWarp = 16;
 constexpr int kDkvMmaWarp = 17;
@@ -481,34 +474,50 @@ constexpr int kDkvMmaWarp = 17;
 constexpr int kDkvComputeRegs = 104;
 constexpr int kDkvIssueRegs = 56;
 
+// One CTA = one kv tile of one (batch, kv head); the q heads of the GQA group and the active q
+// tiles are looped inside and dK / dV of the whole group accumulate in TMEM in fp32 (no atomics,
+// bitwise repeatable).  A q tile is processed whole: the score MMAs run with N = 128 (an N = 64 SS
+// MMA reads 6 KB of shared memory for 32 cycles of tensor time and so runs at about 60 % of the
+// N = 128 rate; a version that double-buffered 64-column halves of the q tile was 21 % slower).
+//   TMEM: S^T [0,128) | dP^T [128,256) | dK [256,384) | dV [384,512)
+// S^T and dP^T are single-buffered.  P^T goes back to TMEM over S^T (A operand of dV += P^T dO);
+// dS^T goes to shared memory in the K-major 128-byte-swizzled layout of an operand tile (A operand
+// of dK += dS^T Q), which frees the dP^T columns for the next step as soon as they have been
+// read.  Issue order of step n:  wait P^T(n) | dV(n) | S^T(n+1) | wait dS^T(n) | dK(n) | dP^T(n+1)
+// — the tensor pipe executes in order, so S^T(n+1) cannot overtake dV(n)'s read of P^T(n), and
+// dP^T(n+1) is issued only after the compute warps have consumed dP^T(n).
+constexpr int kDkvStatsBytes = (kBwdStages / 2) * 2 * kTile * 4;
+constexpr int kDkvSmemBytes = (3 + kBwdStages) * kTileBytes + kDkvStatsBytes + 512;
+
 struct DkvBarriers {
   uint64_t stat_full[2];
   uint64_t ring_full[kBwdStages];
   uint64_t ring_empty[kBwdStages];
-  uint64_t st_full[2];
-  uint64_t dpt_full[2];
-  uint64_t p_full[2];
-  uint64_t ds_full[2];
+  uint64_t st_full;
+  uint64_t dpt_full;
+  uint64_t p_full;
+  uint64_t ds_full;
+  uint64_t ds_free;   // dK(n) has finished reading the dS^T tile in shared memory
   uint64_t acc_done;
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t early_exit;
 };
+static_assert(sizeof(DkvBarriers) <= 512, "barrier block");
 
 template <bool kSoftCap>
 __global__ void __launch_bounds__(kDkvThreads, 1)
 splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
-                  const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
-                  const BwdParams p) {
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
-                                             ~static_cast<uintptr_t>(1023));
+                       const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
+                       const BwdParams p) {
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw;
   uint8_t* k_smem = smem;
   uint8_t* v_smem = smem + kTileBytes;
-  uint8_t* ring = smem + 2 * kTileBytes;
-  // per-step row statistics of the q tile in flight: [slot][0: -lse*log2e | 1: di][128]
-  float* stats = reinterpret_cast<float*>(smem + (2 + kBwdStages) * kTileBytes);
-  DkvBarriers* bars = reinterpret_cast<DkvBarriers*>(smem + (2 + kBwdStages) * kTileBytes + kDkvStatsBytes);
+  uint8_t* ds_smem = smem + 2 * kTileBytes;
+  uint8_t* ring = smem + 3 * kTileBytes;
+  float* stats = reinterpret_cast<float*>(smem + (3 + kBwdStages) * kTileBytes);
+  DkvBarriers* bars = reinterpret_cast<DkvBarriers*>(smem + (3 + kBwdStages) * kTileBytes + kDkvStatsBytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -522,10 +531,20 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const int4* entries = p.entries + (int64_t)batch * p.entries_per_batch;
   const int n_ent = eend - ebeg;
   const int n_steps = n_ent * group;
-  const int n_half = 2 * n_steps;
 
   if (threadIdx.x == 0) {
-    bars->early_exit = *reinterpret_cast<volatile uint32_t*>(p.err);
+    // The operand tiles need a 1024-byte aligned base for the 128-byte swizzle; there is no
+    // slack in the allocation to fix it up, so a misaligned window is reported, not used.
+    uint32_t bad = *reinterpret_cast<volatile uint32_t*>(p.err);
+    if ((smem_u32(smem) & 1023u) != 0u) {
+      if (atomicCAS(p.err, 0u, 2u) == 0u) {
+        p.err[1] = blockIdx.x;
+        p.err[2] = 0x2f00u;
+        p.err[3] = smem_u32(smem);
+      }
+      bad = 2u;
+    }
+    bars->early_exit = bad;
     bars->abort_flag = 0;
     mbar_init(&bars->stat_full[0], 1);
     mbar_init(&bars->stat_full[1], 1);
@@ -533,12 +552,11 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(&bars->ring_full[s], 1);
       mbar_init(&bars->ring_empty[s], 1);
     }
-    for (int i = 0; i < 2; ++i) {
-      mbar_init(&bars->st_full[i], 1);
-      mbar_init(&bars->dpt_full[i], 1);
-      mbar_init(&bars->p_full[i], 8);   // one arrival per warp of the half's group
-      mbar_init(&bars->ds_full[i], 8);
-    }
+    mbar_init(&bars->st_full, 1);
+    mbar_init(&bars->dpt_full, 1);
+    mbar_init(&bars->p_full, 16);   // one arrival per compute warp
+    mbar_init(&bars->ds_full, 16);
+    mbar_init(&bars->ds_free, 1);
     mbar_init(&bars->acc_done, 1);
     mbar_fence_init();
   }
@@ -577,7 +595,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           const int qt = entries[e].x;
           for (int which = 0; which < 2 && ok; ++which, ++it) {
             const uint32_t s = it % kBwdStages;
-            ok = mbar_wait(&bars->ring_empty[s], ((it / kBwdStages) & 1u) ^ 1u, ab, 0x2100u + s);
+            ok = mbar_wait(&bars->ring_empty[s], ((it / kBwdStages) & 1u) ^ 1u, ab, 0x3100u + s);
             if (!ok) break;
             uint8_t* dst = ring + s * kTileBytes;
             const CUtensorMap* tm = which == 0 ? &tm_q : &tm_do;
@@ -595,74 +613,71 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
   } else if (warp == kDkvMmaWarp) {
     if (lane == 0 && n_steps > 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(kTile, 64, false, false);
+      constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kTile, false, false);
       constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, kHeadDim, false, true);
-      const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem), ring_addr = smem_u32(ring);
-      const uint32_t t_dk = tmem + 2 * kTile, t_dv = tmem + 3 * kTile;
-      // scores of half h: S^T = K Q_h^T and dP^T = V dO_h^T, 128 x 64, K = head_dim
-      auto issue_scores = [&](int h) {
-        const int n = h >> 1, hh = h & 1;
-        const uint32_t q_slot = ring_addr + ((2 * n) % kBwdStages) * kTileBytes + hh * 8192;
-        const uint32_t do_slot = ring_addr + ((2 * n + 1) % kBwdStages) * kTileBytes + hh * 8192;
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(tmem + hh * 64, make_smem_desc_sw128(k_addr + off, 16, 1024),
-                  make_smem_desc_sw128(q_slot + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
-        }
-        tc_commit(&bars->st_full[hh]);
-#pragma unroll
-        for (int k = 0; k < 8; ++k) {
-          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(tmem + kTile + hh * 64, make_smem_desc_sw128(v_addr + off, 16, 1024),
-                  make_smem_desc_sw128(do_slot + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
-        }
-        tc_commit(&bars->dpt_full[hh]);
-      };
-      // acc (+)= A_h B_h with A = packed bf16 [128 x 64] in TMEM, B = 64 rows of a q-side tile read
-      // MN-major.  K = 64 -> four K=16 slices; each 32-column quarter of the score buffer holds the
-      // 16 packed columns written by the warps that own it.
-      auto issue_acc = [&](uint32_t d, uint32_t a_base, uint32_t b0, bool acc) {
-#pragma unroll
-        for (int k = 0; k < 4; ++k)
-          umma_ts(d, a_base + (k >> 1) * 32 + (k & 1) * 8,
-                  make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024), idesc_acc,
-                  (acc || k > 0) ? 1u : 0u);
-      };
+      const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem), ds_addr = smem_u32(ds_smem);
+      const uint32_t ring_addr = smem_u32(ring);
+      const uint32_t t_st = tmem, t_dpt = tmem + kTile, t_dk = tmem + 2 * kTile, t_dv = tmem + 3 * kTile;
+      auto slot_addr = [&](uint32_t it) { return ring_addr + (it % kBwdStages) * kTileBytes; };
       auto ring_wait = [&](uint32_t it, uint32_t tag) {
         return mbar_wait(&bars->ring_full[it % kBwdStages], (it / kBwdStages) & 1u, ab, tag);
       };
-      bool ok = mbar_wait(&bars->stat_full[0], 0, ab, 0x2200u) && mbar_wait(&bars->stat_full[1], 0, ab, 0x2201u);
-      ok = ok && ring_wait(0, 0x2210u) && ring_wait(1, 0x2211u);
-      if (ok) {
-        mma_issue_fence();
-        issue_scores(0);
-        issue_scores(1);
-      }
-      for (int h = 0; h < n_half && ok; ++h) {
-        const int n = h >> 1, hh = h & 1;
-        const uint32_t ph = (uint32_t)n & 1u;
-        const uint32_t q_slot = ring_addr + ((2 * n) % kBwdStages) * kTileBytes + hh * 8192;
-        const uint32_t do_slot = ring_addr + ((2 * n + 1) % kBwdStages) * kTileBytes + hh * 8192;
-        ok = mbar_wait(&bars->p_full[hh], ph, ab, 0x2220u + hh);
-        if (!ok) break;
-        mma_issue_fence();
-        issue_acc(t_dv, tmem + hh * 64, do_slot, h > 0);          // dV += P^T dO
-        ok = mbar_wait(&bars->ds_full[hh], ph, ab, 0x2230u + hh);
-        if (!ok) break;
-        mma_issue_fence();
-        issue_acc(t_dk, tmem + kTile + hh * 64, q_slot, h > 0);   // dK += dS^T Q
-        if (hh == 1) {
-          tc_commit(&bars->ring_empty[(2 * n) % kBwdStages]);
-          tc_commit(&bars->ring_empty[(2 * n + 1) % kBwdStages]);
+      // D = A B^T with both operands K-major (head_dim contiguous), K = head_dim
+      auto issue_score = [&](uint32_t d, uint32_t a0, uint32_t b0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_ss(d, make_smem_desc_sw128(a0 + off, 16, 1024), make_smem_desc_sw128(b0 + off, 16, 1024), idesc_s,
+                  k > 0 ? 1u : 0u);
         }
-        if (h + 2 < n_half) {
-          if (hh == 0) {  // half h+2 opens step n+1: its tiles must have landed
-            ok = ring_wait(2 * (n + 1), 0x2240u) && ring_wait(2 * (n + 1) + 1, 0x2241u);
-            if (!ok) break;
-            mma_issue_fence();
-          }
-          issue_scores(h + 2);
+      };
+      bool ok = mbar_wait(&bars->stat_full[0], 0, ab, 0x3200u) && mbar_wait(&bars->stat_full[1], 0, ab, 0x3201u);
+      ok = ok && ring_wait(0, 0x3210u);
+      if (ok) {
+        issue_score(t_st, k_addr, slot_addr(0));
+        tc_commit(&bars->st_full);
+      }
+      ok = ok && ring_wait(1, 0x3211u);
+      if (ok) {
+        issue_score(t_dpt, v_addr, slot_addr(1));
+        tc_commit(&bars->dpt_full);
+      }
+      for (int n = 0; n < n_steps && ok; ++n) {
+        const uint32_t ph = (uint32_t)n & 1u;
+        const uint32_t q_slot = slot_addr(2 * n), do_slot = slot_addr(2 * n + 1);
+        const bool more = n + 1 < n_steps;
+        ok = mbar_wait(&bars->p_full, ph, ab, 0x3220u);
+        if (!ok) break;
+        // dV += P^T dO: A = packed bf16 P^T in TMEM (16 packed columns at the start of every
+        // 32-column quarter), B = the dO tile read MN-major, K = 128 query rows in eight slices
+#pragma unroll
+        for (int k = 0; k < 8; ++k)
+          umma_ts(t_dv, t_st + (k >> 1) * 32 + (k & 1) * 8, make_smem_desc_sw128(do_slot + k * 2048, kHalfBytes, 1024),
+                  idesc_acc, (n > 0 || k > 0) ? 1u : 0u);
+        if (more) {
+          ok = ring_wait(2 * (n + 1), 0x3240u);
+          if (!ok) break;
+          issue_score(t_st, k_addr, slot_addr(2 * (n + 1)));
+          tc_commit(&bars->st_full);
+        }
+        ok = mbar_wait(&bars->ds_full, ph, ab, 0x3230u);
+        if (!ok) break;
+        // dK += dS^T Q: A = dS^T from shared memory (K-major, two 64-column halves), B = the Q
+        // tile read MN-major
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+          umma_ss(t_dk, make_smem_desc_sw128(ds_addr + off, 16, 1024),
+                  make_smem_desc_sw128(q_slot + k * 2048, kHalfBytes, 1024), idesc_acc, (n > 0 || k > 0) ? 1u : 0u);
+        }
+        tc_commit(&bars->ds_free);
+        tc_commit(&bars->ring_empty[(2 * n) % kBwdStages]);
+        tc_commit(&bars->ring_empty[(2 * n + 1) % kBwdStages]);
+        if (more) {
+          ok = ring_wait(2 * (n + 1) + 1, 0x3241u);
+          if (!ok) break;
+          issue_score(t_dpt, v_addr, slot_addr(2 * (n + 1) + 1));
+          tc_commit(&bars->dpt_full);
         }
       }
       tc_commit(&bars->acc_done);
@@ -670,19 +685,21 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
    }
   } else {
     setmaxnreg_inc<kDkvComputeRegs>();
-    // Group w (8 warps) owns half w of every q tile; inside it warp column c owns 32 of the 64
-    // score columns.  The two groups run half a step out of phase.
-    const int w = warp >> 3;
-    const int cq = (warp >> 2) & 1;
-    const int wq = warp & 3;
+    // 16 warps on one 128 x 128 tile: thread = kv row (TMEM lane) x one 32-column quarter.
+    const int cq = warp >> 2;      // column quarter 0..3
+    const int wq = warp & 3;       // TMEM lane quarter
     const int r = wq * 32 + lane;  // kv row within the tile
     const int kv_row = kv_tile * kTile + r;
     const bool has_seg = p.q_seg != nullptr;
     const int kv_seg = has_seg ? p.kv_seg[(int64_t)batch * p.kv_len + kv_row] : 0;
     const int32_t* q_seg_row = has_seg ? p.q_seg + (int64_t)batch * p.q_len : nullptr;
     const uint32_t lane_addr = (uint32_t)(wq * 32) << 16;
-    const uint32_t t_st = tmem + lane_addr + w * 64 + cq * 32;
-    const uint32_t t_dpt = tmem + lane_addr + kTile + w * 64 + cq * 32;
+    const uint32_t t_st = tmem + lane_addr + cq * 32;
+    const uint32_t t_dpt = tmem + lane_addr + kTile + cq * 32;
+    // dS^T row r, columns cq*32 .. +31: 64 bytes = four 16-byte chunks of the row's 128-byte
+    // segment in swizzle half cq / 2; chunk c sits at position c ^ (r mod 8)
+    uint8_t* ds_row = ds_smem + (cq >> 1) * kHalfBytes + r * 128;
+    const int chunk0 = (cq & 1) * 4;
     const float c = kSoftCap ? p.soft_cap * kLog2e : p.scale_log2;
     bool ok = true;
     int n = 0;
@@ -691,21 +708,18 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       int4 ent_next = n_ent > 0 ? entries[ebeg] : make_int4(0, 0, 0, 0);
       for (int e = ebeg; e < eend && ok; ++e, ++n) {
         const int4 ent = ent_next;
-        if (e + 1 < eend) ent_next = entries[e + 1];  // fetched a step ahead of its use
+        if (e + 1 < eend) ent_next = entries[e + 1];
         const int st = ent.y & 3;
         const uint32_t ph = (uint32_t)n & 1u;
-        const int q0 = ent.x * kTile + w * 64 + cq * 32;  // first q column of this thread's 32
-        // Per-column statistics of this step (-lse*log2e, di), staged in shared memory by the
-        // producer on the Q slot's barrier.
+        const int q0 = ent.x * kTile + cq * 32;  // first q column of this thread's 32
         const uint32_t itq = 2u * (uint32_t)n;
-        ok = mbar_wait(&bars->ring_full[itq % kBwdStages], (itq / kBwdStages) & 1u, ab, 0x2420u);
+        ok = mbar_wait(&bars->ring_full[itq % kBwdStages], (itq / kBwdStages) & 1u, ab, 0x3420u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const float4* nl4 =
-            reinterpret_cast<const float4*>(stats + ((itq % kBwdStages) / 2) * 2 * kTile + w * 64 + cq * 32);
+        const float4* nl4 = reinterpret_cast<const float4*>(stats + ((itq % kBwdStages) / 2) * 2 * kTile + cq * 32);
         const float4* dl4 = nl4 + kTile / 4;
 
-        ok = mbar_wait(&bars->st_full[w], ph, ab, 0x2400u + w);
+        ok = mbar_wait(&bars->st_full, ph, ab, 0x3400u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -717,7 +731,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
           for (int j = 0; j < 32; ++j) pr[j] = __uint_as_float(v[j]);
         }
-        if constexpr (kSoftCap) {  // pr <- tanh(scale * s / cap), capped before it is masked
+        if constexpr (kSoftCap) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) pr[j] = tanh_ex2(pr[j] * p.softcap_a);
         }
@@ -737,7 +751,6 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
               }
             }
           } else {
-            // dkv partial blocks are stored transposed: [id, kv, q]
             const int8_t* mrow = p.pmb + ((int64_t)ent.z * p.pm_bkv + (kv_row % p.pm_bkv)) * p.pm_bq +
                                  (q0 % p.pm_bq);
             const int4* m4 = reinterpret_cast<const int4*>(mrow);
@@ -782,7 +795,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             pr[4 * t + 3] = ex2(xb.y);
             pk[2 * t] = pack_bf16(pr[4 * t + 0], pr[4 * t + 1]);
             pk[2 * t + 1] = pack_bf16(pr[4 * t + 2], pr[4 * t + 3]);
-            if constexpr (kSoftCap) {  // dS = (p * (1 - tanh^2)) * (dP - di): fold the factor into p
+            if constexpr (kSoftCap) {
 #pragma unroll
               for (int u = 0; u < 4; ++u) pr[4 * t + u] *= fmaf(-th[u], th[u], 1.0f);
             }
@@ -791,14 +804,14 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           tmem_st_wait();
           tc_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(&bars->p_full[w]);
+          if (lane == 0) mbar_arrive(&bars->p_full);
         }
-        ok = mbar_wait(&bars->dpt_full[w], ph, ab, 0x2410u + w);
+        ok = mbar_wait(&bars->dpt_full, ph, ab, 0x3410u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        uint32_t pk[16];
         {
-          uint32_t pk[16];
           uint32_t v[32];
           tmem_ld32(t_dpt, v);
           tmem_ld_wait();
@@ -814,33 +827,40 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             pk[2 * t] = pack_bf16(a.x, a.y);
             pk[2 * t + 1] = pack_bf16(b.x, b.y);
           }
-          tmem_st16(t_dpt, pk);
-          tmem_st_wait();
-          tc_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive(&bars->ds_full[w]);
         }
+        if (n > 0) {  // the previous step's dK must have finished reading the tile
+          ok = mbar_wait(&bars->ds_free, (uint32_t)(n - 1) & 1u, ab, 0x3430u);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+        }
+#pragma unroll
+        for (int ch = 0; ch < 4; ++ch) {
+          const uint4 w = make_uint4(pk[4 * ch], pk[4 * ch + 1], pk[4 * ch + 2], pk[4 * ch + 3]);
+          *reinterpret_cast<uint4*>(ds_row + (((chunk0 + ch) ^ (r & 7)) << 4)) = w;
+        }
+        fence_proxy_async_smem();  // generic-proxy stores -> visible to the MMA's async-proxy reads
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bars->ds_full);
       }
     }
 
     // epilogue: dK (scaled) and dV, 32 columns per thread
-    const int cb = warp >> 2;  // 0..3
     __nv_bfloat16* dk = p.out0 + (int64_t)batch * p.out0_sb + (int64_t)kv_head * p.out0_sh +
-                        (int64_t)kv_row * p.out0_ss + cb * 32;
+                        (int64_t)kv_row * p.out0_ss + cq * 32;
     __nv_bfloat16* dv = p.out1 + (int64_t)batch * p.out1_sb + (int64_t)kv_head * p.out1_sh +
-                        (int64_t)kv_row * p.out1_ss + cb * 32;
+                        (int64_t)kv_row * p.out1_ss + cq * 32;
     if (n_steps > 0) {
       if (ok) {
-        ok = mbar_wait(&bars->acc_done, 0, ab, 0x2500u);
+        ok = mbar_wait(&bars->acc_done, 0, ab, 0x3500u);
         ok = __all_sync(0xffffffffu, ok);
       }
       if (ok) {
         tc_fence_after();
         uint32_t v[32];
-        tmem_ld32(tmem + lane_addr + 2 * kTile + cb * 32, v);
+        tmem_ld32(tmem + lane_addr + 2 * kTile + cq * 32, v);
         tmem_ld_wait();
         store_row_half(dk, v, p.scale);
-        tmem_ld32(tmem + lane_addr + 3 * kTile + cb * 32, v);
+        tmem_ld32(tmem + lane_addr + 3 * kTile + cq * 32, v);
         tmem_ld_wait();
         store_row_half(dv, v, 1.0f);
       }
@@ -860,7 +880,6 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     tmem_dealloc(tmem, 512);
   }
 }
-
 
 // ------------------------------------------------------------------------------------------
 // host launcher
@@ -937,12 +956,12 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   if (soft_cap && !(a.soft_cap > 0.f)) return SPLASH_ERR_INVALID_ARGUMENT;
   auto* dq_kernel = soft_cap ? splash_dq_kernel<true> : splash_dq_kernel<false>;
   auto* dkv_kernel = soft_cap ? splash_dkv_kernel<true> : splash_dkv_kernel<false>;
+  const int dkv_smem = kDkvSmemBytes;
   static bool attr_set[2] = {false, false};
   if (!attr_set[soft_cap]) {
     if (cudaFuncSetAttribute(dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmemBytes) !=
             cudaSuccess ||
-        cudaFuncSetAttribute(dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDkvSmemBytes) !=
-            cudaSuccess)
+        cudaFuncSetAttribute(dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv_smem) != cudaSuccess)
       return SPLASH_ERR_CUDA;
     attr_set[soft_cap] = true;
   }
@@ -1012,7 +1031,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.chunk_groups = chunk_groups_for(2 * (Hq / Hkv) * Sq * kHeadDim * 2, p.n_groups, 1);
   if ((int64_t)p.n_rows * p.n_groups > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
   if (mask & 4u)
-    dkv_kernel<<<dim3((unsigned)(p.n_rows * p.n_groups), 1u, 1u), kDkvThreads, kDkvSmemBytes, stream>>>(
+    dkv_kernel<<<dim3((unsigned)(p.n_rows * p.n_groups), 1u, 1u), kDkvThreads, dkv_smem, stream>>>(
         tm_q, tm_do, tm_k, tm_v, p);
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
 }
