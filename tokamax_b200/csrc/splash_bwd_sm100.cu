@@ -464,15 +464,14 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // dkv kernel
 // ------------------------------------------------------------------------------------------
 // 16 compute warps (thread = kv row x one 32-column quarter of the q tile) keep the P^T / dS^T
-// phases short; warp 16 feeds TMA, warp 17 issues MMAs, warps 18-19 only complete the fifth
-// warpgroup so registers can be handed to the compute warpgroups.
+// phases short; warp 16 feeds TMA, warp 17 issues MMAs, warps 18-19 are idle (they complete the
+// fifth warpgroup).
 constexpr int kDkvThreads = 640;
 constexpr int kDkvTmaWarp = 16;
 constexpr int kDkvMmaWarp = 17;
-// setmaxnreg.inc can only take what setmaxnreg.dec of the same CTA released: at 96 registers per
-// thread at launch, 512 * (104 - 96) = 4096 <= 128 * (96 - 56) = 5120.
-constexpr int kDkvComputeRegs = 104;
-constexpr int kDkvIssueRegs = 56;
+// No register hand-over here: at 640 threads every thread gets 96 registers, which the compute
+// warps fit in, and the MMA / TMA threads keep their loop state in registers instead of spilling
+// it (with 56 registers the issue loop reloaded descriptor bases from local memory).
 
 // One CTA = one kv tile of one (batch, kv head); the q heads of the GQA group and the active q
 // tiles are looped inside and dK / dV of the whole group accumulate in TMEM in fp32 (no atomics,
@@ -573,7 +572,6 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   AbortCtx ab{&bars->abort_flag, p.err};
 
   if (warp >= 16) {
-   setmaxnreg_dec<kDkvIssueRegs>();
    if (warp == kDkvTmaWarp) {
     if (lane == 0 && n_steps > 0) {
       tma_prefetch_desc(&tm_q);
@@ -684,7 +682,6 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     }
    }
   } else {
-    setmaxnreg_inc<kDkvComputeRegs>();
     // 16 warps on one 128 x 128 tile: thread = kv row (TMEM lane) x one 32-column quarter.
     const int cq = warp >> 2;      // column quarter 0..3
     const int wq = warp & 3;       // TMEM lane quarter
