@@ -240,11 +240,11 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       const uint32_t q_addr = smem_u32(q_smem), do_addr = smem_u32(do_smem), ring_addr = smem_u32(ring);
       const uint32_t t_dp = tmem + 2 * kTile, t_dq = tmem + 3 * kTile;
       auto ss_kmajor = [&](uint32_t d, uint32_t a0, uint32_t b0) {
+        const SmemDesc da = make_smem_desc_sw128(a0, 16, 1024), db = make_smem_desc_sw128(b0, 16, 1024);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(d, make_smem_desc_sw128(a0 + off, 16, 1024), make_smem_desc_sw128(b0 + off, 16, 1024),
-                  idesc_kk, k > 0 ? 1u : 0u);
+          umma_ss(d, desc_at(da, off), desc_at(db, off), idesc_kk, k > 0 ? 1u : 0u);
         }
       };
       auto ring_wait = [&](uint32_t it, uint32_t tag) {
@@ -281,11 +281,10 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         {
           // dQ += dS_n K_n : A = packed dS in the S buffer, B = K tile read MN-major.
           const uint32_t a_base = tmem + (n & 1) * kTile;
-          const uint32_t b0 = ring_addr + (it_k % kDqStages) * kTileBytes;
+          const SmemDesc db = make_smem_desc_sw128(ring_addr + (it_k % kDqStages) * kTileBytes, kHalfBytes, 1024);
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            umma_ts(t_dq, a_base + packed_a_col(k), make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024),
-                    idesc_mn, (n > 0 || k > 0) ? 1u : 0u);
+            umma_ts(t_dq, a_base + packed_a_col(k), desc_at(db, k * 2048), idesc_mn, (n > 0 || k > 0) ? 1u : 0u);
           tc_commit(&bars->ring_empty[it_k % kDqStages]);
         }
         if (has_next) {
@@ -621,23 +620,26 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         return mbar_wait(&bars->ring_full[it % kBwdStages], (it / kBwdStages) & 1u, ab, tag);
       };
       // D = A B^T with both operands K-major (head_dim contiguous), K = head_dim
-      auto issue_score = [&](uint32_t d, uint32_t a0, uint32_t b0) {
+      auto issue_score = [&](uint32_t d, SmemDesc da, uint32_t b0) {
+        const SmemDesc db = make_smem_desc_sw128(b0, 16, 1024);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(d, make_smem_desc_sw128(a0 + off, 16, 1024), make_smem_desc_sw128(b0 + off, 16, 1024), idesc_s,
-                  k > 0 ? 1u : 0u);
+          umma_ss(d, desc_at(da, off), desc_at(db, off), idesc_s, k > 0 ? 1u : 0u);
         }
       };
+      // descriptors of the stationary operands, built once
+      const SmemDesc k_desc = make_smem_desc_sw128(k_addr, 16, 1024), v_desc = make_smem_desc_sw128(v_addr, 16, 1024);
+      const SmemDesc ds_desc = make_smem_desc_sw128(ds_addr, 16, 1024);
       bool ok = mbar_wait(&bars->stat_full[0], 0, ab, 0x3200u) && mbar_wait(&bars->stat_full[1], 0, ab, 0x3201u);
       ok = ok && ring_wait(0, 0x3210u);
       if (ok) {
-        issue_score(t_st, k_addr, slot_addr(0));
+        issue_score(t_st, k_desc, slot_addr(0));
         tc_commit(&bars->st_full);
       }
       ok = ok && ring_wait(1, 0x3211u);
       if (ok) {
-        issue_score(t_dpt, v_addr, slot_addr(1));
+        issue_score(t_dpt, v_desc, slot_addr(1));
         tc_commit(&bars->dpt_full);
       }
       for (int n = 0; n < n_steps && ok; ++n) {
@@ -648,25 +650,26 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (!ok) break;
         // dV += P^T dO: A = packed bf16 P^T in TMEM (16 packed columns at the start of every
         // 32-column quarter), B = the dO tile read MN-major, K = 128 query rows in eight slices
+        const SmemDesc do_mn = make_smem_desc_sw128(do_slot, kHalfBytes, 1024);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ts(t_dv, t_st + (k >> 1) * 32 + (k & 1) * 8, make_smem_desc_sw128(do_slot + k * 2048, kHalfBytes, 1024),
-                  idesc_acc, (n > 0 || k > 0) ? 1u : 0u);
+          umma_ts(t_dv, t_st + (k >> 1) * 32 + (k & 1) * 8, desc_at(do_mn, k * 2048), idesc_acc,
+                  (n > 0 || k > 0) ? 1u : 0u);
         if (more) {
           ok = ring_wait(2 * (n + 1), 0x3240u);
           if (!ok) break;
-          issue_score(t_st, k_addr, slot_addr(2 * (n + 1)));
+          issue_score(t_st, k_desc, slot_addr(2 * (n + 1)));
           tc_commit(&bars->st_full);
         }
         ok = mbar_wait(&bars->ds_full, ph, ab, 0x3230u);
         if (!ok) break;
         // dK += dS^T Q: A = dS^T from shared memory (K-major, two 64-column halves), B = the Q
         // tile read MN-major
+        const SmemDesc q_mn = make_smem_desc_sw128(q_slot, kHalfBytes, 1024);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(t_dk, make_smem_desc_sw128(ds_addr + off, 16, 1024),
-                  make_smem_desc_sw128(q_slot + k * 2048, kHalfBytes, 1024), idesc_acc, (n > 0 || k > 0) ? 1u : 0u);
+          umma_ss(t_dk, desc_at(ds_desc, off), desc_at(q_mn, k * 2048), idesc_acc, (n > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(&bars->ds_free);
         tc_commit(&bars->ring_empty[(2 * n) % kBwdStages]);
@@ -674,7 +677,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (more) {
           ok = ring_wait(2 * (n + 1) + 1, 0x3241u);
           if (!ok) break;
-          issue_score(t_dpt, v_addr, slot_addr(2 * (n + 1) + 1));
+          issue_score(t_dpt, v_desc, slot_addr(2 * (n + 1) + 1));
           tc_commit(&bars->dpt_full);
         }
       }

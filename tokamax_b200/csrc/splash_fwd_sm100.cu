@@ -215,17 +215,16 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       auto issue_qk = [&](int i, uint32_t slot) {
         const uint32_t a0 = q_addr + i * kTB;
         const uint32_t b0 = kv_addr + slot * kTB;
+        const SmemDesc da = make_smem_desc_sw128(a0, 16, 1024), db = make_smem_desc_sw128(b0, 16, 1024);
         if constexpr (kFp8) {
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_ss_f8(tmem + i * kTile, make_smem_desc_sw128(a0 + k * 32, 16, 1024),
-                       make_smem_desc_sw128(b0 + k * 32, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+            umma_ss_f8(tmem + i * kTile, desc_at(da, k * 32), desc_at(db, k * 32), idesc_qk, k > 0 ? 1u : 0u);
         } else {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-            umma_ss(tmem + i * kTile, make_smem_desc_sw128(a0 + off, 16, 1024),
-                    make_smem_desc_sw128(b0 + off, 16, 1024), idesc_qk, k > 0 ? 1u : 0u);
+            umma_ss(tmem + i * kTile, desc_at(da, off), desc_at(db, off), idesc_qk, k > 0 ? 1u : 0u);
           }
         }
         tc_commit(&bars->s_full[i]);
@@ -237,16 +236,16 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       auto issue_pv = [&](int i, uint32_t slot, bool acc) {
         const uint32_t b0 = kv_addr + slot * kTB;
         if constexpr (kFp8) {
+          const SmemDesc db = make_smem_desc_sw128(b0, 16, 1024);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            umma_ts_f8(tmem + 2 * kTile + i * kTile, tmem + i * kTile + k * 8,
-                       make_smem_desc_sw128(b0 + k * 4096, 16, 1024), idesc_pv,
+            umma_ts_f8(tmem + 2 * kTile + i * kTile, tmem + i * kTile + k * 8, desc_at(db, k * 4096), idesc_pv,
                        (acc || k > 0) ? 1u : 0u);
         } else {
+          const SmemDesc db = make_smem_desc_sw128(b0, kHalfBytes, 1024);
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            umma_ts(tmem + 2 * kTile + i * kTile, tmem + i * kTile + k * 8,
-                    make_smem_desc_sw128(b0 + k * 2048, kHalfBytes, 1024), idesc_pv,
+            umma_ts(tmem + 2 * kTile + i * kTile, tmem + i * kTile + k * 8, desc_at(db, k * 2048), idesc_pv,
                     (acc || k > 0) ? 1u : 0u);
           }
         }
