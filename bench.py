@@ -218,7 +218,7 @@ def measured_peaks():
 
 # DRAM traffic of one dkv-kernel launch on the c2 workload (dram__bytes_read.sum +
 # dram__bytes_write.sum), taken from the ncu capture summarised in profiles/splash_dkv_kernel_c2.md.
-DKV_TRAFFIC_BYTES_C2 = 853.6e6
+DKV_TRAFFIC_BYTES_C2 = 843.6e6
 
 
 def per_kernel_times(kernel, q, k, v, do, seg, iters: int = 5) -> dict:
