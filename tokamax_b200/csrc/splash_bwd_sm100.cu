@@ -957,7 +957,11 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   auto* dq_kernel = soft_cap ? splash_dq_kernel<true> : splash_dq_kernel<false>;
   auto* dkv_kernel = soft_cap ? splash_dkv_kernel<true> : splash_dkv_kernel<false>;
   const int dkv_smem = kDkvSmemBytes;
-  static bool attr_set[2] = {false, false};
+  // function attributes are per device: remember which devices have been set up
+  static bool attr_done[64][2] = {};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return SPLASH_ERR_CUDA;
+  bool* attr_set = attr_done[dev & 63];
   if (!attr_set[soft_cap]) {
     if (cudaFuncSetAttribute(dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmemBytes) !=
             cudaSuccess ||

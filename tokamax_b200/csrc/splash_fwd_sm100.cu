@@ -673,7 +673,11 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
     splash_fwd_kernel<false, true><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
   } else {
     constexpr int smem = fwd_smem_bytes(false);
-    static bool attr_set = false;
+    // function attributes are per device: remember which devices have been set up
+    static bool attr_done[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return SPLASH_ERR_CUDA;
+    bool& attr_set = attr_done[dev & 63];
     if (!attr_set) {
       if (cudaFuncSetAttribute(splash_fwd_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                smem) != cudaSuccess)
