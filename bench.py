@@ -567,7 +567,15 @@ def run_context_parallel(args, w, wname):
   kernel = make_kernel(w)
   s_loc = w["seq"] // world
   q, k, v, do = device_inputs(w, dev, seq_slice=s_loc)
-  cp = ulysses.UlyssesSplashAttention(kernel)
+  ring_mode = args.cp == "ring"
+  if ring_mode:
+    from tokamax_b200 import ring_attention
+    from tokamax_b200 import splash_attention_mask as mask_lib
+    if w["mask"] != "causal":
+      raise SystemExit("--cp ring is wired for the causal workloads")
+    cp = ring_attention.make_ring_attention(mask_lib.CausalMask((w["seq"], w["seq"])))
+  else:
+    cp = ulysses.UlyssesSplashAttention(kernel)
   n_live = live_pairs(w, None)
   flops = 14 * D * w["q_heads"] * n_live
 
@@ -599,7 +607,7 @@ def run_context_parallel(args, w, wname):
     kh = torch.empty((w["batch"], w["kv_heads"] // world, w["seq"], D), dtype=q.dtype, device=dev)
     for t in (qh, qh, kh, kh):
       ulysses._exchange(t, None, False)  # pylint: disable=protected-access
-  a2a_ms = max_over_ranks(timed_steps(exchanges, 3, 1, barrier=dist.barrier))
+  a2a_ms = None if ring_mode else max_over_ranks(timed_steps(exchanges, 3, 1, barrier=dist.barrier))
   sent = 2 * (2 * ulysses.exchange_bytes_sent(q.shape, 2, world) + 2 * ulysses.exchange_bytes_sent(k.shape, 2, world))
 
   # end to end: each rank's sequence shard starts and ends in pinned host memory
@@ -627,11 +635,13 @@ def run_context_parallel(args, w, wname):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": wname, **{k_: w[k_] for k_ in ("batch", "q_heads", "kv_heads", "seq", "mask")},
-                   "head_dim": D, "parallelism": f"ulysses cp{world}", "n_live_pairs": n_live,
+                   "head_dim": D, "parallelism": f"{'ring' if ring_mode else 'ulysses'} cp{world}",
+                   "n_live_pairs": n_live,
                    "flops_per_step": flops, "l2": "inputs are larger than the 126 MB L2"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * args.steps,
         "cp": {"tokens_per_s": w["batch"] * w["seq"] / (ms / 1e3), "a2a_ms_per_step": a2a_ms,
-               "a2a_bytes_sent_per_gpu": sent, "a2a_gbs_per_direction": sent / a2a_ms / 1e6,
+               "a2a_bytes_sent_per_gpu": None if ring_mode else sent,
+               "a2a_gbs_per_direction": None if ring_mode else sent / a2a_ms / 1e6,
                "nvlink_nominal_gbs_per_direction": 900.0},
         "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak_sustained, "unit": "TFLOP/s",
                      "frac": value / world / peak_sustained, "peak_source": f"{peak_src} bf16 sustained, per GPU",
@@ -649,6 +659,8 @@ def main():
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4", "c5"])
+  ap.add_argument("--cp", default="ulysses", choices=["ulysses", "ring"],
+                  help="context-parallel scheme for N > 1 (ring: K/V rotate, causal load is unbalanced)")
   ap.add_argument("--no-e2e", action="store_true")
   ap.add_argument("--no-cpu-baseline", action="store_true")
   args = ap.parse_args()
