@@ -567,13 +567,14 @@ def run_context_parallel(args, w, wname):
   kernel = make_kernel(w)
   s_loc = w["seq"] // world
   q, k, v, do = device_inputs(w, dev, seq_slice=s_loc)
-  ring_mode = args.cp == "ring"
+  ring_mode = args.cp in ("ring", "ring_zigzag")
   if ring_mode:
     from tokamax_b200 import ring_attention
     from tokamax_b200 import splash_attention_mask as mask_lib
     if w["mask"] != "causal":
       raise SystemExit("--cp ring is wired for the causal workloads")
-    cp = ring_attention.make_ring_attention(mask_lib.CausalMask((w["seq"], w["seq"])))
+    cp = ring_attention.make_ring_attention(mask_lib.CausalMask((w["seq"], w["seq"])),
+                                            layout="zigzag" if args.cp == "ring_zigzag" else "contiguous")
   else:
     cp = ulysses.UlyssesSplashAttention(kernel)
   n_live = live_pairs(w, None)
@@ -635,7 +636,7 @@ def run_context_parallel(args, w, wname):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": wname, **{k_: w[k_] for k_ in ("batch", "q_heads", "kv_heads", "seq", "mask")},
-                   "head_dim": D, "parallelism": f"{'ring' if ring_mode else 'ulysses'} cp{world}",
+                   "head_dim": D, "parallelism": f"{args.cp if ring_mode else 'ulysses'} cp{world}",
                    "n_live_pairs": n_live,
                    "flops_per_step": flops, "l2": "inputs are larger than the 126 MB L2"},
         "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * args.steps,
@@ -659,7 +660,7 @@ def main():
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4", "c5"])
-  ap.add_argument("--cp", default="ulysses", choices=["ulysses", "ring"],
+  ap.add_argument("--cp", default="ulysses", choices=["ulysses", "ring", "ring_zigzag"],
                   help="context-parallel scheme for N > 1 (ring: K/V rotate, causal load is unbalanced)")
   ap.add_argument("--no-e2e", action="store_true")
   ap.add_argument("--no-cpu-baseline", action="store_true")

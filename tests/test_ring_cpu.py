@@ -63,7 +63,7 @@ def _mask(kind, s):
   return mask_lib.NumpyMask(mask_lib.make_random_mask((s, s), 0.5, 7) | np.eye(s, dtype=bool))
 
 
-def _worker(rank, world, port, kind, with_segments, queue):
+def _worker(rank, world, port, kind, with_segments, queue, layout="contiguous"):
   os.environ["MASTER_ADDR"] = "127.0.0.1"
   os.environ["MASTER_PORT"] = str(port)
   dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -84,17 +84,24 @@ def _worker(rank, world, port, kind, with_segments, queue):
     want = attention_ref.fwd_bwd(q, k, v, do, dense, seg, scale=scale)
     # fwd_bwd takes di from the output rounded to the input dtype; fp32 here, so nothing is rounded
 
-    sl = slice(rank * s // world, (rank + 1) * s // world)
-    ql, kl, vl = (t[:, :, sl].clone().requires_grad_(True) for t in (q, k, v))
-    seg_l = None if seg is None else base.SegmentIds(seg[0][:, sl], seg[1][:, sl])
-    attn = ring.RingSplashAttention(mask, save_residuals=True, shard_attention_factory=OracleShard)
+    if layout == "zigzag":
+      take = lambda t, dim=2: ring.zigzag_shard(t, rank, world, dim)
+    else:
+      take = lambda t, dim=2: t.narrow(dim, rank * s // world, s // world)
+    ql, kl, vl = (take(t).clone().requires_grad_(True) for t in (q, k, v))
+    seg_l = None if seg is None else base.SegmentIds(take(seg[0], 1), take(seg[1], 1))
+    attn = ring.RingSplashAttention(mask, save_residuals=True, shard_attention_factory=OracleShard, layout=layout)
     out, res = attn(ql, kl, vl, seg_l, logits_scale=scale)
-    out.backward(do[:, :, sl])
+    out.backward(take(do))
     ro, rlse, _, rdq, rdk, rdv = want
     for got, ref in ((out.detach(), ro), (res["logsumexp"], rlse), (ql.grad, rdq), (kl.grad, rdk), (vl.grad, rdv)):
-      torch.testing.assert_close(got, ref[:, :, sl], rtol=2e-5, atol=2e-5)
+      torch.testing.assert_close(got, take(ref), rtol=2e-5, atol=2e-5)
+    if layout == "zigzag" and kind == "causal":  # every rank has the same number of live chunk pairs
+      live = sum(not attn.pair_attention(a, c, world).empty
+                 for a in attn.chunks_of(rank, world) for r2 in range(world) for c in attn.chunks_of(r2, world))
+      assert live == 2 * world + 1
     # pairs above the causal diagonal are recognised as empty and skipped
-    if kind == "causal" and world > 1:
+    if kind == "causal" and world > 1 and layout == "contiguous":
       assert attn.shard_attention(0, world - 1).empty and not attn.shard_attention(world - 1, 0).empty
     queue.put((rank, "ok"))
   except Exception as e:  # pylint: disable=broad-except
@@ -104,11 +111,12 @@ def _worker(rank, world, port, kind, with_segments, queue):
     dist.destroy_process_group()
 
 
-def _run(world, kind, with_segments):
+def _run(world, kind, with_segments, layout="contiguous"):
   ctx = mp.get_context("spawn")
   queue = ctx.Queue()
   port = _free_port()
-  procs = [ctx.Process(target=_worker, args=(r, world, port, kind, with_segments, queue)) for r in range(world)]
+  procs = [ctx.Process(target=_worker, args=(r, world, port, kind, with_segments, queue, layout))
+           for r in range(world)]
   for p in procs:
     p.start()
   results = [queue.get(timeout=240) for _ in range(world)]
@@ -125,6 +133,21 @@ def test_ring_matches_unsharded_on_two_gloo_ranks(kind, with_segments):
 @pytest.mark.parametrize("kind", ["composed", "chunked"])
 def test_ring_on_three_gloo_ranks(kind):
   _run(3, kind, kind == "composed")
+
+
+@pytest.mark.parametrize("world,kind,with_segments", [(2, "causal", False), (3, "local", True), (2, "numpy", False)])
+def test_zigzag_ring_matches_unsharded(world, kind, with_segments):
+  _run(world, kind, with_segments, layout="zigzag")
+
+
+def test_zigzag_shard_round_trip():
+  x = torch.arange(2 * 3 * 24 * 2, dtype=torch.float32).view(2, 3, 24, 2)
+  shards = [ring.zigzag_shard(x, r, 3) for r in range(3)]
+  assert shards[0].shape == (2, 3, 8, 2)
+  assert torch.equal(shards[1][:, :, :4], x[:, :, 4:8]) and torch.equal(shards[1][:, :, 4:], x[:, :, 16:20])
+  assert torch.equal(ring.zigzag_unshard(shards), x)
+  with pytest.raises(ValueError):
+    ring.RingSplashAttention(mask_lib.FullMask((8, 8)), layout="spiral")
 
 
 @pytest.mark.parametrize("kind", ["causal", "local", "chunked", "composed", "numpy"])

@@ -163,14 +163,29 @@ def _wait(works):
     w.wait()
 
 
+def _piece(t, idx: int, n: int, dim: int = 2):
+  """Piece ``idx`` of ``n`` equal pieces of ``t`` along ``dim`` (``t`` itself when n == 1)."""
+  if t is None or n == 1:
+    return t
+  size = t.shape[dim] // n
+  return t.narrow(dim, idx * size, size)
+
+
+def _seg_piece(t, idx: int, n: int):
+  return None if t is None else _piece(t, idx, n, dim=1).contiguous()
+
+
 class _RingFunction(torch.autograd.Function):
+  """The ring over whole shards, each shard being one chunk (contiguous layout) or two (zig-zag)."""
 
   @staticmethod
   def forward(ctx, q, k, v, q_seg, kv_seg, ring, scale):
     rank, world, nxt, prv = _ring_peers(ring.group)
     b, hq, sq, d = q.shape
-    o_acc = torch.zeros((b, hq, sq, d), dtype=torch.float32, device=q.device)
-    lse_acc = torch.full((b, hq, sq), -float("inf"), dtype=torch.float32, device=q.device)
+    q_chunks = ring.chunks_of(rank, world)
+    nq = len(q_chunks)
+    o_accs = [torch.zeros((b, hq, sq // nq, d), dtype=torch.float32, device=q.device) for _ in range(nq)]
+    lse_accs = [torch.full((b, hq, sq // nq), -float("inf"), dtype=torch.float32, device=q.device) for _ in range(nq)]
     k_cur, v_cur, seg_cur = k.contiguous(), v.contiguous(), kv_seg
     for i in range(world):
       shard = (rank - i) % world
@@ -178,14 +193,22 @@ class _RingFunction(torch.autograd.Function):
       if i + 1 < world:  # the next step's shard travels under this step's kernels
         moving = [k_cur, v_cur] + ([seg_cur] if seg_cur is not None else [])
         works, received = _post_shift(moving, ring.group, nxt, prv)
-      attn = ring.shard_attention(rank, shard)
-      if not attn.empty:
-        o_i, lse_i = attn.forward(q, k_cur, v_cur, q_seg, seg_cur, scale)
-        merge_partial(o_acc, lse_acc, o_i, lse_i)
+      kv_chunks = ring.chunks_of(shard, world)
+      nk = len(kv_chunks)
+      for a, qc in enumerate(q_chunks):
+        for c, kc in enumerate(kv_chunks):
+          attn = ring.pair_attention(qc, kc, world)
+          if attn.empty:
+            continue
+          o_i, lse_i = attn.forward(_piece(q, a, nq), _piece(k_cur, c, nk), _piece(v_cur, c, nk),
+                                    _seg_piece(q_seg, a, nq), _seg_piece(seg_cur, c, nk), scale)
+          merge_partial(o_accs[a], lse_accs[a], o_i, lse_i)
       if works is not None:
         _wait(works)
         k_cur, v_cur = received[0], received[1]
         seg_cur = received[2] if seg_cur is not None else None
+    o_acc = o_accs[0] if nq == 1 else torch.cat(o_accs, dim=2)
+    lse_acc = lse_accs[0] if nq == 1 else torch.cat(lse_accs, dim=2)
     dead = lse_acc < -1.0e37  # no live key on any shard (or no shard visited at all)
     o = torch.where(dead.unsqueeze(-1), torch.zeros_like(o_acc), o_acc).to(q.dtype)
     lse = torch.where(dead, torch.full_like(lse_acc, ring.mask_value), lse_acc)
@@ -200,7 +223,10 @@ class _RingFunction(torch.autograd.Function):
     ring, scale = ctx.ring, ctx.scale
     rank, world, nxt, prv = _ring_peers(ring.group)
     d_o = d_o.contiguous()
+    q_chunks = ring.chunks_of(rank, world)
+    nq = len(q_chunks)
     dq = torch.zeros(q.shape, dtype=torch.float32, device=q.device)
+    lse_parts = [_piece(lse, a, nq).contiguous() for a in range(nq)]
     k_cur, v_cur, seg_cur = k.contiguous(), v.contiguous(), kv_seg
     acc_in_flight = None  # (works, [dk_acc, dv_acc]) on their way here from the previous rank
     for i in range(world):
@@ -209,11 +235,19 @@ class _RingFunction(torch.autograd.Function):
       if i + 1 < world:
         moving = [k_cur, v_cur] + ([seg_cur] if seg_cur is not None else [])
         works, received = _post_shift(moving, ring.group, nxt, prv)
-      attn = ring.shard_attention(rank, shard)
-      dk_i = dv_i = None
-      if not attn.empty:
-        dq_i, dk_i, dv_i = attn.backward(q, k_cur, v_cur, o, lse, d_o, q_seg, seg_cur, scale)
-        dq += dq_i.float()
+      kv_chunks = ring.chunks_of(shard, world)
+      nk = len(kv_chunks)
+      shares = []  # (kv piece, dk, dv) of this step
+      for a, qc in enumerate(q_chunks):
+        for c, kc in enumerate(kv_chunks):
+          attn = ring.pair_attention(qc, kc, world)
+          if attn.empty:
+            continue
+          dq_i, dk_i, dv_i = attn.backward(_piece(q, a, nq), _piece(k_cur, c, nk), _piece(v_cur, c, nk),
+                                           _piece(o, a, nq), lse_parts[a], _piece(d_o, a, nq),
+                                           _seg_piece(q_seg, a, nq), _seg_piece(seg_cur, c, nk), scale)
+          _piece(dq, a, nq).add_(dq_i.float())
+          shares.append((c, dk_i, dv_i))
       # The accumulators follow their shard: what the previous rank held for the shard now here
       # arrives while this step's kernels run, gets this step's share, and moves on.  After the
       # last step's shift they are home again (reference :255-262).
@@ -223,9 +257,9 @@ class _RingFunction(torch.autograd.Function):
       else:
         _wait(acc_in_flight[0])
         dk_acc, dv_acc = acc_in_flight[1]
-      if dk_i is not None:
-        dk_acc += dk_i.float()
-        dv_acc += dv_i.float()
+      for c, dk_i, dv_i in shares:
+        _piece(dk_acc, c, nk).add_(dk_i.float())
+        _piece(dv_acc, c, nk).add_(dv_i.float())
       acc_in_flight = _post_shift([dk_acc, dv_acc], ring.group, nxt, prv)
       if works is not None:
         _wait(works)
@@ -239,16 +273,25 @@ class _RingFunction(torch.autograd.Function):
 class RingSplashAttention:
   """Sequence-sharded splash attention over a ring of ranks (reference :520-615).
 
-  Call with the local shards ``q [B, Hq, S/P, D]``, ``k, v [B, Hkv, S/P, D]`` (rank ``r`` holds
-  tokens ``[r S/P, (r+1) S/P)`` of both) and optional ``SegmentIds`` shards ``[B, S/P]``.  Returns
-  the local shard of the output, or ``(out, {"logsumexp"})`` with ``save_residuals=True``.
+  Call with the local shards ``q [B, Hq, S/P, D]``, ``k, v [B, Hkv, S/P, D]`` and optional
+  ``SegmentIds`` shards ``[B, S/P]``.  Returns the local shard of the output, or
+  ``(out, {"logsumexp"})`` with ``save_residuals=True``.
+
+  ``layout="contiguous"`` (the reference's): rank ``r`` holds tokens ``[r S/P, (r+1) S/P)``.  Under
+  a causal mask that ring is unbalanced — rank ``r`` has ``r + 1`` live (query, key) shard pairs.
+  ``layout="zigzag"``: the sequence is cut into ``2P`` chunks and rank ``r`` holds chunks ``r`` and
+  ``2P - 1 - r`` back to back (`zigzag_shard` / `zigzag_unshard` convert), which gives every rank
+  the same number of live chunk pairs under a causal mask; results are the same attention.
   """
 
   def __init__(self, mask: mask_lib.Mask, *, group=None, save_residuals: bool = False,
-               mask_value: float = DEFAULT_MASK_VALUE,
+               mask_value: float = DEFAULT_MASK_VALUE, layout: str = "contiguous",
                shard_attention_factory: Callable[[mask_lib.Mask], ShardAttention] | None = None,
                **kernel_kwargs: Any):
+    if layout not in ("contiguous", "zigzag"):
+      raise ValueError(f"layout must be 'contiguous' or 'zigzag', got {layout!r}")
     self.mask = mask
+    self.layout = layout
     self.group = group
     self.save_residuals = save_residuals
     self.mask_value = max(float(mask_value), -3.0e38)
@@ -256,7 +299,22 @@ class RingSplashAttention:
         lambda sub: SplashShardAttention(sub, mask_value=mask_value, **kernel_kwargs))
     self._cache: dict[tuple[int, int, int], ShardAttention] = {}
 
+  def chunks_of(self, rank: int, world: int) -> list[int]:
+    """Sequence chunks (of ``n_chunks(world)``) held by ``rank``, in the order they are stored."""
+    return [rank] if self.layout == "contiguous" else [rank, 2 * world - 1 - rank]
+
+  def n_chunks(self, world: int) -> int:
+    return world if self.layout == "contiguous" else 2 * world
+
+  def pair_attention(self, q_chunk: int, kv_chunk: int, world: int) -> ShardAttention:
+    n = self.n_chunks(world)
+    key = (n, q_chunk, kv_chunk)
+    if key not in self._cache:
+      self._cache[key] = self._factory(shard_mask(self.mask, q_chunk, kv_chunk, n, n))
+    return self._cache[key]
+
   def shard_attention(self, q_shard: int, kv_shard: int) -> ShardAttention:
+    """Attention of (query shard, key shard) in the contiguous layout."""
     world = dist.get_world_size(self.group)
     key = (world, q_shard, kv_shard)
     if key not in self._cache:
@@ -286,11 +344,29 @@ class RingSplashAttention:
     return out
 
 
+def zigzag_shard(x: torch.Tensor, rank: int, world: int, dim: int = 2) -> torch.Tensor:
+  """The zig-zag shard of rank ``rank``: chunks ``rank`` and ``2 world - 1 - rank`` of ``x`` along ``dim``."""
+  chunks = x.chunk(2 * world, dim=dim)
+  return torch.cat([chunks[rank], chunks[2 * world - 1 - rank]], dim=dim)
+
+
+def zigzag_unshard(shards: list[torch.Tensor], dim: int = 2) -> torch.Tensor:
+  """Inverse of `zigzag_shard` over the shards of all ranks, in rank order."""
+  world = len(shards)
+  chunks: list = [None] * (2 * world)
+  for r, s in enumerate(shards):
+    a, b = s.chunk(2, dim=dim)
+    chunks[r], chunks[2 * world - 1 - r] = a, b
+  return torch.cat(chunks, dim=dim)
+
+
 def make_ring_attention(mask: np.ndarray | mask_lib.Mask, *, config=None, is_mqa: bool = False,
                         save_residuals: bool = False, mask_value: float = DEFAULT_MASK_VALUE,
                         downcast_smem_data: bool = True, partial_mask_blocks_dtype: Any = np.int8,
-                        ring_axis=None, q_seq_shards: int = 1, kv_seq_shards: int = 1) -> RingSplashAttention:
-  """Reference factory (:617-705).  ``ring_axis`` is the process group of the ring (default: the world)."""
+                        ring_axis=None, q_seq_shards: int = 1, kv_seq_shards: int = 1,
+                        layout: str = "contiguous") -> RingSplashAttention:
+  """Reference factory (:617-705).  ``ring_axis`` is the process group of the ring (default: the
+  world); ``layout`` is an addition (see `RingSplashAttention`)."""
   del q_seq_shards, kv_seq_shards  # the ring size is the group's size; sub-masks are cut per pair
   if len(mask.shape) != 2:
     raise ValueError(f"Unexpected mask shape: {mask.shape}")
@@ -301,4 +377,5 @@ def make_ring_attention(mask: np.ndarray | mask_lib.Mask, *, config=None, is_mqa
   kwargs = dict(downcast_smem_data=downcast_smem_data, partial_mask_blocks_dtype=partial_mask_blocks_dtype)
   if config is not None:
     kwargs["config"] = config
-  return RingSplashAttention(mask, group=ring_axis, save_residuals=save_residuals, mask_value=mask_value, **kwargs)
+  return RingSplashAttention(mask, group=ring_axis, save_residuals=save_residuals, mask_value=mask_value,
+                             layout=layout, **kwargs)
