@@ -113,7 +113,7 @@ def l2_note(w: dict) -> str:
           "number is launch-bound and is not a bench line")
 
 
-def make_kernel(w: dict):
+def make_kernel(w: dict, bwd: str = "fused"):
   from tokamax_b200 import splash_attention_kernel as splash
   from tokamax_b200 import splash_attention_mask as mask_lib
 
@@ -122,7 +122,7 @@ def make_kernel(w: dict):
     mask = mask_lib.CausalMask((s, s))
   else:
     mask = mask_lib.LocalMask((s, s), (4096, 0), 0)
-  return splash.make_splash_mha(mask, q_seq_shards=1)
+  return splash.make_splash_mha(mask, q_seq_shards=1, repeatable_dq=(bwd == "split"))
 
 
 # ----------------------------------------------------------------------------------------------
@@ -254,9 +254,11 @@ def per_kernel_times(kernel, q, k, v, do, seg, iters: int = 5) -> dict:
   fa.scale = SCALE
   fa.mask_value = -1e30
   fa.error_record = tables.error_record.data_ptr()
-  ws_bytes = lib.splash_bwd_workspace_bytes(b, hq, s)
+  fused = not kernel.repeatable_dq
+  ws_bytes = (lib.splash_bwd_fused_workspace_bytes if fused else lib.splash_bwd_workspace_bytes)(b, hq, s)
   ws = torch.empty(ws_bytes, dtype=torch.uint8, device=dev)
   ba = _native.SplashBwdArgs()
+  ba.flags = _native.BWD_FUSED_DQ if fused else 0
   ba.q, ba.k, ba.v, ba.o, ba.d_o = map(splash._tensor_desc, (q, k, v, o, do))  # pylint: disable=protected-access
   ba.dq, ba.dk, ba.dv = map(splash._tensor_desc, (dq, dk, dv))  # pylint: disable=protected-access
   ba.logsumexp = lse.data_ptr()
@@ -278,9 +280,11 @@ def per_kernel_times(kernel, q, k, v, do, seg, iters: int = 5) -> dict:
   out = {}
   out["fwd"] = timed_steps(run_fwd, iters, 2)
   run_bwd(1)
+  # split form: di pass | dq kernel | dkv kernel.  fused form: di pass + clearing of the fp32 dQ
+  # image | cast of the image to bf16 | the fused kernel (dK, dV and the dQ partials)
   out["delta"] = timed_steps(lambda: run_bwd(1), iters, 1)
-  out["dq"] = timed_steps(lambda: run_bwd(2), iters, 2)
-  out["dkv"] = timed_steps(lambda: run_bwd(4), iters, 2)
+  out["dq_cast" if fused else "dq"] = timed_steps(lambda: run_bwd(2), iters, 2)
+  out["bwd_fused" if fused else "dkv"] = timed_steps(lambda: run_bwd(4), iters, 2)
   kernel.check_errors()
   return out
 
@@ -381,7 +385,7 @@ def run_single_gpu(args, w, wname):
 
   dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
   torch.cuda.set_device(dev)
-  kernel = make_kernel(w)
+  kernel = make_kernel(w, args.bwd)
   seg = seg_np = None
   if "segments" in w["mask"]:
     seg_np = packed_segments(w["batch"], w["seq"], 3000)
@@ -463,17 +467,20 @@ def run_single_gpu(args, w, wname):
   # ---- per-kernel times and the roofline of the dominant kernel
   peak, peak_sustained, peak_src = measured_peaks()
   kt = per_kernel_times(kernel, q, k, v, do, seg)
-  dominant = max(("fwd", "dq", "dkv"), key=lambda n: kt[n])
-  # Split of the 14*D FLOPs per live pair: forward 4*D (QK^T, PV); backward 10*D, attributed as dq
-  # kernel 4*D (dQ = dS K plus half of the shared S / dP recomputation) and dkv kernel 6*D (dK, dV
-  # plus the other half).
-  share = {"fwd": 4, "dq": 4, "dkv": 6}[dominant]
+  # Split of the 14*D FLOPs per live pair: forward 4*D (QK^T, PV); backward 10*D — all of it in the
+  # fused kernel, or, in the split form, dq kernel 4*D (dQ = dS K plus half of the shared S / dP
+  # recomputation) and dkv kernel 6*D (dK, dV plus the other half).
+  shares = {"fwd": 4, "dq": 4, "dkv": 6, "bwd_fused": 10}
+  dominant = max((n for n in kt if n in shares), key=lambda n: kt[n])
+  share = shares[dominant]
   k_flops = share * D * w["q_heads"] * n_live
   achieved = k_flops / kt[dominant] / 1e9
   roofline = {
-      "kernel": {"fwd": "splash_fwd_kernel", "dq": "splash_dq_kernel", "dkv": "splash_dkv_kernel"}[dominant],
+      "kernel": {"fwd": "splash_fwd_kernel", "dq": "splash_dq_kernel", "dkv": "splash_dkv_kernel<.,false>",
+                 "bwd_fused": "splash_dkv_kernel<.,true>"}[dominant],
       "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
       "peak_source": f"{peak_src} bf16 burst", "traffic": DKV_TRAFFIC_BYTES_C2 if (dominant == "dkv" and wname == "c2") else None,
+      "backward_form": args.bwd,
       "kernel_ms": kt,
       "whole_step_frac_of_peak": value / peak, "whole_step_frac_of_sustained": value / peak_sustained,
       "whole_step_frac_of_datasheet_2250": value / 2250.0,
@@ -564,7 +571,7 @@ def run_context_parallel(args, w, wname):
   dev = torch.device("cuda", local)
   torch.cuda.set_device(dev)
   dist.init_process_group("nccl", device_id=dev)
-  kernel = make_kernel(w)
+  kernel = make_kernel(w, args.bwd)
   s_loc = w["seq"] // world
   q, k, v, do = device_inputs(w, dev, seq_slice=s_loc)
   ring_mode = args.cp in ("ring", "ring_zigzag")
@@ -662,6 +669,8 @@ def main():
   ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4", "c5"])
   ap.add_argument("--cp", default="ulysses", choices=["ulysses", "ring", "ring_zigzag"],
                   help="context-parallel scheme for N > 1 (ring: K/V rotate, causal load is unbalanced)")
+  ap.add_argument("--bwd", default="fused", choices=["fused", "split"],
+                  help="backward form: one fused kernel (dQ partials reduced in fp32) or separate dq / dkv kernels")
   ap.add_argument("--no-e2e", action="store_true")
   ap.add_argument("--no-cpu-baseline", action="store_true")
   args = ap.parse_args()

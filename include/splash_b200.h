@@ -297,9 +297,23 @@ typedef struct SplashBwdArgs {
                                        pass must have run on this workspace before bits 1 or 2) */
   float soft_cap;                   /* as in SplashFwdArgs; dS gains the factor 1 - tanh^2
                                        (base.py:159-163).  0 = off */
+  uint32_t flags;                   /* SplashBwdFlags; 0 = split form */
 } SplashBwdArgs;
 
+/* SPLASH_BWD_FUSED_DQ: one kernel per (kv tile, kv head) forms all three gradients, five matmuls
+ * per live block, as the reference's `_flash_attention_dkv_kernel` does with its dq partials
+ * (splash_attention_kernel.py:1395-1410, reduced at :1864).  Here the partials are added into an
+ * fp32 dQ image in the workspace by vector reductions and a last pass scales and casts it, so the
+ * workspace is splash_bwd_fused_workspace_bytes and `sched_dq` is not read.  dK / dV are still
+ * accumulated without atomics and repeat bit for bit; dQ's fp32 sums are formed in an order that
+ * changes from run to run (differences in the last bits).  With this flag launch_mask bit 0 also
+ * clears the image, bit 1 is the cast pass and bit 2 the fused kernel. */
+typedef enum SplashBwdFlags {
+  SPLASH_BWD_FUSED_DQ = 1
+} SplashBwdFlags;
+
 size_t splash_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
+size_t splash_bwd_fused_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
 int splash_bwd(const SplashBwdArgs* args, void* cuda_stream);
 
 /* Ring attention (ring_attention_kernel.py:150-158): folds one ring step's partial result
@@ -317,7 +331,8 @@ int splash_ring_merge(float* o_acc, float* lse_acc, const void* o_i, const float
  * is only handed its operand and result buffers by the runtime that invokes it; code that runs
  * after the process has handed all remaining device memory to another allocator; or a caller whose
  * allocator is not safe to enter from the thread or callback the backward is issued from.  This
- * variant takes the same SplashBwdArgs, ignores `workspace` / `workspace_bytes`, and keeps the
+ * variant takes the same SplashBwdArgs, ignores `workspace` / `workspace_bytes` (and always runs
+ * the split form, whatever `flags` says: the fused form's dQ image would not fit), and keeps the
  * scratch in an array that is part of the loaded library image on every GPU: it performs no
  * cudaMalloc / cudaFree and calls nothing that allocates.
  *

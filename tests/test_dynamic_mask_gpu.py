@@ -76,8 +76,9 @@ def test_tile_states_and_schedules_match_numpy():
       np.testing.assert_array_equal(entries[r, :len(live)], expect)
 
 
+@pytest.mark.parametrize("repeatable_dq", [True, False])
 @pytest.mark.parametrize("with_segments", [False, True])
-def test_device_mask_equals_static_path_bitwise(with_segments):
+def test_device_mask_equals_static_path_bitwise(with_segments, repeatable_dq):
   b, hq, hkv, sq, skv = 2, 4, 2, 512, 768
   m = _mask(sq, skv, 2)
   g = torch.Generator().manual_seed(5)
@@ -89,15 +90,19 @@ def test_device_mask_equals_static_path_bitwise(with_segments):
     ids_kv = torch.from_numpy(np.repeat(np.arange(4, dtype=np.int32), skv // 4))[None].expand(b, -1)
     seg = splash.SegmentIds(ids_q.to(DEV), ids_kv.to(DEV))
   results = []
-  for kernel in (splash.make_dynamic_splash_mha(torch.from_numpy(m).to(DEV), save_residuals=True),
-                 splash.make_splash_mha_single_device(mask_lib.NumpyMask(m), save_residuals=True)):
+  kw = dict(save_residuals=True, repeatable_dq=repeatable_dq)
+  for kernel in (splash.make_dynamic_splash_mha(torch.from_numpy(m).to(DEV), **kw),
+                 splash.make_splash_mha_single_device(mask_lib.NumpyMask(m), **kw)):
     qa, ka, va = (t.clone().requires_grad_(True) for t in (q, k, v))
     out, res = kernel(qa, ka, va, seg, logits_scale=SCALE)
     out.backward(do)
     kernel.check_errors()
     results.append((out, res["logsumexp"], qa.grad, ka.grad, va.grad))
-  for got, ref in zip(*results):
-    assert torch.equal(got, ref)
+  for i, (got, ref) in enumerate(zip(*results)):
+    if i == 2 and not repeatable_dq:  # fused backward: dq is an fp32 sum in varying order
+      assert ((got.float() - ref.float()).norm() / ref.float().norm()).item() <= 1e-3
+    else:
+      assert torch.equal(got, ref)
   if not with_segments:
     ro, rlse, _, rdq, rdk, rdv = attention_ref.fwd_bwd(q.cpu(), k.cpu(), v.cpu(), do.cpu(), m, None, scale=SCALE)
     out, lse, dq, dk, dv = results[0]

@@ -88,3 +88,25 @@ def test_fp8_rejects_bad_arguments():
   short = fp8.quantize_e4m3(_randn(72, 1, 2, 128, D).to(DEV))
   with pytest.raises(ValueError):
     fp8.splash_fwd_fp8(kernel, x, short, short)
+
+
+def test_fp8_device_mask_with_batch_two_and_soft_cap_rejected():
+  """A mask tensor on the device builds one schedule per batch size: batch row 1 must read its
+  own row ends (same result as the host-built tables)."""
+  import dataclasses
+
+  s = 512
+  dense = mask_lib.make_random_mask((s, s), 0.7, 5) | np.eye(s, dtype=np.bool_)
+  q, k, v = (fp8.quantize_e4m3(_randn(81 + i, 2, 2, s, D).to(DEV)) for i in range(3))
+  outs = []
+  for kernel in (splash.make_dynamic_splash_mha(torch.from_numpy(dense).to(DEV), save_residuals=True),
+                 splash.make_splash_mha_single_device(dense, save_residuals=True)):
+    o, res = fp8.splash_fwd_fp8(kernel, q, k, v, logits_scale=0.09, save_residuals=True)
+    kernel.check_errors()
+    outs.append((o, res["logsumexp"]))
+  assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+  assert torch.equal(outs[0][0][0], outs[0][0][0]) and torch.isfinite(outs[0][0].float()).all()
+  capped = splash.make_splash_mha_single_device(
+      dense, config=dataclasses.replace(splash.SplashConfig.get_default(), attn_logits_soft_cap=30.0))
+  with pytest.raises(NotImplementedError):
+    fp8.splash_fwd_fp8(capped, q, k, v)

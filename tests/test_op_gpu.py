@@ -51,6 +51,41 @@ def test_op_matches_oracle(kind):
   assert ((out.float().cpu() - ref).abs() <= 1e-2 + 4e-3 * ref.abs()).all()
 
 
+def _oracle_grads(q, k, v, do, mask, scale):
+  """[B, T, N, H] tensors -> oracle (o, dq, dk, dv) in the same layout."""
+  hm = lambda x: x.permute(0, 2, 1, 3)
+  o, _, _, dq, dk, dv = attention_ref.fwd_bwd(hm(q), hm(k), hm(v), hm(do), mask, scale=scale)
+  return tuple(hm(x) for x in (o, dq, dk, dv))
+
+
+@pytest.mark.parametrize("kind", ["causal", "local", "bool_mask_host", "bool_mask_device", "multi_batch_axes"])
+def test_op_gradients_match_oracle(kind):
+  """dq / dk / dv through the Op: strided [B, T, N, H] views, in-kernel fp32 scale, GQA head map."""
+  dev = torch.device("cuda:0")
+  b, t, n, kh = 2, 384, 4, 2
+  q, k, v, do = _bthd(11, b, t, n), _bthd(12, b, t, kh), _bthd(13, b, t, kh), _bthd(14, b, t, n)
+  kwargs, dense = {}, None
+  if kind in ("causal", "multi_batch_axes"):
+    kwargs, dense = dict(is_causal=True), mask_lib.make_causal_mask((t, t))
+  elif kind == "local":
+    kwargs, dense = dict(local_window_size=(100, 28)), mask_lib.make_local_attention_mask((t, t), (100, 28))
+  else:
+    base = mask_lib.make_random_mask((t, t), 0.5, 4) | np.eye(t, dtype=bool)
+    dense = base & mask_lib.make_causal_mask((t, t))
+    m = torch.from_numpy(base)
+    kwargs = dict(mask=m.to(dev) if kind == "bool_mask_device" else m, is_causal=True)
+  scale = 0.11
+  ref_o, ref_dq, ref_dk, ref_dv = _oracle_grads(q, k, v, do, dense, scale)
+  shape = (lambda x: x.reshape(1, 2, *x.shape[1:])) if kind == "multi_batch_axes" else (lambda x: x)
+  qd, kd, vd = (shape(x).to(dev).requires_grad_(True) for x in (q, k, v))
+  out = op.dot_product_attention(qd, kd, vd, scale=scale, implementation="cuda_sm100", **kwargs)
+  out.backward(shape(do).to(dev))
+  rel = lambda a, r: ((a.float().cpu().reshape(r.shape) - r).norm() / r.norm()).item()
+  assert ((out.float().cpu().reshape(ref_o.shape) - ref_o).abs() <= 1e-2 + 4e-3 * ref_o.abs()).all()
+  assert qd.grad.shape == qd.shape and kd.grad.shape == kd.shape and vd.grad.shape == vd.shape
+  assert rel(qd.grad, ref_dq) <= 1e-2 and rel(kd.grad, ref_dk) <= 1e-2 and rel(vd.grad, ref_dv) <= 1e-2
+
+
 def test_op_backward_and_residuals():
   b, t, n, kh = 1, 256, 2, 1
   dev = torch.device("cuda:0")

@@ -99,10 +99,11 @@ def test_ring_of_one_rank_equals_the_plain_kernel():
     mask = mask_lib.CausalMask((s, s))
     q, k, v, do = (t.to(DEV) for t in _inputs(32, 2, 4, 2, s))
     qa, ka, va = (t.clone().requires_grad_(True) for t in (q, k, v))
-    out, res = ring.make_ring_attention(mask, save_residuals=True)(qa, ka, va, logits_scale=SCALE)
+    out, res = ring.make_ring_attention(mask, save_residuals=True, repeatable_dq=True)(qa, ka, va, logits_scale=SCALE)
     out.backward(do)
     qb, kb, vb = (t.clone().requires_grad_(True) for t in (q, k, v))
-    ref, rres = splash.make_splash_mha_single_device(mask, save_residuals=True)(qb, kb, vb, logits_scale=SCALE)
+    ref, rres = splash.make_splash_mha_single_device(mask, save_residuals=True, repeatable_dq=True)(
+        qb, kb, vb, logits_scale=SCALE)
     ref.backward(do)
     assert torch.equal(out, ref) and torch.equal(res["logsumexp"], rres["logsumexp"])
     assert torch.equal(qa.grad, qb.grad) and torch.equal(ka.grad, kb.grad) and torch.equal(va.grad, vb.grad)

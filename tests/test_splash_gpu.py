@@ -60,6 +60,17 @@ def _run_and_compare(kernel, mask_dense, q, k, v, do, seg=None, scale=1.0 / math
   assert _rel(qd.grad, rdq) <= GRAD_REL
   assert _rel(dk, rdk) <= GRAD_REL
   assert _rel(dv, rdv) <= GRAD_REL
+  # the other backward form (split dq / dkv kernels when the kernel object runs the fused one,
+  # and the other way round) on the same forward
+  other = kernel.with_options(repeatable_dq=not kernel.repeatable_dq)
+  q2, k2, v2 = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+  out2, _ = other(q2, k2, v2, seg_dev, logits_scale=scale, save_residuals=True)
+  out2.backward(do.to(dev))
+  other.check_errors()
+  assert torch.equal(out2, out)
+  dk2, dv2 = (k2.grad, v2.grad) if k.dim() == 4 else (k2.grad[:, None], v2.grad[:, None])
+  assert torch.equal(dk2, dk) and torch.equal(dv2, dv)
+  assert _rel(q2.grad, rdq) <= GRAD_REL
   return out, res, qd.grad, dk, dv
 
 
@@ -249,10 +260,13 @@ def test_dynamic_mask_kernel():
   _run_and_compare(kernel, dense, q, k, v, do)
 
 
-def test_bitwise_repeatable():
+@pytest.mark.parametrize("repeatable_dq", [True, False])
+def test_bitwise_repeatable(repeatable_dq):
+  """Split backward: everything repeats bit for bit.  Fused backward (the default): the output,
+  dK and dV do (no atomics touch them); dQ is an fp32 sum whose order varies."""
   q, k, v, do = _inputs(23, 1, 8, 2, 1024, 1024)
   mask = mask_lib.CausalMask((1024, 1024))
-  kernel = splash.make_splash_mha(mask, q_seq_shards=1)
+  kernel = splash.make_splash_mha(mask, q_seq_shards=1, repeatable_dq=repeatable_dq)
   dev = torch.device("cuda:0")
   runs = []
   for _ in range(2):
@@ -260,8 +274,29 @@ def test_bitwise_repeatable():
     out = kernel(qd, kd, vd, logits_scale=0.0884)
     out.backward(do.to(dev))
     runs.append((out.detach(), qd.grad, kd.grad, vd.grad))
-  for a, b in zip(*runs):
-    assert torch.equal(a, b)
+  for i, (a, b) in enumerate(zip(*runs)):
+    if i == 1 and not repeatable_dq:
+      assert ((a.float() - b.float()).norm() / b.float().norm()).item() <= 1e-3
+    else:
+      assert torch.equal(a, b)
+
+
+def test_fused_and_split_backward_agree():
+  """dK / dV of the two backward forms come from the same MMAs in the same order: bit-equal.
+  dQ differs only by where the fp32 partial sums are rounded."""
+  q, k, v, do = _inputs(29, 2, 8, 2, 1024, 1024)
+  dev = torch.device("cuda:0")
+  grads = []
+  for repeatable in (False, True):
+    kernel = splash.make_splash_mha(mask_lib.LocalMask((1024, 1024), (300, 0), 0), q_seq_shards=1,
+                                    repeatable_dq=repeatable)
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    kernel(qd, kd, vd, logits_scale=0.0884).backward(do.to(dev))
+    kernel.check_errors()
+    grads.append((qd.grad, kd.grad, vd.grad))
+  (dq_f, dk_f, dv_f), (dq_s, dk_s, dv_s) = grads
+  assert torch.equal(dk_f, dk_s) and torch.equal(dv_f, dv_s)
+  assert ((dq_f.float() - dq_s.float()).norm() / dq_s.float().norm()).item() <= 2e-3
 
 
 def test_full_size_properties_llama_shape():

@@ -38,7 +38,8 @@ def _worker(rank, world, port, queue):
     g = torch.Generator().manual_seed(7)
     mk = lambda h: torch.randn(b, h, s, D, generator=g).to(torch.bfloat16)
     q, k, v, do = (t.to(dev) for t in (mk(hq), mk(hkv), mk(hkv), mk(hq)))
-    kernel = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1)
+    # split backward: every gradient repeats bit for bit, so the comparison can be exact
+    kernel = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1, repeatable_dq=True)
     scale = 1 / math.sqrt(D)
     qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
     full = kernel(qf, kf, vf, logits_scale=scale)

@@ -20,12 +20,13 @@ namespace sb {
 // blockIdx.y<<16, [2] tag of the barrier that timed out, [3] threadIdx.x.
 enum : uint32_t { kErrNone = 0, kErrWaitTimeout = 1 };
 
+constexpr long long kWaitLimitCycles = 1500000000ll;  // ~0.8 s at 1.9 GHz
+
 struct AbortCtx {
   volatile uint32_t* cta_flag;   // shared memory word, non-zero once any wait gave up
   uint32_t* global_err;          // device error record (may not be null)
+  long long limit_cycles = kWaitLimitCycles;  // a compile-time constant wherever it is not set
 };
-
-constexpr long long kWaitLimitCycles = 1500000000ll;  // ~0.8 s at 1.9 GHz
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return static_cast<uint32_t>(__cvta_generic_to_shared(p));
@@ -71,7 +72,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
-// Bounded wait: gives up after kWaitLimitCycles (under a second), or as soon as another thread
+// Bounded wait: gives up after ab.limit_cycles (by default under a second), or as soon as another thread
 // of the CTA has given up.  Returns false if the wait was abandoned.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const AbortCtx& ab,
                                           uint32_t tag) {
@@ -81,7 +82,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, const 
     if (mbar_try_wait(bar, parity)) return true;
     if ((spin & 15u) == 15u) {
       if (*ab.cta_flag) return false;
-      if (clock64() - start > kWaitLimitCycles) break;
+      if (clock64() - start > ab.limit_cycles) break;
     }
   }
   *ab.cta_flag = 1u;
@@ -352,6 +353,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
+}
+
+// Four-wide fp32 reduction into global memory (16-byte aligned address); no return value, so the
+// issuing warp does not wait for it.
+__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
+  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d)
+               : "memory");
 }
 
 // Register reallocation between warpgroups (all four warps of a warpgroup must execute it).

@@ -1,6 +1,6 @@
 // Splash attention backward for sm_100a: bf16 inputs, head_dim 128, fp32 accumulation.
 //
-// Three kernels, all atomic-free and bitwise repeatable:
+// Two forms.  The split form is atomic-free and bitwise repeatable in all three gradients:
 //   1. delta      : -di[b,h,q] = -sum_d o * do  (stored negated: dP + (-di) is an add, which has a
 //                   two-wide form)                                   (HBM-bound elementwise pass)
 //   2. dq kernel  : one CTA per (q tile, q head).  Per kv tile: S = Q K^T, dP = dO V^T,
@@ -9,6 +9,14 @@
 //                   head and their active q tiles: S^T = K Q^T, dP^T = V dO^T, dV += P^T dO,
 //                   dK += dS^T Q.  The whole GQA group is summed in the CTA's fp32 TMEM
 //                   accumulators, so dK/dV need no atomics and no second pass.
+// The fused form (SPLASH_BWD_FUSED_DQ) is what the reference's live backward does — one kernel,
+// five matmuls per live block (splash_attention_kernel.py:1234-1459, dq partials :1395-1410
+// reduced at :1864): the dkv kernel also forms dQ_partial = dS K for every (q tile, kv tile) pair
+// it visits, from the dS^T tile it already holds in shared memory, and adds it into an fp32 dQ
+// image in global memory (vector red.add from four drain warps); a last HBM-bound pass scales
+// and casts that image to bf16.  S and dP are then computed once per pair instead of twice (5
+// tile-MMAs instead of 7).  dK / dV stay atomic-free and repeatable; dQ's fp32 sums arrive in an
+// order that varies from run to run, so its last bits are not repeatable in this form.
 // P (and dS in the dq kernel) is written back to TMEM as bf16 and consumed as the A operand of the
 // next MMA; the dkv kernel's dS^T goes through shared memory instead, which frees its TMEM columns
 // a step earlier.  K, V, Q and dO tiles are each staged once by TMA and read both K-major and
@@ -105,6 +113,9 @@ struct BwdParams {
   float soft_cap, softcap_a;   // cap; scale / cap
   float scale, scale_log2;
   uint32_t* err;
+  // fused form only: fp32 dQ image, one 128 x 128 tile per (batch, q head, q tile), each tile
+  // stored as [col / 4][row][col % 4] so that one warp's vector red covers 512 contiguous bytes
+  float* dq_acc;
 };
 
 struct BwdBarriers {
@@ -468,6 +479,16 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 constexpr int kDkvThreads = 640;
 constexpr int kDkvTmaWarp = 16;
 constexpr int kDkvMmaWarp = 17;
+// Fused form: warps 20-23 drain the per-pair dQ tile from TMEM into the fp32 image.  768 threads
+// start at 80 registers.  Registers live in four banks, one per scheduler, and warp w draws on bank
+// w mod 4, so every bank serves four compute warps, one warp of the issuing warpgroup and one
+// drain warp: 6 x 80 at launch, 4 x 88 + 80 + 48 after the hand-over (the sum per bank has to stay
+// at what the launch gave it, or the increase never completes).
+constexpr int kFusedThreads = 768;
+constexpr int kDkvDrainWarp = 20;
+constexpr int kFusedComputeRegs = 88;
+constexpr int kFusedDrainRegs = 48;
+constexpr int kDqTileFloats = kTile * kHeadDim;
 // No register hand-over here: at 640 threads every thread gets 96 registers, which the compute
 // warps fit in, and the MMA / TMA threads keep their loop state in registers instead of spilling
 // it (with 56 registers the issue loop reloaded descriptor bases from local memory).
@@ -497,14 +518,16 @@ struct DkvBarriers {
   uint64_t ds_full;
   uint64_t ds_free;   // dK(n) has finished reading the dS^T tile in shared memory
   uint64_t acc_done;
+  uint64_t dq_full;   // fused: dQ_partial(n) is complete in the dP^T columns
+  uint64_t dq_free;   // fused: the drain warps have read it out (4 arrivals)
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t early_exit;
 };
 static_assert(sizeof(DkvBarriers) <= 512, "barrier block");
 
-template <bool kSoftCap>
-__global__ void __launch_bounds__(kDkvThreads, 1)
+template <bool kSoftCap, bool kFuseDq>
+__global__ void __launch_bounds__(kFuseDq ? kFusedThreads : kDkvThreads, 1)
 splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_do,
                        const __grid_constant__ CUtensorMap tm_k, const __grid_constant__ CUtensorMap tm_v,
                        const BwdParams p) {
@@ -556,6 +579,8 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     mbar_init(&bars->ds_full, 16);
     mbar_init(&bars->ds_free, 1);
     mbar_init(&bars->acc_done, 1);
+    mbar_init(&bars->dq_full, 1);
+    mbar_init(&bars->dq_free, 4);
     mbar_fence_init();
   }
   __syncthreads();
@@ -570,7 +595,45 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   const uint32_t tmem = bars->tmem_base;
   AbortCtx ab{&bars->abort_flag, p.err};
 
-  if (warp >= 16) {
+  if (kFuseDq && warp >= kDkvDrainWarp) {
+    // ------------------------------------------------------------------ dQ drain (fused form)
+    // Thread = q row of the pair's dQ tile (TMEM lane) x all 128 head-dim columns, read 32 at a
+    // time and added to the fp32 image with four-wide reds.  The TMEM columns are handed back
+    // to the issuing thread as soon as the last load has completed, before the last reds go out.
+    setmaxnreg_dec<kFusedDrainRegs>();
+    const int wq = warp & 3;
+    const int r = wq * 32 + lane;
+    const uint32_t t_dq = tmem + ((uint32_t)(wq * 32) << 16) + kTile;
+    const int n_q_tiles = p.q_len / kTile;
+    bool ok = true;
+    uint32_t n = 0;
+    for (int g = 0; g < group && ok; ++g) {
+      const int head = kv_head * group + g;
+      float* head_base = p.dq_acc + ((int64_t)batch * p.q_heads + head) * n_q_tiles * (int64_t)kDqTileFloats + r * 4;
+      for (int e = ebeg; e < eend && ok; ++e, ++n) {
+        float* dst = head_base + (int64_t)entries[e].x * kDqTileFloats;
+        ok = mbar_wait(&bars->dq_full, n & 1u, ab, 0x3600u);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint32_t v[32];
+          tmem_ld32(t_dq + c * 32, v);
+          tmem_ld_wait();
+          if (c == 3) {
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->dq_free);
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            red_add_v4(dst + (c * 8 + j) * (kTile * 4), __uint_as_float(v[4 * j]), __uint_as_float(v[4 * j + 1]),
+                       __uint_as_float(v[4 * j + 2]), __uint_as_float(v[4 * j + 3]));
+        }
+      }
+    }
+  } else if (warp >= 16) {
    if (warp == kDkvTmaWarp) {
     if (lane == 0 && n_steps > 0) {
       tma_prefetch_desc(&tm_q);
@@ -631,6 +694,10 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // descriptors of the stationary operands, built once
       const SmemDesc k_desc = make_smem_desc_sw128(k_addr, 16, 1024), v_desc = make_smem_desc_sw128(v_addr, 16, 1024);
       const SmemDesc ds_desc = make_smem_desc_sw128(ds_addr, 16, 1024);
+      // fused form: the same two tiles seen MN-major (rows are the MMA's K dimension)
+      constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, kHeadDim, true, true);
+      const SmemDesc ds_mn_desc = make_smem_desc_sw128(ds_addr, kHalfBytes, 1024);
+      const SmemDesc k_mn_desc = make_smem_desc_sw128(k_addr, kHalfBytes, 1024);
       bool ok = mbar_wait(&bars->stat_full[0], 0, ab, 0x3200u) && mbar_wait(&bars->stat_full[1], 0, ab, 0x3201u);
       ok = ok && ring_wait(0, 0x3210u);
       if (ok) {
@@ -663,6 +730,16 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         ok = mbar_wait(&bars->ds_full, ph, ab, 0x3230u);
         if (!ok) break;
+        if constexpr (kFuseDq) {
+          // dQ_partial = dS K over the dP^T columns (every compute warp has read dP^T(n) before it
+          // arrived on ds_full): A = the dS^T tile read MN-major (M = q), B = the K tile read
+          // MN-major (N = head dim), K = 128 kv rows in eight slices.  Issued ahead of dK so the
+          // drain warps read it out while dK runs.
+#pragma unroll
+          for (int k = 0; k < 8; ++k)
+            umma_ss(t_dpt, desc_at(ds_mn_desc, k * 2048), desc_at(k_mn_desc, k * 2048), idesc_dq, k > 0 ? 1u : 0u);
+          tc_commit(&bars->dq_full);
+        }
         // dK += dS^T Q: A = dS^T from shared memory (K-major, two 64-column halves), B = the Q
         // tile read MN-major
         const SmemDesc q_mn = make_smem_desc_sw128(q_slot, kHalfBytes, 1024);
@@ -677,6 +754,10 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (more) {
           ok = ring_wait(2 * (n + 1) + 1, 0x3241u);
           if (!ok) break;
+          if constexpr (kFuseDq) {  // the dP^T columns still hold dQ_partial(n) until it is drained
+            ok = mbar_wait(&bars->dq_free, ph, ab, 0x3250u);
+            if (!ok) break;
+          }
           issue_score(t_dpt, v_desc, slot_addr(2 * (n + 1) + 1));
           tc_commit(&bars->dpt_full);
         }
@@ -686,6 +767,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
    }
   } else {
     // 16 warps on one 128 x 128 tile: thread = kv row (TMEM lane) x one 32-column quarter.
+    if constexpr (kFuseDq) setmaxnreg_inc<kFusedComputeRegs>();
     const int cq = warp >> 2;      // column quarter 0..3
     const int wq = warp & 3;       // TMEM lane quarter
     const int r = wq * 32 + lane;  // kv row within the tile
@@ -882,12 +964,61 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 }
 
 // ------------------------------------------------------------------------------------------
+// fused form: fp32 dQ image -> bf16 dQ
+// ------------------------------------------------------------------------------------------
+// One CTA per 128 x 128 tile.  A warp instruction reads eight 64-byte runs of the image (four rows
+// of one 4-column group each) and writes four 64-byte runs of bf16 rows, so both sides move whole
+// 32-byte sectors; HBM-bound: 512 + 256 bytes per q row.
+struct DqConvertParams {
+  const float* acc;
+  __nv_bfloat16* dq;
+  int64_t dq_sb, dq_sh, dq_ss;
+  int q_heads, n_q_tiles;
+  float scale;
+};
+
+__global__ void __launch_bounds__(256) splash_dq_convert_kernel(const DqConvertParams p) {
+  const int64_t tile = blockIdx.x;
+  const int qt = (int)(tile % p.n_q_tiles);
+  const int64_t bh = tile / p.n_q_tiles;
+  const int h = (int)(bh % p.q_heads);
+  const int64_t b = bh / p.q_heads;
+  const float4* src = reinterpret_cast<const float4*>(p.acc + tile * kDqTileFloats);
+  __nv_bfloat16* dst = p.dq + b * p.dq_sb + h * p.dq_sh + (int64_t)qt * kTile * p.dq_ss;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jj = lane & 7, rr = lane >> 3;
+  float4 v[16];
+#pragma unroll
+  for (int it = 0; it < 4; ++it)
+#pragma unroll
+    for (int jg = 0; jg < 4; ++jg) v[it * 4 + jg] = __ldcs(src + (jg * 8 + jj) * kTile + warp * 16 + it * 4 + rr);
+#pragma unroll
+  for (int it = 0; it < 4; ++it) {
+    const int r = warp * 16 + it * 4 + rr;
+#pragma unroll
+    for (int jg = 0; jg < 4; ++jg) {
+      const float4 x = v[it * 4 + jg];
+      uint2 w;
+      w.x = pack_bf16(x.x * p.scale, x.y * p.scale);
+      w.y = pack_bf16(x.z * p.scale, x.w * p.scale);
+      *reinterpret_cast<uint2*>(dst + (int64_t)r * p.dq_ss + (jg * 8 + jj) * 4) = w;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // host launcher
 // ------------------------------------------------------------------------------------------
 size_t bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {
   if (batch <= 0 || q_heads <= 0 || q_len <= 0) return 0;
   const size_t n = (size_t)batch * (size_t)q_heads * (size_t)q_len * sizeof(float);
   return 2 * ((n + 255) & ~(size_t)255);  // di, then -logsumexp * log2(e)
+}
+// Fused form: the same two per-row arrays, then the fp32 dQ image.
+size_t bwd_fused_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {
+  const size_t base = bwd_workspace_bytes(batch, q_heads, q_len);
+  if (base == 0) return 0;
+  return base + (size_t)batch * (size_t)q_heads * (size_t)q_len * kHeadDim * sizeof(float);
 }
 
 int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
@@ -911,13 +1042,14 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     return SPLASH_ERR_INVALID_ARGUMENT;
   if (a.logsumexp == nullptr || a.error_record == nullptr || a.workspace == nullptr)
     return SPLASH_ERR_INVALID_ARGUMENT;
-  if (a.workspace_bytes < bwd_workspace_bytes(B, Hq, Sq)) return SPLASH_ERR_INVALID_ARGUMENT;
+  const bool fused = (a.flags & SPLASH_BWD_FUSED_DQ) != 0;
+  if (a.workspace_bytes < (fused ? bwd_fused_workspace_bytes(B, Hq, Sq) : bwd_workspace_bytes(B, Hq, Sq)))
+    return SPLASH_ERR_INVALID_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0) return SPLASH_ERR_INVALID_ARGUMENT;
-  if (a.sched_dq.row_ptr == nullptr || a.sched_dq.entries == nullptr ||
-      a.sched_dkv.row_ptr == nullptr || a.sched_dkv.entries == nullptr)
+  if (a.sched_dkv.row_ptr == nullptr || a.sched_dkv.entries == nullptr || a.sched_dkv.n_rows != Skv / kTile)
     return SPLASH_ERR_INVALID_ARGUMENT;
-  if (a.sched_dq.n_rows != Sq / kTile || a.sched_dkv.n_rows != Skv / kTile)
-    return SPLASH_ERR_INVALID_ARGUMENT;
+  if (!fused && (a.sched_dq.row_ptr == nullptr || a.sched_dq.entries == nullptr || a.sched_dq.n_rows != Sq / kTile))
+    return SPLASH_ERR_INVALID_ARGUMENT;  // the fused form walks the dkv schedule only
   if (a.mask_fn.kind == SPLASH_MASK_CHUNKED && a.mask_fn.chunk <= 0)
     return SPLASH_ERR_INVALID_ARGUMENT;
   if (Hq > 65535 || B > 65535 || Sq / kTile > 65535 || Skv / kTile > 65535) return SPLASH_ERR_TOO_LARGE;
@@ -931,6 +1063,11 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   const uint32_t mask = a.launch_mask == 0 ? 7u : a.launch_mask;
   float* delta = static_cast<float*>(a.workspace);
   float* nlse2 = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + bwd_workspace_bytes(B, Hq, Sq) / 2);
+  float* dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + bwd_workspace_bytes(B, Hq, Sq));
+  if (fused && (mask & 1u)) {  // the image the reds add into starts at zero
+    if (cudaMemsetAsync(dq_acc, 0, (size_t)B * Hq * Sq * kHeadDim * sizeof(float), stream) != cudaSuccess)
+      return SPLASH_ERR_CUDA;
+  }
   if (mask & 1u) {
     DeltaParams dp;
     dp.o = static_cast<const __nv_bfloat16*>(a.o.data);
@@ -955,19 +1092,24 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   const bool soft_cap = a.soft_cap != 0.f;
   if (soft_cap && !(a.soft_cap > 0.f)) return SPLASH_ERR_INVALID_ARGUMENT;
   auto* dq_kernel = soft_cap ? splash_dq_kernel<true> : splash_dq_kernel<false>;
-  auto* dkv_kernel = soft_cap ? splash_dkv_kernel<true> : splash_dkv_kernel<false>;
+  auto* dkv_kernel = fused ? (soft_cap ? splash_dkv_kernel<true, true> : splash_dkv_kernel<false, true>)
+                           : (soft_cap ? splash_dkv_kernel<true, false> : splash_dkv_kernel<false, false>);
   const int dkv_smem = kDkvSmemBytes;
   // function attributes are per device: remember which devices have been set up
-  static bool attr_done[64][2] = {};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess) return SPLASH_ERR_CUDA;
-  bool* attr_set = attr_done[dev & 63];
-  if (!attr_set[soft_cap]) {
-    if (cudaFuncSetAttribute(dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmemBytes) !=
-            cudaSuccess ||
-        cudaFuncSetAttribute(dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv_smem) != cudaSuccess)
-      return SPLASH_ERR_CUDA;
-    attr_set[soft_cap] = true;
+  {
+    static std::mutex attr_mu;
+    static bool attr_done[64][4] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SPLASH_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(attr_mu);
+    bool& done = attr_done[dev][(soft_cap ? 1 : 0) + (fused ? 2 : 0)];
+    if (!done) {
+      if (cudaFuncSetAttribute(dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kDqSmemBytes) !=
+              cudaSuccess ||
+          cudaFuncSetAttribute(dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, dkv_smem) != cudaSuccess)
+        return SPLASH_ERR_CUDA;
+      done = true;
+    }
   }
 
   BwdParams p;
@@ -986,8 +1128,9 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.err = a.error_record;
   p.soft_cap = a.soft_cap;
   p.softcap_a = soft_cap ? a.scale / a.soft_cap : 0.f;
+  p.dq_acc = fused ? dq_acc : nullptr;
 
-  // dq
+  // dq (split form)
   p.out0 = static_cast<__nv_bfloat16*>(a.dq.data);
   p.out0_sb = a.dq.stride[0];
   p.out0_sh = a.dq.stride[1];
@@ -1007,7 +1150,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.n_groups = (int)(Hq * B);
   p.chunk_groups = chunk_groups_for(2 * Skv * kHeadDim * 2 / (Hq / Hkv), p.n_groups, Hq / Hkv);
   if ((int64_t)p.n_rows * p.n_groups > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
-  if (mask & 2u)
+  if (!fused && (mask & 2u))
     dq_kernel<<<dim3((unsigned)(p.n_rows * p.n_groups), 1u, 1u), kBwdThreads, kDqSmemBytes, stream>>>(
         tm_q, tm_do, tm_k, tm_v, p);
   if (cudaGetLastError() != cudaSuccess) return SPLASH_ERR_CUDA;
@@ -1032,11 +1175,27 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.n_rows = a.sched_dkv.n_rows;
   // dkv: the kv tiles of one (batch, kv head) stream the same Q / dO of its q-head group
   p.n_groups = (int)(Hkv * B);
-  p.chunk_groups = chunk_groups_for(2 * (Hq / Hkv) * Sq * kHeadDim * 2, p.n_groups, 1);
+  // (fused: plus the fp32 dQ image of those heads, which the reds keep in L2)
+  p.chunk_groups = chunk_groups_for((Hq / Hkv) * Sq * kHeadDim * (fused ? 8 : 4), p.n_groups, 1);
   if ((int64_t)p.n_rows * p.n_groups > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
   if (mask & 4u)
-    dkv_kernel<<<dim3((unsigned)(p.n_rows * p.n_groups), 1u, 1u), kDkvThreads, dkv_smem, stream>>>(
-        tm_q, tm_do, tm_k, tm_v, p);
+    dkv_kernel<<<dim3((unsigned)(p.n_rows * p.n_groups), 1u, 1u), fused ? kFusedThreads : kDkvThreads, dkv_smem,
+                 stream>>>(tm_q, tm_do, tm_k, tm_v, p);
+  if (cudaGetLastError() != cudaSuccess) return SPLASH_ERR_CUDA;
+  if (fused && (mask & 2u)) {
+    DqConvertParams cp;
+    cp.acc = dq_acc;
+    cp.dq = static_cast<__nv_bfloat16*>(a.dq.data);
+    cp.dq_sb = a.dq.stride[0];
+    cp.dq_sh = a.dq.stride[1];
+    cp.dq_ss = a.dq.stride[2];
+    cp.q_heads = (int)Hq;
+    cp.n_q_tiles = (int)(Sq / kTile);
+    cp.scale = a.scale;
+    const int64_t n_tiles = B * Hq * (Sq / kTile);
+    if (n_tiles > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
+    splash_dq_convert_kernel<<<(unsigned)n_tiles, 256, 0, stream>>>(cp);
+  }
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
 }
 
@@ -1069,6 +1228,7 @@ int launch_bwd_static_scratch(const SplashBwdArgs& a, cudaStream_t stream) {
     scratch = device_ptr[dev];
   }
   SplashBwdArgs b = a;
+  b.flags &= ~(uint32_t)SPLASH_BWD_FUSED_DQ;  // the array holds the two per-row terms only
   b.workspace = scratch;
   b.workspace_bytes = bwd_workspace_bytes(B, Hq, Sq);  // <= sizeof(g_static_scratch) by the row check
   return launch_bwd(b, stream);

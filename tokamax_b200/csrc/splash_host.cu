@@ -13,6 +13,7 @@ int launch_fwd_fp8(const SplashFwdFp8Args& a, cudaStream_t stream);
 int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream);
 int launch_bwd_static_scratch(const SplashBwdArgs& a, cudaStream_t stream);
 size_t bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
+size_t bwd_fused_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len);
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
@@ -86,9 +87,35 @@ int make_tile_tensor_map(CUtensorMap* out, const SplashTensor& t, int box_rows) 
   return r == CUDA_SUCCESS ? SPLASH_OK : SPLASH_ERR_CUDA;
 }
 
+#ifdef SPLASH_TEST_HOOKS
+// One thread waits, through the same mbar_wait the attention kernels use, on a barrier that
+// nothing ever arrives on; the wait gives up after `limit_cycles` and the kernel returns.
+__global__ void bounded_wait_probe_kernel(uint32_t* err, long long limit_cycles, uint32_t tag) {
+  __shared__ uint64_t bar;
+  __shared__ uint32_t flag;
+  if (threadIdx.x == 0) {
+    flag = 0;
+    mbar_init(&bar, 1);
+    mbar_fence_init();
+    AbortCtx ab{&flag, err, limit_cycles};
+    (void)mbar_wait(&bar, 0, ab, tag);
+  }
+}
+#endif
+
 }  // namespace sb
 
 extern "C" {
+
+#ifdef SPLASH_TEST_HOOKS
+// Test hook (only in the "checked" build): makes a bounded device wait run out.  The record then
+// holds {1, block, tag, thread}; splash_read_error maps it to SPLASH_ERR_KERNEL_TIMEOUT.
+int splash_test_bounded_wait(uint32_t* error_record, long long limit_cycles, uint32_t tag, void* cuda_stream) {
+  if (error_record == nullptr || limit_cycles <= 0 || limit_cycles > 100000000ll) return SPLASH_ERR_INVALID_ARGUMENT;
+  sb::bounded_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(error_record, limit_cycles, tag);
+  return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
+}
+#endif
 
 int splash_fwd(const SplashFwdArgs* args, void* cuda_stream) {
   if (args == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;
@@ -102,6 +129,10 @@ int splash_fwd_fp8(const SplashFwdFp8Args* args, void* cuda_stream) {
 
 size_t splash_bwd_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {
   return sb::bwd_workspace_bytes(batch, q_heads, q_len);
+}
+
+size_t splash_bwd_fused_workspace_bytes(int64_t batch, int64_t q_heads, int64_t q_len) {
+  return sb::bwd_fused_workspace_bytes(batch, q_heads, q_len);
 }
 
 int splash_bwd(const SplashBwdArgs* args, void* cuda_stream) {

@@ -77,7 +77,9 @@ def splash_fwd_fp8(kernel: _k.SplashAttentionKernel, q: Fp8Tensor, k: Fp8Tensor,
                      f"mask {kernel.mask_shape}")
   if kd.shape[1] == 0 or hq % kd.shape[1] != 0:
     raise ValueError(f"q heads ({hq}) must be a multiple of kv heads ({kd.shape[1]})")
-  tables = kernel._tables(qd.device)  # pylint: disable=protected-access
+  if kernel.config.attn_logits_soft_cap is not None:
+    raise NotImplementedError("attn_logits_soft_cap is not built for the e4m3 forward")
+  tables = kernel._tables(qd.device, b)  # pylint: disable=protected-access  (device masks: one table per batch size)
   o = torch.empty((b, hq, sq, d), dtype=torch.bfloat16, device=qd.device)
   lse = torch.empty((b, hq, sq), dtype=torch.float32, device=qd.device)
   max_logits = torch.empty((b, hq, sq), dtype=torch.float32, device=qd.device)

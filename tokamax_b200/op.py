@@ -84,7 +84,32 @@ class CudaSm100SplashAttention:
     scale = h ** -0.5 if logits_scale == AUTO else float(logits_scale)
     cap = None if logits_soft_cap is None else float(logits_soft_cap)
 
-    if mask is not None:
+    if isinstance(mask, torch.Tensor) and mask.is_cuda:
+      # A mask that is data on the device takes the dynamic path, as the reference's adapter does
+      # for array masks (pallas_mosaic_tpu_common.py:96-102): tile states and schedules are built
+      # on the device, nothing is copied to the host.
+      m = mask.to(torch.bool)
+      while m.dim() > 2 and m.shape[0] == 1:
+        m = m[0]
+      if m.dim() != 2:
+        raise NotImplementedError("only a [T, S] mask shared by batch and heads is supported")
+      m = m.expand(t, s)
+      if is_causal or local_window_size is not None:
+        rel = torch.arange(s, device=m.device)[None, :] - torch.arange(t, device=m.device)[:, None]  # k - q
+        if is_causal:
+          m = m & (rel <= 0)
+        if local_window_size is not None:
+          w = (local_window_size, local_window_size) if isinstance(local_window_size, int) else tuple(local_window_size)
+          if w[0] is not None:
+            m = m & (rel >= -w[0])
+          if w[1] is not None:
+            m = m & (rel <= w[1])
+      config = None
+      if cap is not None:
+        config = dataclasses.replace(splash.SplashConfig.get_default(), attn_logits_soft_cap=cap)
+      kernel = splash.make_dynamic_splash_mha(m.contiguous(), save_residuals=True, config=config,
+                                              mask_value=float(np.finfo(np.float32).min), downcast_smem_data=False)
+    elif mask is not None:
       m = np.asarray(mask.detach().cpu() if hasattr(mask, "detach") else mask).astype(np.bool_)
       while m.ndim > 2 and m.shape[0] == 1:
         m = m[0]

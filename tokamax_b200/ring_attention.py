@@ -364,7 +364,7 @@ def make_ring_attention(mask: np.ndarray | mask_lib.Mask, *, config=None, is_mqa
                         save_residuals: bool = False, mask_value: float = DEFAULT_MASK_VALUE,
                         downcast_smem_data: bool = True, partial_mask_blocks_dtype: Any = np.int8,
                         ring_axis=None, q_seq_shards: int = 1, kv_seq_shards: int = 1,
-                        layout: str = "contiguous") -> RingSplashAttention:
+                        layout: str = "contiguous", repeatable_dq: bool = False) -> RingSplashAttention:
   """Reference factory (:617-705).  ``ring_axis`` is the process group of the ring (default: the
   world); ``layout`` is an addition (see `RingSplashAttention`)."""
   del q_seq_shards, kv_seq_shards  # the ring size is the group's size; sub-masks are cut per pair
@@ -374,7 +374,8 @@ def make_ring_attention(mask: np.ndarray | mask_lib.Mask, *, config=None, is_mqa
     mask = mask_lib.NumpyMask(mask)
   if is_mqa:
     raise NotImplementedError("pass MQA keys / values with a kv-head axis of 1")
-  kwargs = dict(downcast_smem_data=downcast_smem_data, partial_mask_blocks_dtype=partial_mask_blocks_dtype)
+  kwargs = dict(downcast_smem_data=downcast_smem_data, partial_mask_blocks_dtype=partial_mask_blocks_dtype,
+                repeatable_dq=repeatable_dq)
   if config is not None:
     kwargs["config"] = config
   return RingSplashAttention(mask, group=ring_axis, save_residuals=save_residuals, mask_value=mask_value,

@@ -218,10 +218,12 @@ class _DynamicDeviceTables:
     q_len, kv_len = mask.shape
     if q_len % _TILE or kv_len % _TILE:
       raise NotImplementedError(f"mask sides must be multiples of {_TILE} on B200, got {tuple(mask.shape)}")
-    m = mask.contiguous().view(torch.uint8)
+    # Snapshot: the kernels read the mask in place on every call, so a copy is kept; a caller who
+    # updates its tensor afterwards builds a new kernel object.
+    m = mask.contiguous().view(torch.uint8).clone()
     mt = m.t().contiguous()
-    if m.data_ptr() % 16 or mt.data_ptr() % 16:
-      m, mt = m.clone(), mt.clone()
+    if mt.data_ptr() % 16:
+      mt = mt.clone()
     states = torch.empty((q_len // _TILE, kv_len // _TILE), dtype=torch.int32, device=device)
     stream = C.c_void_p(torch.cuda.current_stream(device).cuda_stream)
     self.keep = [m, mt, states]
@@ -357,9 +359,12 @@ def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg
   d_o = _usable(d_o)
   dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
   lib = _native.lib()
-  ws_bytes = lib.splash_bwd_workspace_bytes(q.shape[0], q.shape[1], q.shape[2])
+  fused = not kernel.repeatable_dq
+  size_fn = lib.splash_bwd_fused_workspace_bytes if fused else lib.splash_bwd_workspace_bytes
+  ws_bytes = size_fn(q.shape[0], q.shape[1], q.shape[2])
   workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
   args = _native.SplashBwdArgs()
+  args.flags = _native.BWD_FUSED_DQ if fused else 0
   args.q, args.k, args.v, args.o, args.d_o = map(_tensor_desc, (q, k, v, o, d_o))
   args.dq, args.dk, args.dv = map(_tensor_desc, (dq, dk, dv))
   args.logsumexp = lse.data_ptr()
@@ -370,9 +375,11 @@ def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg
   args.sched_dq = tables.dq
   args.sched_dkv = tables.dkv
   if q_seg is not None and not tables.dq.row_end:
-    args.sched_dq, ws1 = _segment_schedule(tables.dq, 1, q_seg, kv_seg, q.shape[2], k.shape[2])
+    if not fused:  # the fused form walks the dkv schedule only
+      args.sched_dq, ws1 = _segment_schedule(tables.dq, 1, q_seg, kv_seg, q.shape[2], k.shape[2])
+      keep.append(ws1)
     args.sched_dkv, ws2 = _segment_schedule(tables.dkv, 2, q_seg, kv_seg, q.shape[2], k.shape[2])
-    keep += [ws1, ws2]
+    keep.append(ws2)
   args.mask_fn = _mask_fn_struct(kernel.mask_function_rule)
   args.scale = scale
   args.workspace = workspace.data_ptr()
@@ -433,6 +440,18 @@ class SplashAttentionKernel:
   mask_function = property(lambda self: self.kwargs.get("mask_function"))
   mask_function_rule = property(lambda self: self.kwargs.get("mask_function_rule"))
   mask_shape = property(lambda self: self.kwargs["mask_shape"])
+  # False (default): the fused backward — one kernel, five matmuls per live block like the
+  # reference's (kernel.py:1234-1459), dq partials summed by fp32 reductions whose order varies
+  # between runs.  True: separate dq and dkv kernels, every gradient bitwise repeatable.
+  repeatable_dq = property(lambda self: bool(self.kwargs.get("repeatable_dq", False)))
+
+  def with_options(self, **kwargs) -> "SplashAttentionKernel":
+    """A kernel object for the same mask with some keyword options replaced (``repeatable_dq``,
+    ``save_residuals``, ``mask_value``); device tables and the error record are shared."""
+    other = SplashAttentionKernel(self._fwd_mask_info, self._dkv_mask_info, dynamic_mask=self._dynamic_mask,
+                                  **dict(self.kwargs, **kwargs))
+    other._device_tables = self._device_tables  # pylint: disable=protected-access
+    return other
 
   def _tables(self, device: torch.device, batch: int = 1):
     if self._dynamic_mask is not None:
@@ -448,7 +467,12 @@ class SplashAttentionKernel:
     return self._device_tables[key]
 
   def check_errors(self) -> None:
-    """Synchronises and raises if a kernel reported a device-side fault (bounded wait ran out)."""
+    """Synchronises and raises if a kernel reported a device-side fault (bounded wait ran out).
+
+    While a record holds an error, every kernel launched with it returns at once and leaves its
+    outputs unwritten, so results produced since the fault are garbage.  Raising clears the
+    record: the kernel object is usable again afterwards.
+    """
     lib = _native.lib()
     for tables in self._device_tables.values():
       rec = (C.c_uint32 * 4)()
@@ -457,6 +481,7 @@ class SplashAttentionKernel:
       with torch.cuda.device(dev):
         st = lib.splash_read_error(tables.error_record.data_ptr(), C.c_void_p(stream), C.byref(rec))
       if st != 0:
+        tables.error_record.zero_()
         raise _native.SplashError(st, f"device error record {list(rec)}")
 
   def _reject_unsupported(self, q, k, sinks, max_logit_value):
@@ -579,6 +604,7 @@ def _make_splash_attention(
     downcast_smem_data: bool = True,
     partial_mask_blocks_dtype: Any = np.int8,
     q_seq_shards: int,
+    repeatable_dq: bool = False,
 ):
   if len(mask.shape) != 2:
     raise ValueError(f"Unexpected mask shape: {mask.shape}")
@@ -626,6 +652,7 @@ def _make_splash_attention(
       mask_shape=tuple(mask.shape),
       fwd_mask_sparsity=fwd_mask_sparsity,
       dkv_mask_sparsity=dkv_mask_sparsity,
+      repeatable_dq=repeatable_dq,
   )
 
 
@@ -640,6 +667,7 @@ def _make_dynamic_splash_attention(
     mask_value: float = DEFAULT_MASK_VALUE,
     downcast_smem_data: bool = True,
     partial_mask_blocks_dtype: Any = np.int8,
+    repeatable_dq: bool = False,
 ):
   """Kernel for a mask that is data (a bool array / tensor) rather than a static object."""
   if (mesh is not None) != (mask_spec is not None):
@@ -657,7 +685,7 @@ def _make_dynamic_splash_attention(
     return SplashAttentionKernel(
         None, None, dynamic_mask=mask, config=config, is_mqa=is_mqa, save_residuals=save_residuals,
         mask_value=mask_value, mask_function=None, mask_function_rule=None, mask_shape=tuple(mask.shape),
-        fwd_mask_sparsity=1.0, dkv_mask_sparsity=1.0)
+        fwd_mask_sparsity=1.0, dkv_mask_sparsity=1.0, repeatable_dq=repeatable_dq)
   process = partial(
       mask_info_lib._process_dynamic_mask,  # pylint: disable=protected-access
       downcast_smem_data=downcast_smem_data,
@@ -679,6 +707,7 @@ def _make_dynamic_splash_attention(
       mask_shape=tuple(mask.shape),
       fwd_mask_sparsity=1.0,
       dkv_mask_sparsity=1.0,
+      repeatable_dq=repeatable_dq,
   )
 
 
