@@ -6,16 +6,20 @@
 A step is one forward + backward of splash attention over one batch of synthetic inputs
 (Q, K, V, dO ~ N(0,1) in bf16 from fixed seeds, softmax scale 1/sqrt(128)).  The metric is
 mask-counted TFLOP/s: 14 * D * B * Hq * N_live FLOPs per step, N_live = number of unmasked
-(query, key) pairs.  Workloads (BASELINE.json configs):
+(query, key) pairs.  Workloads:
 
   c2  causal, B=4, S=8192, Hq=32, Hkv=8, D=128 (Llama-3-8B shape)        -- default at N=1
   c4  causal, B=1, S=131072, Hq=64, Hkv=8, D=128, Ulysses context parallel -- default at N>1
   c1  causal, B=2, S=1024, Hq=Hkv=8                                        -- the CPU-sized case
   c3  local window 4096 + causal with packed-document segment ids, B=8, S=16384, Hq=Hkv=16
 
-One JSON line is printed by rank 0.  ``--impl reference`` times the CPU restatement of the
-reference's own fp32 attention (oracle/) on the host cores on a bounded sample of the same
-workload (JAX, which the reference needs, is not installed on this image).
+  c5  causal, B=2, S=32768, Hq=32, Hkv=8, e4m3 inputs with per-128-token scales, forward only
+
+One JSON line is printed by rank 0.  At N = 1 the line also carries short runs of c3 and c5 under
+``other_workloads``; at N > 1 it carries the same step timed on one GPU alone (``cp.single_gpu_ms_per_step``)
+so that the scaling efficiency refers to one workload.  ``--impl reference`` times the CPU restatement
+of the reference's own fp32 attention (oracle/) on all host cores on a bounded sample of the same
+workload (the reference itself needs JAX, which is not installed here).
 """
 
 from __future__ import annotations
@@ -207,6 +211,34 @@ def timed_steps(step_fn, steps: int, warmup: int, barrier=None) -> float:
   return e0.elapsed_time(e1) / steps
 
 
+def pinned_copy_gbs(device, nbytes: int = 256 << 20) -> dict:
+  """Standalone host<->device copy rates of this box from pinned memory (GB/s), for reading `e2e`:
+  a slow end-to-end number on a fast kernel is the host link, not the pipeline."""
+  host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
+  dev_buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+  out = {}
+  for name, fn in (("h2d", lambda: dev_buf.copy_(host, non_blocking=True)),
+                   ("d2h", lambda: host.copy_(dev_buf, non_blocking=True))):
+    out[name + "_gbs"] = nbytes / timed_steps(fn, 5, 2) / 1e6
+  return out
+
+
+def fp8_gemm_peak_tflops(device) -> float | None:
+  """Dense e4m3 x e4m3 -> bf16 GEMM rate of this GPU (torch._scaled_mm, 8192^3, best of 10), the
+  denominator for the e4m3 forward; None if the call is not available."""
+  try:
+    n = 8192
+    a = torch.randn(n, n, device=device).to(torch.float8_e4m3fn)
+    b = torch.randn(n, n, device=device).to(torch.float8_e4m3fn).t()  # column-major operand
+    one = torch.ones((), device=device, dtype=torch.float32)
+    fn = lambda: torch._scaled_mm(a, b, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)  # pylint: disable=protected-access
+    fn()
+    best = min(timed_steps(fn, 1, 1) for _ in range(10))
+    return 2 * n ** 3 / best / 1e9
+  except Exception:  # pylint: disable=broad-except
+    return None
+
+
 def measured_peaks():
   path = os.path.join(ROOT, "MEASURED_PEAKS.json")
   if os.path.exists(path):
@@ -216,9 +248,9 @@ def measured_peaks():
   return 1590.0, 1400.0, "fallback"
 
 
-# DRAM traffic of one dkv-kernel launch on the c2 workload (dram__bytes_read.sum +
-# dram__bytes_write.sum), taken from the ncu capture summarised in profiles/splash_dkv_kernel_c2.md.
-DKV_TRAFFIC_BYTES_C2 = 843.6e6
+# DRAM traffic of one launch of the dominant kernel on the c2 workload (dram__bytes_read.sum +
+# dram__bytes_write.sum from an ncu capture of that kernel), per backward form; None: not captured.
+KERNEL_TRAFFIC_BYTES_C2 = {"dkv": 843.6e6, "bwd_fused": None}
 
 
 def per_kernel_times(kernel, q, k, v, do, seg, iters: int = 5) -> dict:
@@ -289,22 +321,35 @@ def per_kernel_times(kernel, q, k, v, do, seg, iters: int = 5) -> dict:
   return out
 
 
-def cpu_baseline(w: dict, seconds_budget: float = 20.0) -> dict:
-  """Oracle forward + backward on the host cores over a bounded sample of the workload."""
-  from oracle import attention_ref
-  from tokamax_b200 import splash_attention_mask as mask_lib
+def _dense_causal(s: int) -> np.ndarray:
+  return np.tril(np.ones((s, s), dtype=np.bool_))
 
+
+def _dense_window_causal(s: int, left: int) -> np.ndarray:
+  idx = np.arange(s)
+  return (idx[None, :] <= idx[:, None]) & (idx[None, :] >= idx[:, None] - left)
+
+
+def cpu_baseline(w: dict, seconds_budget: float = 20.0) -> dict:
+  """Oracle forward + backward on the host cores over a bounded sample of the workload.
+
+  Touches nothing but the oracle and numpy / torch-CPU (the CUDA library is not loaded here), and
+  uses every host core: a launcher may have set OMP_NUM_THREADS=1 for its ranks.
+  """
+  from oracle import attention_ref
+
+  torch.set_num_threads(os.cpu_count() or 1)
   s = min(w["seq"], 8192)  # the dense fp32 oracle holds S x S logits; cap the sample's sequence
   group = w["q_heads"] // w["kv_heads"]
   g = torch.Generator().manual_seed(1000 * w["config_id"])
   mk = lambda h: torch.randn(1, h, s, D, generator=g, dtype=torch.float32).to(torch.bfloat16)
   q, k, v, do = mk(group), mk(1), mk(1), mk(group)
   if w["mask"] == "causal":
-    mask = mask_lib.make_causal_mask((s, s))
+    mask = _dense_causal(s)
     seg = None
     n_live = s * (s + 1) // 2
   else:
-    mask = mask_lib.make_local_attention_mask((s, s), (4096, 0))
+    mask = _dense_window_causal(s, 4096)
     ids = packed_segments(1, s, 3)
     seg = (torch.from_numpy(ids), torch.from_numpy(ids))
     n_live = live_pairs(dict(w, batch=1, seq=s), ids)
@@ -324,7 +369,8 @@ def cpu_baseline(w: dict, seconds_budget: float = 20.0) -> dict:
       "kind": "port",
       "sample": (f"1 batch row x 1 kv head ({group} q heads) of {w['mask']} seq {s}, fwd+bwd, {reps} reps in "
                  f"{dt:.1f} s; torch-CPU fp32 restatement of the reference's attention_reference[_vjp]"),
-      "maskinfo_build_ms": maskinfo_build_times(w),
+      "sample_seq": s,
+      "same_seq_as_workload": s == w["seq"],
   }
 
 
@@ -372,7 +418,9 @@ def run_reference(args, w, wname):
       "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
       "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
       "config": {"workload": wname, **{k: w[k] for k in ("batch", "q_heads", "kv_heads", "seq", "mask")},
-                 "head_dim": D, "note": "bounded sample per step on host cores"},
+                 "head_dim": D, "sample_seq": base["sample_seq"],
+                 "note": "each step is a bounded sample of the workload (one batch row x one kv-head group at "
+                         "sample_seq tokens) on all host cores"},
       "cpu_baseline": base,
       "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
       "gpu_launches": 0,
@@ -380,7 +428,7 @@ def run_reference(args, w, wname):
   print(json.dumps(line), flush=True)
 
 
-def run_single_gpu(args, w, wname):
+def run_single_gpu(args, w, wname, emit=True):
   from tokamax_b200 import splash_attention_kernel as splash
 
   dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
@@ -457,12 +505,14 @@ def run_single_gpu(args, w, wname):
             src.record_stream(s_out)
       main.wait_stream(s_out)
 
-    ms_e2e = timed_steps(e2e_step, max(2, min(args.steps, 5)), 1)
+    e2e_steps = max(10, min(args.steps, 20))
+    ms_e2e = timed_steps(e2e_step, e2e_steps, 2)
     h2d = sum(t.numel() * 2 for t in (hq, hk, hv, hdo))
     d2h = sum(t.numel() * 2 for t in outs_host)
-    e2e = {"value": flops / ms_e2e / 1e9, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
-           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+    e2e = {"value": flops / ms_e2e / 1e9, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "steps": e2e_steps,
+           "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "pinned_copy": pinned_copy_gbs(dev),
            "note": "pinned host buffers in and out, copies pipelined per (batch row, kv-head range) unit on side streams"}
+    del hq, hk, hv, hdo, outs_host
 
   # ---- per-kernel times and the roofline of the dominant kernel
   peak, peak_sustained, peak_src = measured_peaks()
@@ -479,7 +529,7 @@ def run_single_gpu(args, w, wname):
       "kernel": {"fwd": "splash_fwd_kernel", "dq": "splash_dq_kernel", "dkv": "splash_dkv_kernel<.,false>",
                  "bwd_fused": "splash_dkv_kernel<.,true>"}[dominant],
       "bound": "tensor", "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
-      "peak_source": f"{peak_src} bf16 burst", "traffic": DKV_TRAFFIC_BYTES_C2 if (dominant == "dkv" and wname == "c2") else None,
+      "peak_source": f"{peak_src} bf16 burst", "traffic": KERNEL_TRAFFIC_BYTES_C2.get(dominant) if wname == "c2" else None,
       "backward_form": args.bwd,
       "kernel_ms": kt,
       "whole_step_frac_of_peak": value / peak, "whole_step_frac_of_sustained": value / peak_sustained,
@@ -489,18 +539,39 @@ def run_single_gpu(args, w, wname):
   line = {
       "metric": "splash fwd+bwd TFLOP/s (masked FLOPs)", "value": value, "unit": "TFLOP/s", "n_gpus": 1,
       "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
+      "scaling_note": "single GPU; the N > 1 runs of this script time another workload (c4, one long sequence split "
+                      "over the GPUs, strong scaling) and carry their own one-GPU time in cp.single_gpu_ms_per_step",
       "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
       "config": {"workload": wname, **{k_: w[k_] for k_ in ("batch", "q_heads", "kv_heads", "seq", "mask")},
                  "head_dim": D, "n_live_pairs": n_live, "flops_per_step": flops,
                  "l2": l2_note(w)},
       "clocks": clocks, "e2e": e2e, "gpu_launches": 4 * args.steps, "roofline": roofline,
   }
+  line["maskinfo_build_ms"] = maskinfo_build_times(w)
+  if wname == "c2" and not args.no_other_workloads:
+    # short runs of the other single-GPU workloads, so their numbers come from the same record
+    del q, k, v, do
+    torch.cuda.empty_cache()
+    short = argparse.Namespace(**{**vars(args), "steps": 5, "warmup": 3, "no_e2e": True, "no_cpu_baseline": True,
+                                  "no_other_workloads": True})
+    other = {}
+    for name, fn in (("c3", run_single_gpu), ("c5", run_fp8_prefill)):
+      sub = fn(short, WORKLOADS[name], name, emit=False)
+      other[name] = {"metric": sub["metric"], "value": sub["value"], "unit": sub["unit"], "ms_per_step": sub["ms_per_step"],
+                     "steps": sub["steps"], "dtype": sub["dtype"], "clocks": sub["clocks"],
+                     "frac_of_peak": sub["roofline"]["frac"], "peak": sub["roofline"]["peak"],
+                     "peak_source": sub["roofline"]["peak_source"], "config": sub["config"],
+                     "kernel_ms": sub["roofline"].get("kernel_ms")}
+      torch.cuda.empty_cache()
+    line["other_workloads"] = other
   if not args.no_cpu_baseline:
     line["cpu_baseline"] = cpu_baseline(w)
-  print(json.dumps(line), flush=True)
+  if emit:
+    print(json.dumps(line), flush=True)
+  return line
 
 
-def run_fp8_prefill(args, w, wname):
+def run_fp8_prefill(args, w, wname, emit=True):
   """Forward only on block-scaled e4m3 Q/K/V (scales per 128-token tile), bf16 output."""
   from tokamax_b200 import fp8
 
@@ -540,12 +611,19 @@ def run_fp8_prefill(args, w, wname):
       ts = [fp8.Fp8Tensor(d[2 * i].view(torch.float8_e4m3fn), d[2 * i + 1]) for i in range(3)]
       o_host.copy_(fp8.splash_fwd_fp8(kernel, *ts, logits_scale=SCALE), non_blocking=True)
 
-    ms_e2e = timed_steps(e2e_step, max(2, min(args.steps, 5)), 1)
-    e2e = {"value": flops / ms_e2e / 1e9, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+    e2e_steps = max(10, min(args.steps, 20))
+    ms_e2e = timed_steps(e2e_step, e2e_steps, 2)
+    e2e = {"value": flops / ms_e2e / 1e9, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "steps": e2e_steps,
+           "pinned_copy": pinned_copy_gbs(dev),
            "h2d_bytes_per_step": sum(t.numel() * t.element_size() for t in host),
            "d2h_bytes_per_step": o_host.numel() * 2}
 
   peak, _, peak_src = measured_peaks()
+  fp8_peak = fp8_gemm_peak_tflops(dev)
+  if fp8_peak is not None:
+    peak8, peak8_src = fp8_peak, "e4m3 GEMM (torch._scaled_mm, 8192^3) measured in this run"
+  else:
+    peak8, peak8_src = 2 * peak, f"2 x {peak_src} bf16 burst (an e4m3 GEMM could not be timed here)"
   line = {
       "metric": "splash fp8 forward TFLOP/s (masked FLOPs)", "value": value, "unit": "TFLOP/s", "n_gpus": 1,
       "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak",
@@ -554,12 +632,13 @@ def run_fp8_prefill(args, w, wname):
                  "head_dim": D, "n_live_pairs": n_live, "flops_per_step": flops,
                  "l2": "inputs (168 MB of e4m3 plus a 537 MB output) are larger than the 126 MB L2"},
       "clocks": clocks, "e2e": e2e, "gpu_launches": args.steps,
-      "roofline": {"kernel": "splash_fwd_kernel<true>", "bound": "tensor", "achieved": value, "peak": 2 * peak,
-                   "unit": "TFLOP/s", "frac": value / (2 * peak),
-                   "peak_source": f"2 x {peak_src} bf16 burst (no fp8 GEMM peak was measured on this pool)",
+      "roofline": {"kernel": "splash_fwd_kernel<true>", "bound": "tensor", "achieved": value, "peak": peak8,
+                   "unit": "TFLOP/s", "frac": value / peak8, "peak_source": peak8_src,
                    "traffic": None, "bf16_forward_same_shape_tflops": flops / ms_bf16 / 1e9},
   }
-  print(json.dumps(line), flush=True)
+  if emit:
+    print(json.dumps(line), flush=True)
+  return line
 
 
 def run_context_parallel(args, w, wname):
@@ -606,6 +685,8 @@ def run_context_parallel(args, w, wname):
   ms = max_over_ranks(timed_steps(step, args.steps, 0, barrier=dist.barrier))
   clocks = sampler.stop()
   kernel.check_errors()
+  if ring_mode:
+    cp.check_errors()  # the ring runs its own per-pair kernels
 
   # exchange alone: the 4 + 4 all-to-alls of one step (q, k, v, o forward; do, dq, dk, dv backward)
   def exchanges():
@@ -618,22 +699,86 @@ def run_context_parallel(args, w, wname):
   a2a_ms = None if ring_mode else max_over_ranks(timed_steps(exchanges, 3, 1, barrier=dist.barrier))
   sent = 2 * (2 * ulysses.exchange_bytes_sent(q.shape, 2, world) + 2 * ulysses.exchange_bytes_sent(k.shape, 2, world))
 
-  # end to end: each rank's sequence shard starts and ends in pinned host memory
+  # end to end: each rank's sequence shard starts and ends in pinned host memory.  Copies run on two
+  # side streams and are double-buffered across steps: while step n computes, step n+1's inputs come
+  # in and step n-1's gradients go out; within a step dO follows q/k/v (the forward does not need
+  # it) and the output leaves while the backward runs.
   e2e = None
   if not args.no_e2e:
     hq, hk, hv, hdo = [t.cpu().pin_memory() for t in (q, k, v, do)]
     outs_host = [torch.empty_like(t).pin_memory() for t in (hq, hq, hk, hv)]
+    s_in, s_out = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
+    slots = [[torch.empty_like(t) for t in (q, k, v, do)] for _ in range(2)]
+    slot_free = [None, None]
+    counter = [0]
+
     def e2e_step():
-      a, b_, c, d_ = (t.to(dev, non_blocking=True) for t in (hq, hk, hv, hdo))
-      qd, kd, vd = a.requires_grad_(True), b_.requires_grad_(True), c.requires_grad_(True)
+      main = torch.cuda.current_stream(dev)
+      i = counter[0] & 1
+      counter[0] += 1
+      a, b_, c, d_ = slots[i]
+      with torch.cuda.stream(s_in):
+        if slot_free[i] is not None:
+          s_in.wait_event(slot_free[i])  # the step that last used this slot has finished with it
+        a.copy_(hq, non_blocking=True)
+        b_.copy_(hk, non_blocking=True)
+        c.copy_(hv, non_blocking=True)
+        qkv_in = torch.cuda.Event()
+        qkv_in.record(s_in)
+        d_.copy_(hdo, non_blocking=True)
+        do_in = torch.cuda.Event()
+        do_in.record(s_in)
+      main.wait_event(qkv_in)
+      qd, kd, vd = a.detach().requires_grad_(True), b_.detach().requires_grad_(True), c.detach().requires_grad_(True)
       out = cp(qd, kd, vd, logits_scale=SCALE)
+      fwd_done = torch.cuda.Event()
+      fwd_done.record(main)
+      with torch.cuda.stream(s_out):
+        s_out.wait_event(fwd_done)
+        outs_host[0].copy_(out.detach(), non_blocking=True)
+        out.record_stream(s_out)
+      main.wait_event(do_in)
       out.backward(d_)
-      for dst, src in zip(outs_host, (out.detach(), qd.grad, kd.grad, vd.grad)):
-        dst.copy_(src, non_blocking=True)
-    ms_e2e = max_over_ranks(timed_steps(e2e_step, 2, 1, barrier=dist.barrier))
-    e2e = {"value": flops / ms_e2e / 1e9, "unit": "TFLOP/s", "ms_per_step": ms_e2e,
+      bwd_done = torch.cuda.Event()
+      bwd_done.record(main)
+      slot_free[i] = bwd_done
+      with torch.cuda.stream(s_out):
+        s_out.wait_event(bwd_done)
+        for dst, src in zip(outs_host[1:], (qd.grad, kd.grad, vd.grad)):
+          dst.copy_(src, non_blocking=True)
+          src.record_stream(s_out)
+
+    def e2e_run(n):
+      for _ in range(n):
+        e2e_step()
+      torch.cuda.current_stream(dev).wait_stream(s_out)
+
+    e2e_steps = max(10, min(args.steps, 20))
+    ms_e2e = max_over_ranks(timed_steps(lambda: e2e_run(e2e_steps), 1, 1, barrier=dist.barrier)) / e2e_steps
+    e2e = {"value": flops / ms_e2e / 1e9, "unit": "TFLOP/s", "ms_per_step": ms_e2e, "steps": e2e_steps,
            "h2d_bytes_per_step": world * sum(t.numel() * 2 for t in (hq, hk, hv, hdo)),
-           "d2h_bytes_per_step": world * sum(t.numel() * 2 for t in outs_host)}
+           "d2h_bytes_per_step": world * sum(t.numel() * 2 for t in outs_host),
+           "pinned_copy_rank0_alone": pinned_copy_gbs(dev) if rank == 0 else None,
+           "note": "per-rank pinned host buffers in and out; copies on side streams, double-buffered across steps"}
+    del hq, hk, hv, hdo, outs_host, slots
+
+  # the same workload on one GPU alone (all heads, no exchange), timed on rank 0 while the others
+  # wait: the denominator-free way to read the scaling of THIS workload
+  single_ms = None
+  if not args.no_single_gpu_ref and not ring_mode:
+    del q, k, v, do
+    torch.cuda.empty_cache()
+    if rank == 0:
+      q1, k1, v1, do1 = device_inputs(w, dev)
+
+      def step1():
+        qd, kd, vd = q1.detach().requires_grad_(True), k1.detach().requires_grad_(True), v1.detach().requires_grad_(True)
+        kernel(qd, kd, vd, logits_scale=SCALE).backward(do1)
+
+      single_ms = timed_steps(step1, 3, 2)
+      kernel.check_errors()
+      del q1, k1, v1, do1
+    dist.barrier()
 
   if rank == 0:
     peak, peak_sustained, peak_src = measured_peaks()
@@ -642,6 +787,8 @@ def run_context_parallel(args, w, wname):
         "metric": "splash fwd+bwd TFLOP/s (masked FLOPs)", "value": value, "unit": "TFLOP/s", "n_gpus": world,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "scaling_note": "total work is fixed (one 131072-token sequence) and split over the GPUs; the N = 1 default "
+                        "line of this script is a different workload (c2), so use cp.scaling_efficiency",
         "config": {"workload": wname, **{k_: w[k_] for k_ in ("batch", "q_heads", "kv_heads", "seq", "mask")},
                    "head_dim": D, "parallelism": f"{args.cp if ring_mode else 'ulysses'} cp{world}",
                    "n_live_pairs": n_live,
@@ -650,7 +797,10 @@ def run_context_parallel(args, w, wname):
         "cp": {"tokens_per_s": w["batch"] * w["seq"] / (ms / 1e3), "a2a_ms_per_step": a2a_ms,
                "a2a_bytes_sent_per_gpu": None if ring_mode else sent,
                "a2a_gbs_per_direction": None if ring_mode else sent / a2a_ms / 1e6,
-               "nvlink_nominal_gbs_per_direction": 900.0},
+               "nvlink_nominal_gbs_per_direction": 900.0,
+               "single_gpu_ms_per_step": single_ms,
+               "scaling_efficiency": None if single_ms is None else single_ms / (world * ms),
+               "exposed_a2a_ms_per_step": cp.exposed_exchange_ms() if hasattr(cp, "exposed_exchange_ms") else None},
         "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak_sustained, "unit": "TFLOP/s",
                      "frac": value / world / peak_sustained, "peak_source": f"{peak_src} bf16 sustained, per GPU",
                      "traffic": None},
@@ -673,6 +823,10 @@ def main():
                   help="backward form: one fused kernel (dQ partials reduced in fp32) or separate dq / dkv kernels")
   ap.add_argument("--no-e2e", action="store_true")
   ap.add_argument("--no-cpu-baseline", action="store_true")
+  ap.add_argument("--no-single-gpu-ref", action="store_true",
+                  help="N > 1: skip timing the same workload on rank 0 alone (cp.single_gpu_ms_per_step)")
+  ap.add_argument("--no-other-workloads", action="store_true",
+                  help="N = 1, c2: skip the short c3 / c5 runs reported under other_workloads")
   args = ap.parse_args()
   args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
   world = int(os.environ.get("WORLD_SIZE", "1"))

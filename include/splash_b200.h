@@ -353,6 +353,24 @@ int splash_bwd_static_scratch(const SplashBwdArgs* args, void* cuda_stream);
  * status: SPLASH_OK or SPLASH_ERR_KERNEL_TIMEOUT.  record_out may be NULL. */
 int splash_read_error(const uint32_t* error_record, void* cuda_stream, uint32_t record_out[4]);
 
+/* Diagnostic for the error path (no counterpart in the reference): launches one tiny kernel in
+ * which a thread waits, through the same bounded wait the attention kernels use, on a barrier
+ * nothing ever arrives on.  The wait gives up after `limit_cycles` SM cycles (1 .. 1e8, i.e. at
+ * most some tens of milliseconds), the kernel writes {1, block, tag, thread} to the record and
+ * returns; splash_read_error then reports SPLASH_ERR_KERNEL_TIMEOUT.  Lets an integration check
+ * its handling of a device-side timeout without hanging anything. */
+int splash_probe_bounded_wait(uint32_t* error_record, int64_t limit_cycles, uint32_t tag, void* cuda_stream);
+
+/* XLA custom-call adapter (tokamax_b200/csrc/splash_xla_ffi.cc; stands where the reference calls
+ * `pl.pallas_call`, splash_attention_kernel.py:888, :1840).  When the library is built with XLA's
+ * "xla/ffi/api/ffi.h" on the include path it also exports the FFI handlers `SplashFwd` and
+ * `SplashBwd` (XLA_FFI_DEFINE_HANDLER_SYMBOL) for jax.ffi.register_ffi_target;
+ * splash_xla_ffi_compiled says whether it was (1) or not (0).  splash_xla_ffi_signature(0 | 1)
+ * returns the forward / backward handler's operands, results and attributes in binding order as
+ * "operands=name:kind,...;results=...;attrs=name:type,...;". */
+int splash_xla_ffi_compiled(void);
+const char* splash_xla_ffi_signature(int which);
+
 /* Human-readable text for a SplashStatus.  Never NULL. */
 const char* splash_status_str(int status);
 

@@ -3,8 +3,8 @@
 The reference's ``splash_attention_mask.py`` is pure numpy and ``splash_attention_mask_info.py``
 only touches JAX in ``find_bounds`` and ``_process_dynamic_mask``; with a stub ``jax`` package
 pre-seeded in ``sys.modules`` both load and ``process_mask`` / ``process_mask_dkv`` run
-unmodified.  This works only where the reference tree is present (the build container); it is
-used to generate ``tests/golden/maskinfo_*.npz`` and to run the reference's MaskInfo test-suite
+unmodified.  This works only where a checkout of the reference is present and the environment
+variable SPLASH_REFERENCE_ROOT points at it; it is used to generate ``tests/golden/maskinfo_*.npz`` and to run the reference's MaskInfo test-suite
 against the oracle restatement and against the product's builder.
 
 Nothing here copies reference sources: modules are loaded from where they lie.
@@ -17,13 +17,13 @@ import os
 import sys
 import types
 
-REFERENCE_ROOT = os.environ.get("SPLASH_REFERENCE_ROOT", "/root/reference")
+REFERENCE_ROOT = os.environ.get("SPLASH_REFERENCE_ROOT", "")  # unset: available() is False
 _SA = "tokamax/_src/ops/experimental/tpu/splash_attention"
 _PKG = "tokamax._src.ops.experimental.tpu.splash_attention"
 
 
 def available() -> bool:
-  return os.path.isfile(os.path.join(REFERENCE_ROOT, _SA, "splash_attention_mask_info.py"))
+  return bool(REFERENCE_ROOT) and os.path.isfile(os.path.join(REFERENCE_ROOT, _SA, "splash_attention_mask_info.py"))
 
 
 def _install_jax_stub() -> None:

@@ -1,7 +1,7 @@
 """Runs the reference's own mask / MaskInfo test-suite against this package's modules.
 
-Only possible where the reference tree is present (the build container); skipped elsewhere —
-the committed golden tables (test_maskinfo_golden.py) carry the same pin to other machines.
+Only possible where a checkout of the reference is present (SPLASH_REFERENCE_ROOT points at it);
+skipped elsewhere — the committed golden tables (test_maskinfo_golden.py) carry the same pin to other machines.
 The suite is the reference's splash_attention_mask_test.py (126 tests, literal expected tables
 at :752-1750), with its ``mask_lib`` / ``mask_info_lib`` aliases pointed at tokamax_b200.
 """
@@ -28,7 +28,7 @@ for t, tb in r.failures + r.errors:
 """
 
 
-@pytest.mark.skipif(not ref_loader.available(), reason="reference tree not present")
+@pytest.mark.skipif(not ref_loader.available(), reason="SPLASH_REFERENCE_ROOT is not set to a checkout of the reference")
 def test_reference_mask_suite_passes_on_this_implementation():
   # a fresh interpreter: the stub jax module and the aliased test module stay out of this process
   out = subprocess.run([sys.executable, "-c", _SCRIPT.format(root=ROOT)], capture_output=True, text=True,

@@ -79,7 +79,7 @@ def test_library_loaded_and_identifies_itself():
 
 
 def test_c1_causal_mha_1024():
-  """BASELINE config 1: causal, B=2, Hq=Hkv=8, S=1024, D=128."""
+  """The CPU-sized benchmark case: causal, B=2, Hq=Hkv=8, S=1024, D=128."""
   q, k, v, do = _inputs(1000, 2, 8, 8, 1024, 1024)
   mask = mask_lib.CausalMask((1024, 1024))
   kernel = splash.make_splash_mha(mask, q_seq_shards=1)
@@ -155,7 +155,7 @@ def _packed_segments(batch, s, seed, lo, hi):
 
 
 def test_segment_ids_with_local_window():
-  """Shape of BASELINE config 3, scaled down: window+causal composed with packed documents."""
+  """The packed-sequence benchmark case scaled down: window + causal composed with packed documents."""
   s = 1024
   q, k, v, do = _inputs(3000, 2, 4, 4, s, s)
   mask = mask_lib.LocalMask((s, s), (256, 0), 0)
@@ -300,7 +300,7 @@ def test_fused_and_split_backward_agree():
 
 
 def test_full_size_properties_llama_shape():
-  """BASELINE config 2 at full size, checked through size-independent identities.
+  """The Llama-3-8B-shape case (B=4, S=8192, Hq=32, Hkv=8) at full size, checked through size-independent identities.
 
   (1) rows of P sum to one, so with V = 1 the output is exactly 1; (2) the first causal row
   attends to key 0 only; (3) sum_kv dV = sum_q dO over each kv-head group; (4) <q, dq> = <k, dk>

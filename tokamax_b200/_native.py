@@ -26,6 +26,7 @@ SOURCES = (
     "segment_schedule.cu",
     "dynamic_schedule.cu",
     "ring_merge.cu",
+    "splash_xla_ffi.cc",  # handlers compile only where xla/ffi/api/ffi.h is on the include path
 )
 
 NVCC_FLAGS = (
@@ -195,6 +196,9 @@ _PROTOTYPES = {
     "splash_bwd": (C.c_int, [C.POINTER(SplashBwdArgs), C.c_void_p]),
     "splash_bwd_static_scratch": (C.c_int, [C.POINTER(SplashBwdArgs), C.c_void_p]),
     "splash_read_error": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32 * 4)]),
+    "splash_probe_bounded_wait": (C.c_int, [C.c_void_p, C.c_int64, C.c_uint32, C.c_void_p]),
+    "splash_xla_ffi_compiled": (C.c_int, []),
+    "splash_xla_ffi_signature": (C.c_char_p, [C.c_int]),
     "splash_status_str": (C.c_char_p, [C.c_int]),
     "splash_version": (C.c_char_p, []),
 }
@@ -203,34 +207,18 @@ _lib = None
 _lock = threading.Lock()
 
 
-# Build variants: name -> (file name, extra nvcc flags).  "checked" differs from the default
-# build in two ways that exist only to be tested: the MMA-issuing threads execute a
-# tcgen05.fence::after_thread_sync between every mbarrier wait and the MMAs that follow it (the
-# default build relies on program order there), and it exports splash_test_bounded_wait, a probe
-# kernel whose bounded wait runs out after a given number of cycles.
-VARIANTS = {
-    "default": ("libsplash_b200.so", ()),
-    "checked": ("libsplash_b200_checked.so", ("-DSPLASH_MMA_ISSUE_FENCE", "-DSPLASH_TEST_HOOKS")),
-}
-
-
-def variant_path(variant: str = "default") -> str:
-  return os.path.join(_LIB_DIR, VARIANTS[variant][0])
-
-
-def build(force: bool = False, verbose: bool = False, variant: str = "default") -> str:
-  """Compiles the CUDA/C++ sources into ``lib/libsplash_b200*.so`` (sm_100a). Returns its path."""
-  out_path = variant_path(variant)
+def build(force: bool = False, verbose: bool = False) -> str:
+  """Compiles the CUDA/C++ sources into ``lib/libsplash_b200.so`` (sm_100a). Returns its path."""
   srcs = [os.path.join(_CSRC, s) for s in SOURCES if os.path.exists(os.path.join(_CSRC, s))]
   deps = srcs + [os.path.join(_CSRC, f) for f in os.listdir(_CSRC) if f.endswith(".cuh")]
   deps.append(os.path.join(os.path.dirname(_PKG_DIR), "include", "splash_b200.h"))
-  if not force and os.path.exists(out_path):
+  if not force and os.path.exists(LIB_PATH):
     newest = max(os.path.getmtime(d) for d in deps)
-    if os.path.getmtime(out_path) >= newest:
-      return out_path
+    if os.path.getmtime(LIB_PATH) >= newest:
+      return LIB_PATH
   os.makedirs(_LIB_DIR, exist_ok=True)
   nvcc = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-  cmd = [nvcc, *NVCC_FLAGS, *VARIANTS[variant][1], "-o", out_path, *srcs]
+  cmd = [nvcc, *NVCC_FLAGS, "-o", LIB_PATH, *srcs]
   if verbose:
     cmd.insert(1, "-Xptxas")
     cmd.insert(2, "-v")
@@ -239,16 +227,7 @@ def build(force: bool = False, verbose: bool = False, variant: str = "default") 
     raise RuntimeError("nvcc failed:\n" + res.stdout + res.stderr)
   if verbose:
     print(res.stderr)
-  return out_path
-
-
-def _load(path: str) -> C.CDLL:
-  handle = C.CDLL(path)
-  for name, (restype, argtypes) in _PROTOTYPES.items():
-    fn = getattr(handle, name)  # AttributeError if the symbol is missing
-    fn.restype = restype
-    fn.argtypes = argtypes
-  return handle
+  return LIB_PATH
 
 
 def lib() -> C.CDLL:
@@ -256,33 +235,15 @@ def lib() -> C.CDLL:
   global _lib
   with _lock:
     if _lib is None:
-      variant = os.environ.get("SPLASH_B200_VARIANT", "default")  # "checked": the fenced build
-      if variant not in VARIANTS:
-        raise RuntimeError(f"SPLASH_B200_VARIANT={variant!r}: expected one of {sorted(VARIANTS)}")
-      path = variant_path(variant)
-      if not os.path.exists(path):
-        build(variant=variant)
-      _lib = _load(path)
+      if not os.path.exists(LIB_PATH):
+        build()
+      handle = C.CDLL(LIB_PATH)
+      for name, (restype, argtypes) in _PROTOTYPES.items():
+        fn = getattr(handle, name)  # AttributeError if the symbol is missing
+        fn.restype = restype
+        fn.argtypes = argtypes
+      _lib = handle
     return _lib
-
-
-_variants: dict = {}
-
-
-def lib_variant(variant: str) -> C.CDLL:
-  """A second, independently loaded build of the same sources (see VARIANTS); used by tests."""
-  if variant == "default":
-    return lib()
-  with _lock:
-    if variant not in _variants:
-      path = variant_path(variant)
-      if not os.path.exists(path):
-        build(variant=variant)
-      handle = _load(path)
-      handle.splash_test_bounded_wait.restype = C.c_int
-      handle.splash_test_bounded_wait.argtypes = [C.c_void_p, C.c_longlong, C.c_uint32, C.c_void_p]
-      _variants[variant] = handle
-    return _variants[variant]
 
 
 def exported_symbols() -> tuple[str, ...]:

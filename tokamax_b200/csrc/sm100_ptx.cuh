@@ -165,16 +165,12 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-// Fence used by the MMA-issuing thread between an mbarrier wait and the MMAs that consume what
-// the wait published.  The issuing thread's program order already places the tcgen05.mma after
-// the wait has returned, and the producers completed their TMEM stores (tcgen05.wait::st) before
-// arriving; a full tcgen05.fence here was measured to stall the issuing thread for several
-// hundred cycles per use while earlier MMAs were still in flight, so it is compiled out unless
-// SPLASH_MMA_ISSUE_FENCE is defined.
+// Fence the MMA-issuing thread executes between an mbarrier wait and the MMAs that consume what
+// the wait published (TMEM written by other warps' tcgen05.st, or TMEM columns other warps have
+// finished reading): the consumer half of the before_thread_sync / after_thread_sync pair the
+// tcgen05 ordering rules ask for.
 __device__ __forceinline__ void mma_issue_fence() {
-#ifdef SPLASH_MMA_ISSUE_FENCE
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#endif
 }
 // One thread: the mbarrier receives one arrival once every tcgen05 async op this thread
 // issued before the commit has completed.

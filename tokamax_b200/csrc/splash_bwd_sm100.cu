@@ -53,35 +53,50 @@ struct DeltaParams {
   int64_t n_rows;
 };
 
+// 64 rows per block: a warp takes eight rows, half a warp per row (16 lanes x 16 bytes = one row of
+// 128 bf16), four rows deep, with all eight 16-byte loads of a lane in flight before the first is
+// used (the pass is a pure stream: 512 bytes read and 8 written per row).
+constexpr int kDeltaRowsPerBlock = 64;
 __global__ void __launch_bounds__(256) splash_delta_kernel(const DeltaParams p) {
-  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  if (row >= p.n_rows) return;
-  const int q = (int)(row % p.q_len);
-  const int64_t bh = row / p.q_len;
-  const int h = (int)(bh % p.q_heads);
-  const int64_t b = bh / p.q_heads;
-  const uint2* po = reinterpret_cast<const uint2*>(p.o + b * p.o_sb + h * p.o_sh + (int64_t)q * p.o_ss);
-  const uint2* pd =
-      reinterpret_cast<const uint2*>(p.d_o + b * p.do_sb + h * p.do_sh + (int64_t)q * p.do_ss);
-  const uint2 a = __ldg(po + lane);
-  const uint2 g = __ldg(pd + lane);
-  const __nv_bfloat162 a0 = *reinterpret_cast<const __nv_bfloat162*>(&a.x);
-  const __nv_bfloat162 a1 = *reinterpret_cast<const __nv_bfloat162*>(&a.y);
-  const __nv_bfloat162 g0 = *reinterpret_cast<const __nv_bfloat162*>(&g.x);
-  const __nv_bfloat162 g1 = *reinterpret_cast<const __nv_bfloat162*>(&g.y);
-  float acc = __bfloat162float(a0.x) * __bfloat162float(g0.x) +
-              __bfloat162float(a0.y) * __bfloat162float(g0.y) +
-              __bfloat162float(a1.x) * __bfloat162float(g1.x) +
-              __bfloat162float(a1.y) * __bfloat162float(g1.y);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane & 15, half = lane >> 4;
+  const int64_t row0 = (int64_t)blockIdx.x * kDeltaRowsPerBlock + warp * 8 + half;
+  uint4 a[4], g[4];
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-  if (lane == 0) {
-    p.delta[row] = -acc;
-    // Rows that never met a live key carry the mask value as logsumexp; -inf keeps their
-    // probabilities at exactly zero instead of overflowing the product to +inf.
-    const float lse = p.lse[row];
-    p.nlse2[row] = lse < -1.0e20f ? -INFINITY : -lse * kLog2e;
+  for (int i = 0; i < 4; ++i) {
+    const int64_t row = row0 + 2 * i;
+    a[i] = make_uint4(0u, 0u, 0u, 0u);
+    g[i] = a[i];
+    if (row < p.n_rows) {
+      const int q = (int)(row % p.q_len);
+      const int64_t bh = row / p.q_len;
+      const int h = (int)(bh % p.q_heads);
+      const int64_t b = bh / p.q_heads;
+      a[i] = __ldg(reinterpret_cast<const uint4*>(p.o + b * p.o_sb + h * p.o_sh + (int64_t)q * p.o_ss) + sub);
+      g[i] = __ldg(reinterpret_cast<const uint4*>(p.d_o + b * p.do_sb + h * p.do_sh + (int64_t)q * p.do_ss) + sub);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint32_t aw[4] = {a[i].x, a[i].y, a[i].z, a[i].w}, gw[4] = {g[i].x, g[i].y, g[i].z, g[i].w};
+    float acc = 0.f;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&aw[j]);
+      const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(&gw[j]);
+      acc = fmaf(__bfloat162float(x.x), __bfloat162float(y.x), acc);
+      acc = fmaf(__bfloat162float(x.y), __bfloat162float(y.y), acc);
+    }
+#pragma unroll
+    for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    const int64_t row = row0 + 2 * i;
+    if (sub == 0 && row < p.n_rows) {
+      p.delta[row] = -acc;
+      // Rows that never met a live key carry the mask value as logsumexp; -inf keeps their
+      // probabilities at exactly zero instead of overflowing the product to +inf.
+      const float lse = p.lse[row];
+      p.nlse2[row] = lse < -1.0e20f ? -INFINITY : -lse * kLog2e;
+    }
   }
 }
 
@@ -715,6 +730,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const bool more = n + 1 < n_steps;
         ok = mbar_wait(&bars->p_full, ph, ab, 0x3220u);
         if (!ok) break;
+        mma_issue_fence();
         // dV += P^T dO: A = packed bf16 P^T in TMEM (16 packed columns at the start of every
         // 32-column quarter), B = the dO tile read MN-major, K = 128 query rows in eight slices
         const SmemDesc do_mn = make_smem_desc_sw128(do_slot, kHalfBytes, 1024);
@@ -730,6 +746,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         }
         ok = mbar_wait(&bars->ds_full, ph, ab, 0x3230u);
         if (!ok) break;
+        mma_issue_fence();
         if constexpr (kFuseDq) {
           // dQ_partial = dS K over the dP^T columns (every compute warp has read dP^T(n) before it
           // arrived on ds_full): A = the dS^T tile read MN-major (M = q), B = the K tile read
@@ -757,6 +774,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if constexpr (kFuseDq) {  // the dP^T columns still hold dQ_partial(n) until it is drained
             ok = mbar_wait(&bars->dq_free, ph, ab, 0x3250u);
             if (!ok) break;
+            mma_issue_fence();
           }
           issue_score(t_dpt, v_desc, slot_addr(2 * (n + 1) + 1));
           tc_commit(&bars->dpt_full);
@@ -1084,7 +1102,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     dp.q_heads = (int)Hq;
     dp.q_len = (int)Sq;
     dp.n_rows = B * Hq * Sq;
-    const unsigned blocks = (unsigned)((dp.n_rows + 7) / 8);
+    const unsigned blocks = (unsigned)((dp.n_rows + kDeltaRowsPerBlock - 1) / kDeltaRowsPerBlock);
     splash_delta_kernel<<<blocks, 256, 0, stream>>>(dp);
     if (cudaGetLastError() != cudaSuccess) return SPLASH_ERR_CUDA;
   }

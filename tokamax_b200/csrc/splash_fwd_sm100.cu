@@ -30,6 +30,8 @@
 // largest V scale of the (batch, kv head), so that it sits in the normal range of the format and
 // never exceeds it.  There is no counterpart of this variant in the reference, which accepts
 // bf16 / f32 only.
+#include <mutex>
+
 #include "splash_common.cuh"
 
 namespace sb {
@@ -659,33 +661,30 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   p.chunk_groups = chunk_groups_for(2 * Skv * kHeadDim * (fp8 ? 1 : 2) / (Hq / Hkv), p.n_groups, Hq / Hkv);
   if ((int64_t)p.n_rows * p.n_groups > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
   dim3 grid((unsigned)(p.n_rows * p.n_groups), 1u, 1u);
-  if (fp8) {
-    constexpr int smem = fwd_smem_bytes(true);
-    if (cudaFuncSetAttribute(splash_fwd_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem) != cudaSuccess)
-      return SPLASH_ERR_CUDA;
-    splash_fwd_kernel<true, false><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
-  } else if (soft_cap) {
-    constexpr int smem = fwd_smem_bytes(false);
-    if (cudaFuncSetAttribute(splash_fwd_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                             smem) != cudaSuccess)
-      return SPLASH_ERR_CUDA;
-    splash_fwd_kernel<false, true><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
-  } else {
-    constexpr int smem = fwd_smem_bytes(false);
-    // function attributes are per device: remember which devices have been set up
-    static bool attr_done[64] = {};
+  // The dynamic shared-memory attribute is per device and per kernel variant: set once, under a
+  // lock (calls may come from several threads).
+  const int variant = fp8 ? 1 : (soft_cap ? 2 : 0);
+  const int smem = fp8 ? fwd_smem_bytes(true) : fwd_smem_bytes(false);
+  const void* fn = fp8 ? (const void*)splash_fwd_kernel<true, false>
+                       : (soft_cap ? (const void*)splash_fwd_kernel<false, true> : (const void*)splash_fwd_kernel<false, false>);
+  {
+    static std::mutex attr_mu;
+    static bool attr_done[64][3] = {};
     int dev = 0;
-    if (cudaGetDevice(&dev) != cudaSuccess) return SPLASH_ERR_CUDA;
-    bool& attr_set = attr_done[dev & 63];
-    if (!attr_set) {
-      if (cudaFuncSetAttribute(splash_fwd_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                               smem) != cudaSuccess)
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SPLASH_ERR_CUDA;
+    std::lock_guard<std::mutex> lock(attr_mu);
+    if (!attr_done[dev][variant]) {
+      if (cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess)
         return SPLASH_ERR_CUDA;
-      attr_set = true;
+      attr_done[dev][variant] = true;
     }
-    splash_fwd_kernel<false, false><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
   }
+  if (fp8)
+    splash_fwd_kernel<true, false><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
+  else if (soft_cap)
+    splash_fwd_kernel<false, true><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
+  else
+    splash_fwd_kernel<false, false><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
 }
 

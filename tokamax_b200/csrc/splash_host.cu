@@ -87,7 +87,6 @@ int make_tile_tensor_map(CUtensorMap* out, const SplashTensor& t, int box_rows) 
   return r == CUDA_SUCCESS ? SPLASH_OK : SPLASH_ERR_CUDA;
 }
 
-#ifdef SPLASH_TEST_HOOKS
 // One thread waits, through the same mbar_wait the attention kernels use, on a barrier that
 // nothing ever arrives on; the wait gives up after `limit_cycles` and the kernel returns.
 __global__ void bounded_wait_probe_kernel(uint32_t* err, long long limit_cycles, uint32_t tag) {
@@ -101,21 +100,16 @@ __global__ void bounded_wait_probe_kernel(uint32_t* err, long long limit_cycles,
     (void)mbar_wait(&bar, 0, ab, tag);
   }
 }
-#endif
 
 }  // namespace sb
 
 extern "C" {
 
-#ifdef SPLASH_TEST_HOOKS
-// Test hook (only in the "checked" build): makes a bounded device wait run out.  The record then
-// holds {1, block, tag, thread}; splash_read_error maps it to SPLASH_ERR_KERNEL_TIMEOUT.
-int splash_test_bounded_wait(uint32_t* error_record, long long limit_cycles, uint32_t tag, void* cuda_stream) {
+int splash_probe_bounded_wait(uint32_t* error_record, int64_t limit_cycles, uint32_t tag, void* cuda_stream) {
   if (error_record == nullptr || limit_cycles <= 0 || limit_cycles > 100000000ll) return SPLASH_ERR_INVALID_ARGUMENT;
-  sb::bounded_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(error_record, limit_cycles, tag);
+  sb::bounded_wait_probe_kernel<<<1, 32, 0, static_cast<cudaStream_t>(cuda_stream)>>>(error_record, (long long)limit_cycles, tag);
   return cudaGetLastError() == cudaSuccess ? SPLASH_OK : SPLASH_ERR_CUDA;
 }
-#endif
 
 int splash_fwd(const SplashFwdArgs* args, void* cuda_stream) {
   if (args == nullptr) return SPLASH_ERR_INVALID_ARGUMENT;

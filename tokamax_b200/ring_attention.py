@@ -321,6 +321,14 @@ class RingSplashAttention:
       self._cache[key] = self._factory(shard_mask(self.mask, q_shard, kv_shard, world, world))
     return self._cache[key]
 
+  def check_errors(self) -> None:
+    """Raises if any of the per-pair kernels reported a device-side fault (see
+    SplashAttentionKernel.check_errors)."""
+    for attn in self._cache.values():
+      kernel = getattr(attn, "kernel", None)
+      if kernel is not None:
+        kernel.check_errors()
+
   def __call__(self, q, k, v, segment_ids: base.SegmentIds | None = None, sinks=None, *,
                logits_scale: float = 1.0):
     if sinks is not None:
