@@ -37,13 +37,13 @@ def _oracle_attention(mask_dense):
   return fn
 
 
-def _worker(rank, world, port, with_segments, result_queue):
+def _worker(rank, world, port, with_segments, result_queue, heads=(4, 2), batch=2):
   os.environ["MASTER_ADDR"] = "127.0.0.1"
   os.environ["MASTER_PORT"] = str(port)
   dist.init_process_group("gloo", rank=rank, world_size=world)
   try:
     torch.manual_seed(0)
-    b, hq, hkv, s, d = 2, 4, 2, 64, 16
+    (hq, hkv), b, s, d = heads, batch, 64, 16
     q = torch.randn(b, hq, s, d, requires_grad=True)
     k = torch.randn(b, hkv, s, d, requires_grad=True)
     v = torch.randn(b, hkv, s, d, requires_grad=True)
@@ -97,6 +97,34 @@ def test_ulysses_matches_unsharded_on_two_gloo_ranks(with_segments):
   for p in procs:
     p.join(timeout=60)
   assert sorted(results) == [(0, "ok"), (1, "ok")], results
+
+
+@pytest.mark.parametrize("world,heads,batch", [(2, (4, 1), 1), (4, (8, 2), 2)])
+def test_ulysses_replicates_kv_heads_when_ranks_outnumber_them(world, heads, batch):
+  """More ranks than kv heads (MQA on 2 ranks; 2 kv heads on 4 ranks): the kv head a rank's q heads
+  read is replicated to it, and its gradient is the sum over the copies."""
+  ctx = mp.get_context("spawn")
+  queue = ctx.Queue()
+  port = _free_port()
+  procs = [ctx.Process(target=_worker, args=(r, world, port, False, queue, heads, batch)) for r in range(world)]
+  for p in procs:
+    p.start()
+  results = [queue.get(timeout=180) for _ in range(world)]
+  for p in procs:
+    p.join(timeout=60)
+  assert sorted(results) == [(r, "ok") for r in range(world)], results
+
+
+def test_kv_head_assignment():
+  f = ulysses.UlyssesSplashAttention.kv_heads_for_ranks
+  assert f(64, 8, 8) is None and f(32, 8, 4) is None
+  assert f(64, 8, 16) == [r // 2 for r in range(16)]
+  assert f(8, 1, 4) == [0, 0, 0, 0]
+  with pytest.raises(NotImplementedError):
+    f(12, 4, 8)   # ranks do not divide the q heads
+  assert f(12, 2, 4) == [0, 0, 1, 1]  # 3 q heads per rank, groups of 6
+  with pytest.raises(NotImplementedError):
+    f(12, 3, 2)   # 6 q heads per rank over groups of 4: a rank would straddle kv heads
 
 
 def test_heads_not_divisible_is_rejected():

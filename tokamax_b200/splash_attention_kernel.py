@@ -152,15 +152,17 @@ def _build_schedule(state: np.ndarray, pid: np.ndarray, block_q: int, block_kv: 
 class _DeviceTables:
   """Schedules, partial-mask blocks and the error record of one kernel object on one device."""
 
-  def __init__(self, kernel: "SplashAttentionKernel", device: torch.device):
+  def __init__(self, kernel: "SplashAttentionKernel", device: torch.device, shard: int = 0):
     cfg = kernel.config
     fwd, dkv = kernel.fwd_mask_info, kernel.dkv_mask_info
+    n_shards = kernel.q_seq_shards
     q_len, kv_len = kernel.mask_shape
+    q_len //= n_shards  # the q rows of this shard; keys are never sharded here
     for b in (cfg.block_q, cfg.block_kv):
       if b % _TILE != 0:
         raise NotImplementedError(f"block sizes must be multiples of {_TILE} on B200, got {b}")
     nq, nkv = q_len // cfg.block_q, kv_len // cfg.block_kv
-    state, pid = mask_info_lib.block_grids(fwd, nq, nkv, is_dkv=False)
+    state, pid = mask_info_lib.block_grids(fwd, nq, nkv, is_dkv=False, shard=shard, n_shards=n_shards)
     self.keep = []
     self.fwd = self._upload(state, pid, cfg.block_q, cfg.block_kv, 0, fwd.partial_mask_blocks, device)
     self.dq = self._upload(state, pid, cfg.block_q, cfg.block_kv, 1, fwd.partial_mask_blocks, device)
@@ -169,7 +171,7 @@ class _DeviceTables:
       for b in (bq, bkv):
         if b % _TILE != 0:
           raise NotImplementedError(f"block sizes must be multiples of {_TILE} on B200, got {b}")
-      st2, pid2 = mask_info_lib.block_grids(dkv, q_len // bq, kv_len // bkv, is_dkv=True)
+      st2, pid2 = mask_info_lib.block_grids(dkv, q_len // bq, kv_len // bkv, is_dkv=True, shard=shard, n_shards=n_shards)
       self.dkv = self._upload(st2, pid2, bq, bkv, 2, dkv.partial_mask_blocks, device)
     else:
       pmb_t = None
@@ -178,6 +180,8 @@ class _DeviceTables:
       self.dkv = self._upload(state, pid, cfg.block_q, cfg.block_kv, 2, pmb_t, device)
     self.error_record = torch.zeros(4, dtype=torch.int32, device=device)
     q_seq = fwd.q_sequence
+    if q_seq is not None and n_shards > 1:  # global q indices of this shard's rows
+      q_seq = np.asarray(q_seq)[shard * q_len:(shard + 1) * q_len]
     self.q_sequence = None
     if q_seq is not None and not np.array_equal(np.asarray(q_seq), np.arange(q_len, dtype=np.int32)):
       self.q_sequence = torch.from_numpy(np.ascontiguousarray(q_seq, dtype=np.int32)).to(device)
@@ -296,9 +300,9 @@ class _SplashFunction(torch.autograd.Function):
   """forward = splash_fwd, backward = splash_bwd (reference custom_vjp: kernel.py:998-1108)."""
 
   @staticmethod
-  def forward(ctx, q, k, v, q_seg, kv_seg, kernel, scale, sinks, max_logit):
+  def forward(ctx, q, k, v, q_seg, kv_seg, kernel, scale, sinks, max_logit, shard=0):
     _require_cuda(q)
-    tables = kernel._tables(q.device, q.shape[0])  # pylint: disable=protected-access
+    tables = kernel._tables(q.device, q.shape[0], shard)  # pylint: disable=protected-access
     q, k, v = _usable(q), _usable(k), _usable(v)
     b, hq, sq, d = q.shape
     o = torch.empty_like(q)  # keeps q's (dense) stride order, e.g. [B,T,H,D] storage stays [B,T,H,D]
@@ -331,22 +335,23 @@ class _SplashFunction(torch.autograd.Function):
     ctx.sinks_dtype = None if sinks is None else sinks.dtype
     ctx.kernel = kernel
     ctx.scale = scale
+    ctx.shard = shard
     ctx.mark_non_differentiable(lse, max_logits)
     return o, lse, max_logits
 
   @staticmethod
   def backward(ctx, d_o, _dlse, _dmax):
     q, k, v, o, lse, q_seg, kv_seg, sinks = ctx.saved_tensors
-    dq, dk, dv, neg_di = splash_backward(ctx.kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale)
+    dq, dk, dv, neg_di = splash_backward(ctx.kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale, ctx.shard)
     dsinks = None
     if sinks is not None:
       # reference kernel.py:1928-1935: dsinks[h] = -sum_rows exp(sink - lse) * sum_d(o * do)
       dsinks = (torch.exp(sinks[None, :, None] - lse) * neg_di).sum(dim=(0, 2)).to(ctx.sinks_dtype)
-    return dq, dk, dv, None, None, None, None, dsinks, None
+    return dq, dk, dv, None, None, None, None, dsinks, None, None
 
 
 def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg=None, kv_seg=None,
-                    scale: float = 1.0):
+                    scale: float = 1.0, shard: int = 0):
   """One `splash_bwd` call: ``(dq, dk, dv, neg_di)`` for batched ``[B, H, S, 128]`` bf16 tensors.
 
   ``o`` and ``lse`` are the forward's output and logsumexp for these q rows; they may come from a
@@ -355,7 +360,7 @@ def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg
   ``neg_di`` is ``-sum_d(o * do)`` (fp32 ``[B, Hq, Sq]``), a view of the backward's workspace, which
   keeps the row sums negated.
   """
-  tables = kernel._tables(q.device, q.shape[0])  # pylint: disable=protected-access
+  tables = kernel._tables(q.device, q.shape[0], shard)  # pylint: disable=protected-access
   d_o = _usable(d_o)
   dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
   lib = _native.lib()
@@ -444,6 +449,10 @@ class SplashAttentionKernel:
   # reference's (kernel.py:1234-1459), dq partials summed by fp32 reductions whose order varies
   # between runs.  True: separate dq and dkv kernels, every gradient bitwise repeatable.
   repeatable_dq = property(lambda self: bool(self.kwargs.get("repeatable_dq", False)))
+  # > 1: the MaskInfo tables hold one segment per contiguous q-sequence shard (reference
+  # kernel.py:2023-2053 hands shard i of them to device i under shard_map); a call then takes the
+  # q rows of ONE shard ([.., q_len / shards, 128], `q_shard=i`) against all keys.
+  q_seq_shards = property(lambda self: int(self.kwargs.get("q_seq_shards", 1)))
 
   def with_options(self, **kwargs) -> "SplashAttentionKernel":
     """A kernel object for the same mask with some keyword options replaced (``repeatable_dq``,
@@ -453,7 +462,9 @@ class SplashAttentionKernel:
     other._device_tables = self._device_tables  # pylint: disable=protected-access
     return other
 
-  def _tables(self, device: torch.device, batch: int = 1):
+  def _tables(self, device: torch.device, batch: int = 1, shard: int = 0):
+    if shard and (self._dynamic_mask is not None or not 0 <= shard < self.q_seq_shards):
+      raise ValueError(f"q shard {shard} does not exist in a kernel built with q_seq_shards={self.q_seq_shards}")
     if self._dynamic_mask is not None:
       if self._dynamic_mask.device != device:
         raise ValueError(f"the mask lives on {self._dynamic_mask.device}, the inputs on {device}")
@@ -461,9 +472,9 @@ class SplashAttentionKernel:
       if key not in self._device_tables:
         self._device_tables[key] = _DynamicDeviceTables(self._dynamic_mask, int(batch))
       return self._device_tables[key]
-    key = (device.type, device.index)
+    key = (device.type, device.index, shard) if self.q_seq_shards > 1 else (device.type, device.index)
     if key not in self._device_tables:
-      self._device_tables[key] = _DeviceTables(self, device)
+      self._device_tables[key] = _DeviceTables(self, device, shard)
     return self._device_tables[key]
 
   def check_errors(self) -> None:
@@ -494,7 +505,7 @@ class SplashAttentionKernel:
       raise NotImplementedError(f"only bfloat16 inputs are built on B200, got {q.dtype}")
 
   def __call__(self, q, k, v, segment_ids: SegmentIds | None = None, sinks=None, *,
-               max_logit_value=None, logits_scale: float = 1.0, **overrides):
+               max_logit_value=None, logits_scale: float = 1.0, q_shard: int = 0, **overrides):
     kw = dict(self.kwargs, **overrides)
     save_residuals = kw.get("save_residuals", False)
     self._reject_unsupported(q, k, sinks, max_logit_value)
@@ -519,8 +530,10 @@ class SplashAttentionKernel:
     if q.dim() != 4 or k.dim() != 4 or v.dim() != 4:
       raise ValueError(f"Unexpected ranks: q {q.shape}, k {k.shape}, v {v.shape}")
     q_len, kv_len = self.mask_shape
+    q_len //= self.q_seq_shards
     if q.shape[2] != q_len or k.shape[2] != kv_len or v.shape[2] != kv_len:
-      raise ValueError(f"Sequence lengths {q.shape[2]}, {k.shape[2]} do not match the mask {self.mask_shape}")
+      raise ValueError(f"Sequence lengths {q.shape[2]}, {k.shape[2]} do not match the mask {self.mask_shape}"
+                       + (f" cut into {self.q_seq_shards} q shards" if self.q_seq_shards > 1 else ""))
     if k.shape[1] == 0 or q.shape[1] % k.shape[1] != 0:
       raise ValueError(f"q heads ({q.shape[1]}) must be a multiple of kv heads ({k.shape[1]})")
     # The MMA tiles are 128 wide.  Smaller head dims run zero-padded (q k^T and p v are unchanged
@@ -559,7 +572,7 @@ class SplashAttentionKernel:
         raise ValueError(f"max_logit_value should have shape (), (1,) or ({hq},), got {tuple(value.shape)}")
       max_logit = value.reshape(-1).expand(hq).contiguous()
     o, lse, max_logits = _SplashFunction.apply(q, k, v, q_seg, kv_seg, self, float(logits_scale), sinks,
-                                               max_logit)
+                                               max_logit, int(q_shard))
     if d_v < _HEAD_DIM:
       o = o[..., :d_v]
     if not batched:
@@ -570,8 +583,9 @@ class SplashAttentionKernel:
 
   def manual_sharding_spec(self, sharding):
     raise NotImplementedError(
-        "q-sequence sharding under shard_map is a JAX construct; on B200 sequence parallelism is "
-        "tokamax_b200.ulysses.UlyssesSplashAttention"
+        "a shard_map partition spec is a JAX construct; a kernel built with q_seq_shards=n takes the q rows of "
+        "shard i through `kernel(q_i, k, v, q_shard=i)`, and tokamax_b200.q_seq_sharding.QSeqShardedSplashAttention "
+        "runs one shard per rank of a process group"
     )
 
   # pytree-style helpers kept for API parity with the reference
@@ -612,11 +626,8 @@ def _make_splash_attention(
     mask = mask_lib.NumpyMask(mask)
   if config is None:
     config = SplashConfig.get_default()
-  if q_seq_shards != 1:
-    raise NotImplementedError(
-        "q_seq_shards > 1 builds tables for shard_map; on B200 use tokamax_b200.ulysses for "
-        "sequence parallelism (MaskInfo tables for shards are available from process_mask)"
-    )
+  if q_seq_shards < 1 or mask.shape[0] % (q_seq_shards * _TILE) != 0:
+    raise ValueError(f"q_seq_shards={q_seq_shards} must cut the {mask.shape[0]} q rows into multiples of {_TILE}")
   process_fn = partial(
       mask_info_lib.process_mask,
       downcast_smem_data=downcast_smem_data,
@@ -653,6 +664,7 @@ def _make_splash_attention(
       fwd_mask_sparsity=fwd_mask_sparsity,
       dkv_mask_sparsity=dkv_mask_sparsity,
       repeatable_dq=repeatable_dq,
+      q_seq_shards=q_seq_shards,
   )
 
 

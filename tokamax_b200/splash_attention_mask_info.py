@@ -346,33 +346,45 @@ process_dynamic_mask_dkv = functools.partial(_process_dynamic_mask, is_dkv=True)
 # MaskInfo -> block grids (what the kernel schedule is cut from)
 # ----------------------------------------------------------------------------------------------
 def block_grids(
-    info: MaskInfo, n_q_blocks: int, n_kv_blocks: int, *, is_dkv: bool
+    info: MaskInfo, n_q_blocks: int, n_kv_blocks: int, *, is_dkv: bool, shard: int = 0, n_shards: int = 1
 ) -> tuple[np.ndarray, np.ndarray]:
-  """Rebuilds ``(state[n_q_blocks, n_kv_blocks], partial_id[...])`` from an unsharded MaskInfo.
+  """Rebuilds ``(state[n_q_blocks, n_kv_blocks], partial_id[...])`` from a MaskInfo.
 
   ``state`` is 0 / 1 / 2 per block in (q block, kv block) orientation whatever table it came
-  from; ``partial_id`` is the ``partial_mask_blocks`` index of partial blocks, else -1.
+  from; ``partial_id`` is the ``partial_mask_blocks`` index of partial blocks, else -1.  For tables
+  built with ``q_seq_shards = n_shards > 1`` (reference :494-544: one padded segment per shard,
+  shard-local indices) ``shard`` selects the segment and ``n_q_blocks`` counts that shard's q blocks.
   """
+  if not 0 <= shard < n_shards:
+    raise ValueError(f"shard {shard} out of range for {n_shards} shards")
   if info.block_mask is None:  # all-full mask
     return (np.full((n_q_blocks, n_kv_blocks), 2, np.int32), np.full((n_q_blocks, n_kv_blocks), -1, np.int32))
   shape = (n_kv_blocks, n_q_blocks) if is_dkv else (n_q_blocks, n_kv_blocks)
   block_mask = np.asarray(info.block_mask).astype(np.int32)
   mask_next = None if info.mask_next is None else np.asarray(info.mask_next).astype(np.int32)
+  if block_mask.size % n_shards != 0:
+    raise ValueError(f"a table of {block_mask.size} entries does not split into {n_shards} shards")
+  seg = block_mask.size // n_shards
+  lo = shard * seg
+  block_mask = block_mask[lo:lo + seg]
+  if mask_next is not None:
+    mask_next = mask_next[lo:lo + seg]
   state = np.zeros(shape, np.int32)
   pid = np.full(shape, -1, np.int32)
   if info.active_rows is not None:
-    if info.num_active_blocks is not None and len(info.num_active_blocks) != 1:
-      raise ValueError("block_grids expects an unsharded MaskInfo (q_seq_shards == kv_seq_shards == 1)")
-    n = int(info.num_active_blocks[0]) if info.num_active_blocks is not None else block_mask.size
-    rows = np.asarray(info.active_rows).astype(np.int64)[:n]
-    cols = np.asarray(info.active_cols).astype(np.int64)[:n]
+    counts = info.num_active_blocks
+    if counts is not None and len(counts) != n_shards:
+      raise ValueError(f"the MaskInfo holds {len(counts)} shards, the caller expects {n_shards}")
+    n = int(counts[shard]) if counts is not None else block_mask.size
+    rows = np.asarray(info.active_rows).astype(np.int64)[lo:lo + n]
+    cols = np.asarray(info.active_cols).astype(np.int64)[lo:lo + n]
     state[rows, cols] = block_mask[:n]
     if mask_next is not None:
       part = block_mask[:n] == 1
       pid[rows[part], cols[part]] = mask_next[:n][part]
   else:
     if block_mask.size != shape[0] * shape[1]:
-      raise ValueError("block_grids expects an unsharded MaskInfo (q_seq_shards == kv_seq_shards == 1)")
+      raise ValueError(f"a static grid of {block_mask.size} blocks per shard does not match {shape}")
     state = block_mask.reshape(shape).copy()
     if mask_next is not None:
       pid = np.where(state == 1, mask_next.reshape(shape), -1).astype(np.int32)

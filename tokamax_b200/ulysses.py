@@ -13,11 +13,18 @@ contract kept here is the one its tests state for sharded execution
 the gathered inputs.  Because the kernels are deterministic and each rank computes whole heads,
 the result is bitwise equal to a single-GPU run of the same heads.
 
-Layout: tensors are ``[batch, heads, seq, head_dim]``.  The exchange posts one send and one
-receive per (peer, batch, head) slab — a contiguous ``[seq/P, head_dim]`` block on both sides — so
-data lands directly in the ``[batch, heads/P, seq, head_dim]`` layout the kernels read: there is
-no pack or unpack copy on either side of the collective.  With NCCL the slabs of one exchange
-are coalesced into a single group launch over NVLink.
+Layout: tensors are ``[batch, heads, seq, head_dim]``.  An exchange is ONE collective
+(``all_to_all_single``, which NCCL runs as a single grouped transfer over NVLink): the send buffer is
+peer-major ``[P, batch, heads/P, seq/P, head_dim]`` — for ``batch == 1`` that is the tensor itself,
+otherwise one permuting copy — and the receive buffer ``[P(source), batch, heads/P, seq/P, head_dim]``
+is permuted into ``[batch, heads/P, seq, head_dim]`` (a view when one head arrives per rank, as for the
+K / V of a GQA model whose kv-head count equals ``P``; one local copy otherwise).  The kernels then
+read the result in place through their strided tensor maps.
+
+When ``P`` does not divide the kv-head count but every rank's q heads share one kv head (``P`` a
+multiple of ``Hkv``, e.g. 8 kv heads on 16 GPUs), that kv head is replicated: each rank receives the
+whole sequence of the one kv head its q heads read, and the backward pass sums the gradients of the
+copies (autograd of the head gather) after the reverse exchange.
 """
 
 from __future__ import annotations
@@ -36,45 +43,29 @@ def _world(group) -> tuple[int, int]:
 
 def _exchange(x: torch.Tensor, group, seq_to_head: bool) -> torch.Tensor:
   """seq_to_head: [B, H, S/P, D] -> [B, H/P, S, D]; otherwise the inverse."""
-  rank, world = _world(group)
+  _, world = _world(group)
   if world == 1:
     return x
-  x = x.contiguous()
-  b = x.shape[0]
+  b, d = x.shape[0], x.shape[3]
   if seq_to_head:
     h_all, s_loc = x.shape[1], x.shape[2]
     if h_all % world != 0:
       raise ValueError(f"heads ({h_all}) must be divisible by the context-parallel size ({world})")
     h_loc = h_all // world
-    out = torch.empty((b, h_loc, s_loc * world, x.shape[3]), dtype=x.dtype, device=x.device)
+    # peer j gets my sequence shard of its heads [j*h_loc, (j+1)*h_loc)
+    send = x.reshape(b, world, h_loc, s_loc, d).permute(1, 0, 2, 3, 4).contiguous()
   else:
     h_loc, s_all = x.shape[1], x.shape[2]
     if s_all % world != 0:
       raise ValueError(f"sequence ({s_all}) must be divisible by the context-parallel size ({world})")
     s_loc = s_all // world
-    out = torch.empty((b, h_loc * world, s_loc, x.shape[3]), dtype=x.dtype, device=x.device)
-
-  ops = []
-  for step in range(world):
-    # stagger peers so that no rank is everybody's first target
-    peer = (rank + step) % world
-    for bi in range(b):
-      for h in range(h_loc):
-        if seq_to_head:
-          send = x[bi, peer * h_loc + h]                              # my seq shard, peer's head
-          recv = out[bi, h, peer * s_loc:(peer + 1) * s_loc]          # peer's seq shard, my head
-        else:
-          send = x[bi, h, peer * s_loc:(peer + 1) * s_loc]            # peer's seq shard, my head
-          recv = out[bi, peer * h_loc + h]                            # my seq shard, peer's head
-        if peer == rank:
-          recv.copy_(send)
-        else:
-          ops.append(dist.P2POp(dist.isend, send, dist.get_global_rank(group, peer) if group else peer, group))
-          ops.append(dist.P2POp(dist.irecv, recv, dist.get_global_rank(group, peer) if group else peer, group))
-  if ops:
-    for work in dist.batch_isend_irecv(ops):
-      work.wait()
-  return out
+    # peer j gets its sequence shard of my heads
+    send = x.reshape(b, h_loc, world, s_loc, d).permute(2, 0, 1, 3, 4).contiguous()
+  recv = torch.empty_like(send)  # [P(source), B, h_loc, s_loc, D]
+  dist.all_to_all_single(recv, send, group=group)
+  if seq_to_head:  # source rank = sequence shard
+    return recv.permute(1, 2, 0, 3, 4).reshape(b, h_loc, world * s_loc, d)
+  return recv.permute(1, 0, 2, 3, 4).reshape(b, world * h_loc, s_loc, d)  # source rank = head block
 
 
 class _SeqToHead(torch.autograd.Function):
@@ -128,22 +119,37 @@ class UlyssesSplashAttention:
     group: process group spanning the context-parallel ranks (default: the world).
 
   Call with the local sequence shards ``q [B, Hq, S/P, D]``, ``k, v [B, Hkv, S/P, D]``; rank ``r``
-  holds tokens ``[r*S/P, (r+1)*S/P)``.  ``P`` must divide both head counts, which keeps the
-  reference's GQA mapping ``kv_head = q_head // (Hq / Hkv)`` rank-local.  Returns the local
-  sequence shard of the output ``[B, Hq, S/P, D]``.
+  holds tokens ``[r*S/P, (r+1)*S/P)``.  ``P`` must divide the q-head count, and either divide the
+  kv-head count too or be a multiple of it such that each rank's q heads read a single kv head (that
+  head is then replicated); this keeps the reference's GQA mapping ``kv_head = q_head // (Hq / Hkv)``
+  rank-local.  Returns the local sequence shard of the output ``[B, Hq, S/P, D]``.
   """
 
   def __init__(self, attention: Callable, group=None):
     self.attention = attention
     self.group = group
 
+  @staticmethod
+  def kv_heads_for_ranks(q_heads: int, kv_heads: int, world: int) -> list[int] | None:
+    """None if ``world`` divides ``kv_heads`` (plain exchange); else the kv head each rank reads."""
+    if q_heads % world != 0 or q_heads % kv_heads != 0:
+      raise NotImplementedError(
+          f"context-parallel size {world} must divide the q heads ({q_heads}), a multiple of the kv heads ({kv_heads})")
+    if kv_heads % world == 0:
+      return None
+    per_rank, group = q_heads // world, q_heads // kv_heads
+    if group % per_rank != 0:
+      raise NotImplementedError(
+          f"{world} ranks over {q_heads} q heads / {kv_heads} kv heads: a rank's q heads would read more than one kv "
+          "head without owning any; use ring attention for this shape")
+    return [(r * per_rank) // group for r in range(world)]
+
   def __call__(self, q, k, v, segment_ids: base.SegmentIds | None = None, *, logits_scale: float = 1.0):
     _, world = _world(self.group)
-    if q.shape[1] % world != 0 or k.shape[1] % world != 0:
-      raise NotImplementedError(
-          f"context-parallel size {world} must divide q heads ({q.shape[1]}) and kv heads ({k.shape[1]}); "
-          "kv-head replication is not built"
-      )
+    replicate = self.kv_heads_for_ranks(q.shape[1], k.shape[1], world) if world > 1 else None
+    if replicate is not None:
+      index = torch.tensor(replicate, device=k.device)
+      k, v = k.index_select(1, index), v.index_select(1, index)  # [B, P, S/P, D]: one head per destination
     q_h = seq_to_head(q, self.group)
     k_h = seq_to_head(k, self.group)
     v_h = seq_to_head(v, self.group)
