@@ -352,9 +352,10 @@ def test_unsupported_and_invalid_arguments():
                                q[:, :64], q[:, :64], q[:, :64])
 
 
-@pytest.mark.parametrize("d_qk,d_v", [(64, 64), (96, 128), (128, 32)])
-def test_head_dims_below_128_run_zero_padded(d_qk, d_v):
-  """Reference head-dim cases (splash_attention_kernel_test.py:233-237) that fit one MMA tile."""
+@pytest.mark.parametrize("d_qk,d_v", [(64, 64), (96, 128), (128, 32), (40, 72)])
+def test_head_dims_below_128_are_read_in_place(d_qk, d_v):
+  """Reference head-dim cases (splash_attention_kernel_test.py:233-237) that fit one MMA tile: no
+  padded copies, the TMA boxes zero-fill past the end of a row."""
   b, hq, hkv, s = 1, 4, 2, 384
   g = torch.Generator().manual_seed(d_qk + d_v)
   mk = lambda h, d: torch.randn(b, h, s, d, generator=g).to(torch.bfloat16)
@@ -373,6 +374,55 @@ def test_head_dims_below_128_run_zero_padded(d_qk, d_v):
   assert (res["logsumexp"].cpu() - rlse).abs().max().item() <= LSE_ATOL
   assert qd.grad.shape == q.shape and kd.grad.shape == k.shape and vd.grad.shape == v.shape
   assert _rel(qd.grad, rdq) <= GRAD_REL and _rel(kd.grad, rdk) <= GRAD_REL and _rel(vd.grad, rdv) <= GRAD_REL
+
+
+def test_small_head_dim_outputs_stay_inside_their_columns():
+  """Outputs and gradients that are column slices of wider buffers: nothing is written beyond
+  column d (the kernels hold 128-wide tiles internally)."""
+  import abi_util
+
+  b, hq, hkv, s, d = 1, 2, 1, 256, 64
+  dev = torch.device("cuda:0")
+  g = torch.Generator().manual_seed(77)
+  wide = lambda h: torch.randn(b, h, s, 128, generator=g).to(torch.bfloat16).to(dev)
+  qw, kw, vw, dow = wide(hq), wide(hkv), wide(hkv), wide(hq)
+  q, k, v, do = (t[..., :d] for t in (qw, kw, vw, dow))  # row stride 128, 64 columns: read in place
+  kernel = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1)
+  tables = kernel._tables(dev, b)  # pylint: disable=protected-access
+  lib = _native.lib()
+  import ctypes as C
+  desc = splash._tensor_desc  # pylint: disable=protected-access
+  outs = {n: torch.full((b, h, s, 128), 5.0, dtype=torch.bfloat16, device=dev)
+          for n, h in (("o", hq), ("dq", hq), ("dk", hkv), ("dv", hkv))}
+  lse = torch.empty((b, hq, s), dtype=torch.float32, device=dev)
+  stream = C.c_void_p(torch.cuda.current_stream(dev).cuda_stream)
+  fa = _native.SplashFwdArgs()
+  fa.q, fa.k, fa.v, fa.o = desc(q), desc(k), desc(v), desc(outs["o"][..., :d])
+  fa.logsumexp, fa.sched, fa.scale, fa.mask_value = lse.data_ptr(), tables.fwd, 0.125, -1e30
+  fa.mask_fn = splash._mask_fn_struct(kernel.mask_function_rule)  # pylint: disable=protected-access
+  fa.error_record = tables.error_record.data_ptr()
+  _native.check(lib.splash_fwd(C.byref(fa), stream), "splash_fwd")
+  for fused in (True, False):
+    ba = _native.SplashBwdArgs()
+    ba.q, ba.k, ba.v, ba.o, ba.d_o = desc(q), desc(k), desc(v), desc(outs["o"][..., :d]), desc(do)
+    ba.dq, ba.dk, ba.dv = (desc(outs[n][..., :d]) for n in ("dq", "dk", "dv"))
+    ba.logsumexp, ba.sched_dq, ba.sched_dkv, ba.mask_fn, ba.scale = lse.data_ptr(), tables.dq, tables.dkv, fa.mask_fn, 0.125
+    ba.error_record = fa.error_record
+    ba.flags = _native.BWD_FUSED_DQ if fused else 0
+    nbytes = (lib.splash_bwd_fused_workspace_bytes if fused else lib.splash_bwd_workspace_bytes)(b, hq, s)
+    ws = torch.empty(nbytes, dtype=torch.uint8, device=dev)
+    ba.workspace, ba.workspace_bytes = ws.data_ptr(), nbytes
+    _native.check(lib.splash_bwd(C.byref(ba), stream), "splash_bwd")
+    torch.cuda.synchronize()
+    kernel.check_errors()
+    for name, t in outs.items():
+      assert (t[..., d:] == 5.0).all(), name
+      assert not (t[..., :d] == 5.0).all(), name
+  ro, _, _, rdq, rdk, rdv = attention_ref.fwd_bwd(q.cpu(), k.cpu(), v.cpu(), do.cpu(), _dense(mask_lib.CausalMask((s, s))),
+                                                  None, scale=0.125)
+  assert ((outs["o"][..., :d].float().cpu() - ro).abs() <= 1e-2 + 4e-3 * ro.abs()).all()
+  assert _rel(outs["dq"][..., :d], rdq) <= GRAD_REL and _rel(outs["dk"][..., :d], rdk) <= GRAD_REL
+  assert _rel(outs["dv"][..., :d], rdv) <= GRAD_REL
 
 
 def test_seq_minor_layouts_give_the_head_dim_minor_result():

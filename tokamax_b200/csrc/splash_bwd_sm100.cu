@@ -50,6 +50,7 @@ struct DeltaParams {
   const float* lse;  // [B, Hq, Sq] natural log
   float* nlse2;      // [B, Hq, Sq]  -lse * log2(e): the exponent offset the MMA kernels subtract
   int q_heads, q_len;
+  int d_v;  // columns of o / do
   int64_t n_rows;
 };
 
@@ -67,7 +68,7 @@ __global__ void __launch_bounds__(256) splash_delta_kernel(const DeltaParams p) 
     const int64_t row = row0 + 2 * i;
     a[i] = make_uint4(0u, 0u, 0u, 0u);
     g[i] = a[i];
-    if (row < p.n_rows) {
+    if (row < p.n_rows && sub * 8 < p.d_v) {
       const int q = (int)(row % p.q_len);
       const int64_t bh = row / p.q_len;
       const int h = (int)(bh % p.q_heads);
@@ -123,6 +124,7 @@ struct BwdParams {
   int pm_bq, pm_bkv;
   SplashMaskFn fn;
   int q_len, kv_len, q_heads, kv_heads, n_rows;
+  int d_qk, d_v;               // real columns of q / k / dq / dk and of v / o / do / dv (<= 128)
   int n_groups, chunk_groups;  // (batch, head) pairs of the grid; how many share a launch chunk
   // soft-cap variants: logits = cap * tanh(scale * q k^T / cap); dS gains the factor 1 - tanh^2
   float soft_cap, softcap_a;   // cap; scale / cap
@@ -157,11 +159,14 @@ __device__ __forceinline__ uint32_t packed_a_col(int k) {
   return (uint32_t)((k >> 2) * 64 + (k & 3) * 8);
 }
 
+// 32 columns of a row, starting at column `col0` of a tensor that has `cols` columns: chunks of
+// eight that lie beyond the tensor's last column (head dims below 128) are not stored.
 __device__ __forceinline__ void store_row_half(__nv_bfloat16* dst, const uint32_t (&v)[32],
-                                               float mul) {
+                                               float mul, int col0 = 0, int cols = kHeadDim) {
   uint4* d4 = reinterpret_cast<uint4*>(dst);
 #pragma unroll
   for (int j = 0; j < 4; ++j) {
+    if (col0 + 8 * j >= cols) break;
     uint4 w;
     w.x = pack_bf16(__uint_as_float(v[8 * j + 0]) * mul, __uint_as_float(v[8 * j + 1]) * mul);
     w.y = pack_bf16(__uint_as_float(v[8 * j + 2]) * mul, __uint_as_float(v[8 * j + 3]) * mul);
@@ -465,15 +470,15 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           uint32_t v[32];
           tmem_ld32(tmem + lane_addr + 3 * kTile + w * 64 + g * 32, v);
           tmem_ld_wait();
-          store_row_half(dst + g * 32, v, p.scale);
+          store_row_half(dst + g * 32, v, p.scale, w * 64 + g * 32, p.d_qk);
         }
       }
     } else {
       uint32_t v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = 0u;
-      store_row_half(dst, v, 0.f);
-      store_row_half(dst + 32, v, 0.f);
+      store_row_half(dst, v, 0.f, w * 64, p.d_qk);
+      store_row_half(dst + 32, v, 0.f, w * 64 + 32, p.d_qk);
     }
   }
 
@@ -959,17 +964,17 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         uint32_t v[32];
         tmem_ld32(tmem + lane_addr + 2 * kTile + cq * 32, v);
         tmem_ld_wait();
-        store_row_half(dk, v, p.scale);
+        store_row_half(dk, v, p.scale, cq * 32, p.d_qk);
         tmem_ld32(tmem + lane_addr + 3 * kTile + cq * 32, v);
         tmem_ld_wait();
-        store_row_half(dv, v, 1.0f);
+        store_row_half(dv, v, 1.0f, cq * 32, p.d_v);
       }
     } else {
       uint32_t v[32];
 #pragma unroll
       for (int j = 0; j < 32; ++j) v[j] = 0u;
-      store_row_half(dk, v, 0.f);
-      store_row_half(dv, v, 0.f);
+      store_row_half(dk, v, 0.f, cq * 32, p.d_qk);
+      store_row_half(dv, v, 0.f, cq * 32, p.d_v);
     }
   }
 
@@ -992,6 +997,7 @@ struct DqConvertParams {
   __nv_bfloat16* dq;
   int64_t dq_sb, dq_sh, dq_ss;
   int q_heads, n_q_tiles;
+  int d_qk;  // columns of dq
   float scale;
 };
 
@@ -1019,7 +1025,7 @@ __global__ void __launch_bounds__(256) splash_dq_convert_kernel(const DqConvertP
       uint2 w;
       w.x = pack_bf16(x.x * p.scale, x.y * p.scale);
       w.y = pack_bf16(x.z * p.scale, x.w * p.scale);
-      *reinterpret_cast<uint2*>(dst + (int64_t)r * p.dq_ss + (jg * 8 + jj) * 4) = w;
+      if ((jg * 8 + jj) * 4 < p.d_qk) *reinterpret_cast<uint2*>(dst + (int64_t)r * p.dq_ss + (jg * 8 + jj) * 4) = w;
     }
   }
 }
@@ -1046,13 +1052,16 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     if ((st = check_bf16_tensor(*ts[i]))) return st;
   const int64_t B = a.q.size[0], Hq = a.q.size[1], Sq = a.q.size[2], D = a.q.size[3];
   const int64_t Hkv = a.k.size[1], Skv = a.k.size[2];
-  if (D != kHeadDim) return SPLASH_ERR_UNSUPPORTED;
-  auto same = [](const SplashTensor& x, const SplashTensor& y) {
-    return x.size[0] == y.size[0] && x.size[1] == y.size[1] && x.size[2] == y.size[2] &&
-           x.size[3] == y.size[3];
+  // head dims below 128 are read in place (zero-extended by the TMA boxes), see splash_fwd
+  const int64_t Dv = a.v.size[3];
+  if (D > kHeadDim || Dv > kHeadDim) return SPLASH_ERR_UNSUPPORTED;
+  if (D % 8 != 0 || Dv % 8 != 0) return SPLASH_ERR_INVALID_ARGUMENT;
+  auto same3 = [](const SplashTensor& x, const SplashTensor& y) {
+    return x.size[0] == y.size[0] && x.size[1] == y.size[1] && x.size[2] == y.size[2];
   };
-  if (!same(a.q, a.o) || !same(a.q, a.d_o) || !same(a.q, a.dq) || !same(a.k, a.v) ||
-      !same(a.k, a.dk) || !same(a.k, a.dv) || a.k.size[0] != B || a.k.size[3] != D)
+  if (!same3(a.q, a.o) || !same3(a.q, a.d_o) || !same3(a.q, a.dq) || !same3(a.k, a.v) || !same3(a.k, a.dk) ||
+      !same3(a.k, a.dv) || a.k.size[0] != B || a.k.size[3] != D || a.dq.size[3] != D || a.dk.size[3] != D ||
+      a.o.size[3] != Dv || a.d_o.size[3] != Dv || a.dv.size[3] != Dv)
     return SPLASH_ERR_INVALID_ARGUMENT;
   if (Hkv <= 0 || Hq % Hkv != 0) return SPLASH_ERR_INVALID_ARGUMENT;
   if (Sq % kTile != 0 || Skv % kTile != 0) return SPLASH_ERR_INVALID_ARGUMENT;
@@ -1101,6 +1110,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     dp.nlse2 = nlse2;
     dp.q_heads = (int)Hq;
     dp.q_len = (int)Sq;
+    dp.d_v = (int)Dv;
     dp.n_rows = B * Hq * Sq;
     const unsigned blocks = (unsigned)((dp.n_rows + kDeltaRowsPerBlock - 1) / kDeltaRowsPerBlock);
     splash_delta_kernel<<<blocks, 256, 0, stream>>>(dp);
@@ -1141,6 +1151,8 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.kv_len = (int)Skv;
   p.q_heads = (int)Hq;
   p.kv_heads = (int)Hkv;
+  p.d_qk = (int)D;
+  p.d_v = (int)Dv;
   p.scale = a.scale;
   p.scale_log2 = a.scale * kLog2e;
   p.err = a.error_record;
@@ -1209,6 +1221,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     cp.dq_ss = a.dq.stride[2];
     cp.q_heads = (int)Hq;
     cp.n_q_tiles = (int)(Sq / kTile);
+    cp.d_qk = (int)D;
     cp.scale = a.scale;
     const int64_t n_tiles = B * Hq * (Sq / kTile);
     if (n_tiles > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;

@@ -54,6 +54,7 @@ constexpr int kFp8TileBytes = kTile * kHeadDim;  // 16 KiB
 struct FwdParams {
   __nv_bfloat16* o;
   int64_t o_sb, o_sh, o_ss;
+  int d_v;  // columns of v / o (<= 128; the tile's remaining columns are zeros and are not stored)
   float* lse;
   float* maxl;
   const int32_t* q_seg;
@@ -552,7 +553,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           w.y = pack_bf16(__uint_as_float(v[8 * j + 2]) * inv, __uint_as_float(v[8 * j + 3]) * inv);
           w.z = pack_bf16(__uint_as_float(v[8 * j + 4]) * inv, __uint_as_float(v[8 * j + 5]) * inv);
           w.w = pack_bf16(__uint_as_float(v[8 * j + 6]) * inv, __uint_as_float(v[8 * j + 7]) * inv);
-          o4[g * 4 + j] = w;
+          if ((g * 4 + j) * 8 < p.d_v) o4[g * 4 + j] = w;
         }
       }
       const int64_t stat = ((int64_t)batch * p.q_heads + head) * p.q_len + q_row;
@@ -594,11 +595,16 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   if ((st = check_bf16_tensor(a.o))) return st;
   const int64_t B = a.q.size[0], Hq = a.q.size[1], Sq = a.q.size[2], D = a.q.size[3];
   const int64_t Hkv = a.k.size[1], Skv = a.k.size[2];
-  if (D != kHeadDim || a.k.size[3] != kHeadDim || a.v.size[3] != kHeadDim)
-    return SPLASH_ERR_UNSUPPORTED;
+  // Head dims: the MMA tile is 128 wide.  bf16 tensors with fewer columns (a multiple of 8, so rows
+  // stay 16-byte aligned) are read in place — the TMA boxes reach past the row's end and the part
+  // outside the tensor arrives as zeros, which change neither q k^T nor p v — and only the real
+  // columns of the output are stored.  Larger head dims are not built; e4m3 takes 128 only.
+  const int64_t Dv = a.v.size[3];
+  if (D > kHeadDim || Dv > kHeadDim || (fp8 && (D != kHeadDim || Dv != kHeadDim))) return SPLASH_ERR_UNSUPPORTED;
+  if (D % 8 != 0 || Dv % 8 != 0 || a.k.size[3] != D) return SPLASH_ERR_INVALID_ARGUMENT;
   if (a.k.size[0] != B || a.v.size[0] != B || a.o.size[0] != B) return SPLASH_ERR_INVALID_ARGUMENT;
   if (a.v.size[1] != Hkv || a.v.size[2] != Skv || a.o.size[1] != Hq || a.o.size[2] != Sq ||
-      a.o.size[3] != D)
+      a.o.size[3] != Dv)
     return SPLASH_ERR_INVALID_ARGUMENT;
   if (Hkv <= 0 || Hq % Hkv != 0) return SPLASH_ERR_INVALID_ARGUMENT;
   if (Sq % kTile != 0 || Skv % kTile != 0 || Sq <= 0 || Skv <= 0) return SPLASH_ERR_INVALID_ARGUMENT;
@@ -623,6 +629,7 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   p.o_sb = a.o.stride[0];
   p.o_sh = a.o.stride[1];
   p.o_ss = a.o.stride[2];
+  p.d_v = (int)Dv;
   p.lse = a.logsumexp;
   p.maxl = a.max_logits;
   p.q_seg = a.q_segment_ids;

@@ -305,7 +305,10 @@ class _SplashFunction(torch.autograd.Function):
     tables = kernel._tables(q.device, q.shape[0], shard)  # pylint: disable=protected-access
     q, k, v = _usable(q), _usable(k), _usable(v)
     b, hq, sq, d = q.shape
-    o = torch.empty_like(q)  # keeps q's (dense) stride order, e.g. [B,T,H,D] storage stays [B,T,H,D]
+    if v.shape[-1] == d:
+      o = torch.empty_like(q)  # keeps q's (dense) stride order, e.g. [B,T,H,D] storage stays [B,T,H,D]
+    else:
+      o = torch.empty((b, hq, sq, v.shape[-1]), dtype=q.dtype, device=q.device)
     lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
     max_logits = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
     args = _native.SplashFwdArgs()
@@ -536,19 +539,17 @@ class SplashAttentionKernel:
                        + (f" cut into {self.q_seq_shards} q shards" if self.q_seq_shards > 1 else ""))
     if k.shape[1] == 0 or q.shape[1] % k.shape[1] != 0:
       raise ValueError(f"q heads ({q.shape[1]}) must be a multiple of kv heads ({k.shape[1]})")
-    # The MMA tiles are 128 wide.  Smaller head dims run zero-padded (q k^T and p v are unchanged
-    # by zero columns; the padding of the output and of the gradients is sliced off again), at
-    # the cost of the padded work; larger ones are not built.
+    # The MMA tiles are 128 wide.  Smaller head dims (multiples of 8; q / k and v may differ) are
+    # read in place: the kernels' TMA boxes reach past the end of a row and get zeros there, which
+    # change neither q k^T nor p v, and only the real columns of outputs and gradients are stored.
+    # No copy is made, but the MMAs still run at the full tile width.  Larger ones are not built.
     d_qk, d_v = q.shape[-1], v.shape[-1]
     if k.shape[-1] != d_qk:
       raise ValueError(f"q and k head dims differ: {d_qk} vs {k.shape[-1]}")
     if d_qk > _HEAD_DIM or d_v > _HEAD_DIM:
       raise NotImplementedError(f"head dims above {_HEAD_DIM} are not built on B200, got {d_qk} / {d_v}")
-    if d_qk < _HEAD_DIM:
-      q = torch.nn.functional.pad(q, (0, _HEAD_DIM - d_qk))
-      k = torch.nn.functional.pad(k, (0, _HEAD_DIM - d_qk))
-    if d_v < _HEAD_DIM:
-      v = torch.nn.functional.pad(v, (0, _HEAD_DIM - d_v))
+    if d_qk % 8 or d_v % 8:
+      raise NotImplementedError(f"head dims must be multiples of 8 (16-byte rows), got {d_qk} / {d_v}")
     q_seg = kv_seg = None
     if segment_ids is not None:
       q_seg = torch.as_tensor(segment_ids.q, device=q.device).to(torch.int32)
@@ -573,8 +574,6 @@ class SplashAttentionKernel:
       max_logit = value.reshape(-1).expand(hq).contiguous()
     o, lse, max_logits = _SplashFunction.apply(q, k, v, q_seg, kv_seg, self, float(logits_scale), sinks,
                                                max_logit, int(q_shard))
-    if d_v < _HEAD_DIM:
-      o = o[..., :d_v]
     if not batched:
       o, lse, max_logits = o[0], lse[0], max_logits[0]
     if save_residuals:
