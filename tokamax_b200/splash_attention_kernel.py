@@ -625,7 +625,7 @@ def _make_splash_attention(
     mask = mask_lib.NumpyMask(mask)
   if config is None:
     config = SplashConfig.get_default()
-  if q_seq_shards < 1 or mask.shape[0] % (q_seq_shards * _TILE) != 0:
+  if q_seq_shards < 1 or (q_seq_shards > 1 and mask.shape[0] % (q_seq_shards * _TILE) != 0):
     raise ValueError(f"q_seq_shards={q_seq_shards} must cut the {mask.shape[0]} q rows into multiples of {_TILE}")
   process_fn = partial(
       mask_info_lib.process_mask,
