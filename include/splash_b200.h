@@ -323,6 +323,34 @@ int splash_bwd(const SplashBwdArgs* args, void* cuda_stream);
 int splash_ring_merge(float* o_acc, float* lse_acc, const void* o_i, const float* lse_i, int64_t n_rows,
                       int64_t head_dim, void* cuda_stream);
 
+/* ------------------------------------------------------------------------------------------
+ * Context-parallel exchange by peer stores (sequence shard <-> head shard, the Ulysses all-to-all).
+ * The reference has no all-to-all — its context-parallel wrapper is ring attention over
+ * lax.ppermute (ring_attention_kernel.py:95-99) — so this stands where
+ * `jax.lax.all_to_all(x, axis, split_axis=heads, concat_axis=seq)` would around the kernels.
+ *
+ * seq_to_head = 1: `src` is this rank's [batch, h_loc * world, s_loc, head_dim] (its sequence shard
+ * of all heads); peer j receives heads [j * h_loc, (j + 1) * h_loc) at sequence offset
+ * rank * s_loc of its [batch, h_loc, s_loc * world, head_dim] buffer.  seq_to_head = 0 is the
+ * inverse.  `dst_ptrs` is a DEVICE array of `world` pointers to the ranks' receive buffers (peer
+ * mappings of symmetric / IPC memory; entry `rank` is this rank's own buffer), every one laid out as
+ * the kernels read it, so there is no pack or unpack pass.  Plain 16-byte loads and stores: no TMA,
+ * no multicast.  The caller orders the ranks: a barrier before the call (receive buffers no longer
+ * in use) and one after it (all pushes have landed); any stream-ordered collective does (the Python
+ * layer uses a one-element NCCL all-reduce).  Tensors are contiguous; row_bytes =
+ * head_dim * element size must be a multiple of 16. */
+typedef struct SplashExchangeArgs {
+  const void* src;
+  void* const* dst_ptrs;   /* device memory: world pointers */
+  int32_t world, rank;
+  int32_t seq_to_head;
+  int64_t batch, h_loc, s_loc, row_bytes;
+  int64_t dst_base_bytes;  /* offset of the receive buffer inside each rank's mapped block (the same
+                              on every rank for symmetric allocations; 0 if dst_ptrs point at the
+                              buffers themselves); a multiple of 16 */
+} SplashExchangeArgs;
+int splash_exchange_push(const SplashExchangeArgs* args, void* cuda_stream);
+
 /* Backward pass for callers that cannot obtain device memory at the point of the call.
  * (No counterpart in the reference; it exists only on this side of the boundary.)
  *

@@ -24,7 +24,7 @@ def _free_port():
     return s.getsockname()[1]
 
 
-def _worker(rank, world, port, queue):
+def _worker(rank, world, port, queue, exchange="nccl"):
   os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
   dev = torch.device("cuda", rank)
   torch.cuda.set_device(dev)
@@ -46,12 +46,18 @@ def _worker(rank, world, port, queue):
     full.backward(do)
     sl = slice(rank * s // world, (rank + 1) * s // world)
     ql, kl, vl = (t[:, :, sl].clone().requires_grad_(True) for t in (q, k, v))
-    out = ulysses.UlyssesSplashAttention(kernel)(ql, kl, vl, logits_scale=scale)
-    out.backward(do[:, :, sl].contiguous())
-    torch.cuda.synchronize()
-    kernel.check_errors()
-    ok = (torch.equal(out, full[:, :, sl]) and torch.equal(ql.grad, qf.grad[:, :, sl])
-          and torch.equal(kl.grad, kf.grad[:, :, sl]) and torch.equal(vl.grad, vf.grad[:, :, sl]))
+    cp = ulysses.UlyssesSplashAttention(kernel, exchange=exchange)
+    ok = True
+    for _ in range(2):  # twice: the peer exchange reuses its buffers
+      ql.grad = kl.grad = vl.grad = None
+      out = cp(ql, kl, vl, logits_scale=scale)
+      out.backward(do[:, :, sl].contiguous())
+      torch.cuda.synchronize()
+      kernel.check_errors()
+      ok = ok and (torch.equal(out, full[:, :, sl]) and torch.equal(ql.grad, qf.grad[:, :, sl])
+                   and torch.equal(kl.grad, kf.grad[:, :, sl]) and torch.equal(vl.grad, vf.grad[:, :, sl]))
+    with torch.no_grad():
+      ok = ok and torch.equal(cp(ql, kl, vl, logits_scale=scale), full[:, :, sl])
     queue.put((rank, "ok" if ok else "mismatch"))
   except Exception as e:  # pylint: disable=broad-except
     queue.put((rank, f"{type(e).__name__}: {e}"))
@@ -60,12 +66,13 @@ def _worker(rank, world, port, queue):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-def test_ulysses_matches_single_gpu_bitwise():
+@pytest.mark.parametrize("exchange", ["nccl", "peer"])
+def test_ulysses_matches_single_gpu_bitwise(exchange):
   world = 2
   ctx = mp.get_context("spawn")
   queue = ctx.Queue()
   port = _free_port()
-  procs = [ctx.Process(target=_worker, args=(r, world, port, queue)) for r in range(world)]
+  procs = [ctx.Process(target=_worker, args=(r, world, port, queue, exchange)) for r in range(world)]
   for p in procs:
     p.start()
   results = [queue.get(timeout=300) for _ in range(world)]

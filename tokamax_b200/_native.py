@@ -26,6 +26,7 @@ SOURCES = (
     "segment_schedule.cu",
     "dynamic_schedule.cu",
     "ring_merge.cu",
+    "exchange.cu",
     "splash_xla_ffi.cc",  # handlers compile only where xla/ffi/api/ffi.h is on the include path
 )
 
@@ -171,6 +172,17 @@ class SplashBwdArgs(C.Structure):
 BWD_FUSED_DQ = 1  # SplashBwdFlags.SPLASH_BWD_FUSED_DQ
 
 
+class SplashExchangeArgs(C.Structure):
+  _fields_ = [
+      ("src", C.c_void_p),
+      ("dst_ptrs", C.c_void_p),
+      ("world", C.c_int32), ("rank", C.c_int32),
+      ("seq_to_head", C.c_int32),
+      ("batch", C.c_int64), ("h_loc", C.c_int64), ("s_loc", C.c_int64), ("row_bytes", C.c_int64),
+      ("dst_base_bytes", C.c_int64),
+  ]
+
+
 # name -> (restype, argtypes); every function include/splash_b200.h declares.
 _PROTOTYPES = {
     "splash_maskinfo_build": (C.c_int, [C.POINTER(SplashMaskNode), C.c_int32, C.c_int64, C.c_int64,
@@ -195,6 +207,7 @@ _PROTOTYPES = {
     "splash_bwd_fused_workspace_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "splash_bwd": (C.c_int, [C.POINTER(SplashBwdArgs), C.c_void_p]),
     "splash_bwd_static_scratch": (C.c_int, [C.POINTER(SplashBwdArgs), C.c_void_p]),
+    "splash_exchange_push": (C.c_int, [C.POINTER(SplashExchangeArgs), C.c_void_p]),
     "splash_read_error": (C.c_int, [C.c_void_p, C.c_void_p, C.POINTER(C.c_uint32 * 4)]),
     "splash_probe_bounded_wait": (C.c_int, [C.c_void_p, C.c_int64, C.c_uint32, C.c_void_p]),
     "splash_xla_ffi_compiled": (C.c_int, []),

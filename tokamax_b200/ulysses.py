@@ -68,38 +68,150 @@ def _exchange(x: torch.Tensor, group, seq_to_head: bool) -> torch.Tensor:
   return recv.permute(1, 0, 2, 3, 4).reshape(b, world * h_loc, s_loc, d)  # source rank = head block
 
 
+class PeerExchange:
+  """The same exchange by peer stores instead of a collective (``splash_exchange_push``).
+
+  Receive buffers are symmetric-memory allocations (``torch.distributed._symmetric_memory``: every
+  rank maps every other rank's buffer), laid out as the attention kernels read them; a rank copies
+  its outgoing ``[S/P, D]`` slabs straight into its peers' buffers with its own copy kernel — plain
+  16-byte loads and stores over NVLink, no TMA, no multicast — between two stream-ordered barriers
+  (buffers free / all pushes landed; each a one-element NCCL all-reduce, so a rank that never
+  arrives ends in NCCL's own timeout rather than in a spinning kernel).  Nothing is packed or
+  unpacked.
+
+  Buffers are cached per (tag, shape) and reused by the next call, so what a call leaves in them is
+  only valid until the same tag is exchanged again: :class:`UlyssesSplashAttention` copies what it
+  hands back to the caller (output, gradients) and gives each forward call whose backward is still
+  pending its own set of buffers (``max_pending`` sets at most).
+  """
+
+  def __init__(self, group=None, max_pending: int = 4):
+    import torch.distributed._symmetric_memory as symm_mem  # pylint: disable=g-import-not-at-top
+
+    self._symm_mem = symm_mem
+    self.group = group if group is not None else dist.group.WORLD
+    self.max_pending = max_pending
+    self._buffers: dict = {}
+    self._pending: set[int] = set()
+    self._flag: torch.Tensor | None = None
+
+  def _barrier(self, device) -> None:
+    if self._flag is None:
+      self._flag = torch.zeros(1, dtype=torch.float32, device=device)
+    dist.all_reduce(self._flag, group=self.group)  # enqueued on the current stream, ordered with the kernels around it
+
+  def acquire(self, hold: bool) -> int:
+    """A buffer-set index for one forward call; held until :meth:`release` if ``hold``."""
+    slot = next(i for i in range(self.max_pending + 1) if i not in self._pending)
+    if slot == self.max_pending:
+      raise RuntimeError(f"{self.max_pending} forward calls are waiting for their backward; run backward (or call "
+                         "under torch.no_grad()) before calling again, or raise max_pending")
+    if hold:
+      self._pending.add(slot)
+    return slot
+
+  def release(self, slot: int) -> None:
+    self._pending.discard(slot)
+
+  def _buffer(self, tag: str, shape, dtype, device):
+    key = (tag, tuple(shape), dtype)
+    if key not in self._buffers:
+      t = self._symm_mem.empty(*shape, dtype=dtype, device=device)
+      handle = self._symm_mem.rendezvous(t, self.group)  # collective: ranks create buffers in the same order
+      # the mapped block may be larger than the tensor: where the tensor starts inside it
+      base = t.data_ptr() - int(handle.buffer_ptrs[handle.rank])
+      if base < 0 or base + t.numel() * t.element_size() > int(handle.buffer_size):
+        raise RuntimeError(f"symmetric buffer for {tag}: tensor at {base} outside its block of {handle.buffer_size} bytes")
+      self._buffers[key] = (t, handle, base)
+    return self._buffers[key]
+
+  def exchange(self, x: torch.Tensor, seq_to_head: bool, tag: str) -> torch.Tensor:
+    import ctypes as C  # pylint: disable=g-import-not-at-top
+    from tokamax_b200 import _native  # pylint: disable=g-import-not-at-top
+
+    rank, world = _world(self.group)
+    x = x.contiguous()
+    b, d = x.shape[0], x.shape[3]
+    if seq_to_head:
+      if x.shape[1] % world:
+        raise ValueError(f"heads ({x.shape[1]}) must be divisible by the context-parallel size ({world})")
+      h_loc, s_loc = x.shape[1] // world, x.shape[2]
+      out_shape = (b, h_loc, s_loc * world, d)
+    else:
+      if x.shape[2] % world:
+        raise ValueError(f"sequence ({x.shape[2]}) must be divisible by the context-parallel size ({world})")
+      h_loc, s_loc = x.shape[1], x.shape[2] // world
+      out_shape = (b, h_loc * world, s_loc, d)
+    out, handle, base = self._buffer(tag, out_shape, x.dtype, x.device)
+    args = _native.SplashExchangeArgs()
+    args.src, args.dst_ptrs = x.data_ptr(), int(handle.buffer_ptrs_dev)
+    args.world, args.rank, args.seq_to_head = world, rank, int(seq_to_head)
+    args.batch, args.h_loc, args.s_loc, args.row_bytes = b, h_loc, s_loc, d * x.element_size()
+    args.dst_base_bytes = base
+    stream = torch.cuda.current_stream(x.device).cuda_stream
+    with torch.cuda.device(x.device):
+      self._barrier(x.device)  # every rank's earlier readers of its receive buffer are behind this point
+      _native.check(_native.lib().splash_exchange_push(C.byref(args), C.c_void_p(stream)), "splash_exchange_push")
+      self._barrier(x.device)  # every rank's stores have landed
+    return out
+
+
+def _run_exchange(x, group, seq_to_head: bool, engine, tag):
+  if engine is None or dist.get_world_size(group) == 1:
+    return _exchange(x, group, seq_to_head)
+  return engine.exchange(x, seq_to_head, tag)
+
+
 class _SeqToHead(torch.autograd.Function):
 
   @staticmethod
-  def forward(ctx, x, group):
-    ctx.group = group
-    return _exchange(x, group, True)
+  def forward(ctx, x, group, engine=None, tag=None):
+    ctx.group, ctx.engine, ctx.tag = group, engine, tag
+    return _run_exchange(x, group, True, engine, tag)
 
   @staticmethod
   def backward(ctx, g):
-    return _exchange(g, ctx.group, False), None
+    out = _run_exchange(g, ctx.group, False, ctx.engine, None if ctx.tag is None else ctx.tag + ".grad")
+    if ctx.engine is not None:
+      out = out.clone()  # handed to the caller as a .grad: must outlive the buffer's next use
+    return out, None, None, None
 
 
 class _HeadToSeq(torch.autograd.Function):
 
   @staticmethod
-  def forward(ctx, x, group):
-    ctx.group = group
-    return _exchange(x, group, False)
+  def forward(ctx, x, group, engine=None, tag=None):
+    ctx.group, ctx.engine, ctx.tag = group, engine, tag
+    return _run_exchange(x, group, False, engine, tag)
 
   @staticmethod
   def backward(ctx, g):
-    return _exchange(g, ctx.group, True), None
+    return _run_exchange(g, ctx.group, True, ctx.engine, None if ctx.tag is None else ctx.tag + ".grad"), None, None, None
 
 
-def seq_to_head(x: torch.Tensor, group=None) -> torch.Tensor:
+def seq_to_head(x: torch.Tensor, group=None, engine: PeerExchange | None = None, tag: str | None = None) -> torch.Tensor:
   """Differentiable all-to-all: sequence shard of all heads -> all of the sequence for H/P heads."""
-  return _SeqToHead.apply(x, group)
+  return _SeqToHead.apply(x, group, engine, tag)
 
 
-def head_to_seq(x: torch.Tensor, group=None) -> torch.Tensor:
+def head_to_seq(x: torch.Tensor, group=None, engine: PeerExchange | None = None, tag: str | None = None) -> torch.Tensor:
   """Differentiable inverse of :func:`seq_to_head`."""
-  return _HeadToSeq.apply(x, group)
+  return _HeadToSeq.apply(x, group, engine, tag)
+
+
+class _ReleaseOnBackward(torch.autograd.Function):
+  """Identity on q's path; its backward runs after the attention's, which is when the buffer set of
+  the forward call is no longer needed."""
+
+  @staticmethod
+  def forward(ctx, x, engine, slot):
+    ctx.engine, ctx.slot = engine, slot
+    return x.view_as(x)
+
+  @staticmethod
+  def backward(ctx, g):
+    ctx.engine.release(ctx.slot)
+    return g, None, None
 
 
 def exchange_bytes_sent(shape, itemsize: int, world: int) -> int:
@@ -117,6 +229,8 @@ class UlyssesSplashAttention:
     attention: a ``SplashAttentionKernel`` built for the FULL (unsharded) mask, or any callable
       ``(q, k, v, segment_ids, *, logits_scale) -> out`` over ``[batch, heads, seq, dim]``.
     group: process group spanning the context-parallel ranks (default: the world).
+    exchange: "nccl" (default: one ``all_to_all_single`` per tensor) or "peer" (:class:`PeerExchange`:
+      own copy kernel over symmetric memory; CUDA + NVLink peers only).
 
   Call with the local sequence shards ``q [B, Hq, S/P, D]``, ``k, v [B, Hkv, S/P, D]``; rank ``r``
   holds tokens ``[r*S/P, (r+1)*S/P)``.  ``P`` must divide the q-head count, and either divide the
@@ -125,9 +239,12 @@ class UlyssesSplashAttention:
   rank-local.  Returns the local sequence shard of the output ``[B, Hq, S/P, D]``.
   """
 
-  def __init__(self, attention: Callable, group=None):
+  def __init__(self, attention: Callable, group=None, exchange: str = "nccl"):
+    if exchange not in ("nccl", "peer"):
+      raise ValueError(f"exchange must be 'nccl' or 'peer', got {exchange!r}")
     self.attention = attention
     self.group = group
+    self.engine = PeerExchange(group) if exchange == "peer" else None
 
   @staticmethod
   def kv_heads_for_ranks(q_heads: int, kv_heads: int, world: int) -> list[int] | None:
@@ -150,14 +267,23 @@ class UlyssesSplashAttention:
     if replicate is not None:
       index = torch.tensor(replicate, device=k.device)
       k, v = k.index_select(1, index), v.index_select(1, index)  # [B, P, S/P, D]: one head per destination
-    q_h = seq_to_head(q, self.group)
-    k_h = seq_to_head(k, self.group)
-    v_h = seq_to_head(v, self.group)
+    engine = self.engine if world > 1 else None
+    tags = (None, None, None, None)
+    if engine is not None:
+      needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v))
+      slot = engine.acquire(needs_grad)
+      tags = tuple(f"{name}{slot}" for name in ("q", "k", "v", "o"))
+      if needs_grad:
+        q = _ReleaseOnBackward.apply(q, engine, slot)
+    q_h = seq_to_head(q, self.group, engine, tags[0])
+    k_h = seq_to_head(k, self.group, engine, tags[1])
+    v_h = seq_to_head(v, self.group, engine, tags[2])
     seg_full = None
     if segment_ids is not None:
       seg_full = base.SegmentIds(self._gather_seq(segment_ids.q), self._gather_seq(segment_ids.kv))
     o_h = self.attention(q_h, k_h, v_h, seg_full, logits_scale=logits_scale)
-    return head_to_seq(o_h, self.group)
+    out = head_to_seq(o_h, self.group, engine, tags[3])
+    return out.clone() if engine is not None else out  # the caller's tensor must outlive the buffer's next use
 
   def _gather_seq(self, ids: torch.Tensor) -> torch.Tensor:
     _, world = _world(self.group)
