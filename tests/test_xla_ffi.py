@@ -108,3 +108,25 @@ def test_jax_backend_needs_jax_and_says_so():
     pass
   with pytest.raises(ImportError, match="jax"):
     import tokamax_b200.jax_backend  # noqa: F401  pylint: disable=unused-import,g-import-not-at-top
+
+
+def test_autotuning_cache_entries_are_in_the_reference_format():
+  """<device kind>/<snake-cased op class>.json: bound arguments (JSON) -> config (JSON) -> timings
+  (reference tokamax/_src/autotuning/cache.py:72-112 and its shipped data files)."""
+  import json
+  import re
+
+  op_name = re.sub(r"(?!^)([A-Z])", r"_\1", "CudaSm100SplashAttention").lower()
+  root = os.path.join(os.path.dirname(HERE), "tokamax_b200", "data", "autotuning", "nvidia_b200")
+  path = os.path.join(root, f"{op_name}.json")
+  assert os.path.isfile(path), path
+  data = json.load(open(path))
+  assert data
+  for key, configs in data.items():
+    bound = json.loads(key)
+    assert {"q", "k", "v", "mask", "logits_scale", "return_residuals"} <= set(bound)
+    assert re.fullmatch(r"bf16\[\d+,\d+,\d+,128\]", bound["q"])
+    for cfg, timing in configs.items():
+      assert set(json.loads(cfg)) == {"block_q", "block_kv"}
+      assert {"compile_time_ms", "lower_time_ms", "evaluation_times_ms", "metadata"} <= set(timing)
+      assert all(t > 0 for t in timing["evaluation_times_ms"])

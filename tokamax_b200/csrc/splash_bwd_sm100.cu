@@ -125,6 +125,7 @@ struct BwdParams {
   SplashMaskFn fn;
   int q_len, kv_len, q_heads, kv_heads, n_rows;
   int d_qk, d_v;               // real columns of q / k / dq / dk and of v / o / do / dv (<= 128)
+  int nk_qk, nk_v;             // K = 16 slices with real columns in contractions over d_qk / d_v
   int n_groups, chunk_groups;  // (batch, head) pairs of the grid; how many share a launch chunk
   // soft-cap variants: logits = cap * tanh(scale * q k^T / cap); dS gains the factor 1 - tanh^2
   float soft_cap, softcap_a;   // cap; scale / cap
@@ -270,10 +271,11 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       constexpr uint32_t idesc_mn = make_idesc_bf16(kTile, kHeadDim, false, true);
       const uint32_t q_addr = smem_u32(q_smem), do_addr = smem_u32(do_smem), ring_addr = smem_u32(ring);
       const uint32_t t_dp = tmem + 2 * kTile, t_dq = tmem + 3 * kTile;
-      auto ss_kmajor = [&](uint32_t d, uint32_t a0, uint32_t b0) {
+      auto ss_kmajor = [&](uint32_t d, uint32_t a0, uint32_t b0, int nk) {
         const SmemDesc da = make_smem_desc_sw128(a0, 16, 1024), db = make_smem_desc_sw128(b0, 16, 1024);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
+          if (nk != 8 && k >= nk) break;  // head dims below 128: the remaining slices multiply zeros
           const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
           umma_ss(d, desc_at(da, off), desc_at(db, off), idesc_kk, k > 0 ? 1u : 0u);
         }
@@ -286,13 +288,13 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       ok = ok && ring_wait(0, 0x1210u);
       if (ok) {
         mma_issue_fence();
-        ss_kmajor(tmem, q_addr, ring_addr);
+        ss_kmajor(tmem, q_addr, ring_addr, p.nk_qk);
         tc_commit(&bars->s_full[0]);
       }
       ok = ok && ring_wait(1, 0x1211u);
       if (ok) {
         mma_issue_fence();
-        ss_kmajor(t_dp, do_addr, ring_addr + kTileBytes);
+        ss_kmajor(t_dp, do_addr, ring_addr + kTileBytes, p.nk_v);
         tc_commit(&bars->dp_full);
         tc_commit(&bars->ring_empty[1]);
       }
@@ -303,7 +305,7 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ok = ring_wait(it_kn, 0x1220u);
           if (!ok) break;
           mma_issue_fence();
-          ss_kmajor(tmem + ((n + 1) & 1) * kTile, q_addr, ring_addr + (it_kn % kDqStages) * kTileBytes);
+          ss_kmajor(tmem + ((n + 1) & 1) * kTile, q_addr, ring_addr + (it_kn % kDqStages) * kTileBytes, p.nk_qk);
           tc_commit(&bars->s_full[(n + 1) & 1]);
         }
         ok = mbar_wait(&bars->ds_full, n & 1u, ab, 0x1230u);
@@ -322,7 +324,7 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           ok = ring_wait(it_vn, 0x1240u);
           if (!ok) break;
           mma_issue_fence();
-          ss_kmajor(t_dp, do_addr, ring_addr + (it_vn % kDqStages) * kTileBytes);
+          ss_kmajor(t_dp, do_addr, ring_addr + (it_vn % kDqStages) * kTileBytes, p.nk_v);
           tc_commit(&bars->dp_full);
           tc_commit(&bars->ring_empty[it_vn % kDqStages]);
         }
@@ -703,10 +705,11 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         return mbar_wait(&bars->ring_full[it % kBwdStages], (it / kBwdStages) & 1u, ab, tag);
       };
       // D = A B^T with both operands K-major (head_dim contiguous), K = head_dim
-      auto issue_score = [&](uint32_t d, SmemDesc da, uint32_t b0) {
+      auto issue_score = [&](uint32_t d, SmemDesc da, uint32_t b0, int nk) {
         const SmemDesc db = make_smem_desc_sw128(b0, 16, 1024);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
+          if (nk != 8 && k >= nk) break;  // head dims below 128: the remaining slices multiply zeros
           const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
           umma_ss(d, desc_at(da, off), desc_at(db, off), idesc_s, k > 0 ? 1u : 0u);
         }
@@ -721,12 +724,12 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       bool ok = mbar_wait(&bars->stat_full[0], 0, ab, 0x3200u) && mbar_wait(&bars->stat_full[1], 0, ab, 0x3201u);
       ok = ok && ring_wait(0, 0x3210u);
       if (ok) {
-        issue_score(t_st, k_desc, slot_addr(0));
+        issue_score(t_st, k_desc, slot_addr(0), p.nk_qk);
         tc_commit(&bars->st_full);
       }
       ok = ok && ring_wait(1, 0x3211u);
       if (ok) {
-        issue_score(t_dpt, v_desc, slot_addr(1));
+        issue_score(t_dpt, v_desc, slot_addr(1), p.nk_v);
         tc_commit(&bars->dpt_full);
       }
       for (int n = 0; n < n_steps && ok; ++n) {
@@ -746,7 +749,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         if (more) {
           ok = ring_wait(2 * (n + 1), 0x3240u);
           if (!ok) break;
-          issue_score(t_st, k_desc, slot_addr(2 * (n + 1)));
+          issue_score(t_st, k_desc, slot_addr(2 * (n + 1)), p.nk_qk);
           tc_commit(&bars->st_full);
         }
         ok = mbar_wait(&bars->ds_full, ph, ab, 0x3230u);
@@ -781,7 +784,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (!ok) break;
             mma_issue_fence();
           }
-          issue_score(t_dpt, v_desc, slot_addr(2 * (n + 1) + 1));
+          issue_score(t_dpt, v_desc, slot_addr(2 * (n + 1) + 1), p.nk_v);
           tc_commit(&bars->dpt_full);
         }
       }
@@ -1153,6 +1156,8 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.kv_heads = (int)Hkv;
   p.d_qk = (int)D;
   p.d_v = (int)Dv;
+  p.nk_qk = (int)((D + 15) / 16);
+  p.nk_v = (int)((Dv + 15) / 16);
   p.scale = a.scale;
   p.scale_log2 = a.scale * kLog2e;
   p.err = a.error_record;

@@ -55,6 +55,7 @@ struct FwdParams {
   __nv_bfloat16* o;
   int64_t o_sb, o_sh, o_ss;
   int d_v;  // columns of v / o (<= 128; the tile's remaining columns are zeros and are not stored)
+  int nk_qk;  // K = 16 slices of q k^T that hold real columns: ceil(d_qk / 16); the rest are zeros and are skipped
   float* lse;
   float* maxl;
   const int32_t* q_seg;
@@ -226,6 +227,9 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         } else {
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
+            // head dims below 128: the remaining slices multiply zeros (nk_qk == 8 is tested first so
+            // that the full-width path stays a straight run of eight MMAs)
+            if (p.nk_qk != 8 && k >= p.nk_qk) break;
             const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
             umma_ss(tmem + i * kTile, desc_at(da, off), desc_at(db, off), idesc_qk, k > 0 ? 1u : 0u);
           }
@@ -630,6 +634,7 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   p.o_sh = a.o.stride[1];
   p.o_ss = a.o.stride[2];
   p.d_v = (int)Dv;
+  p.nk_qk = (int)((D + 15) / 16);
   p.lse = a.logsumexp;
   p.maxl = a.max_logits;
   p.q_seg = a.q_segment_ids;

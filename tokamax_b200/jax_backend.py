@@ -49,6 +49,19 @@ from tokamax_b200 import xla_ffi
 
 _registered = False
 
+# Autotuning-cache entries for this backend in the reference's format
+# (tokamax/_src/autotuning/cache.py:72-112: <cache dir>/<device kind>/<op name>.json, bound
+# arguments -> config -> timings) ship in tokamax_b200/data/autotuning/nvidia_b200/; pass that
+# directory to tokamax's AutotuningCache(paths=[...]) to have them picked up.
+AUTOTUNING_CACHE_DIR = "data/autotuning"
+
+
+@dataclasses.dataclass(frozen=True)
+class Config:
+  """The backend's only configuration: the MaskInfo block size (the MMA tile is fixed at 128 x 128)."""
+  block_q: int = 128
+  block_kv: int = 128
+
 
 def _register_ffi_targets() -> None:
   global _registered
@@ -162,6 +175,7 @@ class CudaSm100SplashAttentionVjp(attention_base.DotProductAttentionVjp):
 class CudaSm100SplashAttention(attention_base.DotProductAttention):
   """Splash attention on B200 through the XLA custom call."""
 
+  config_cls: ClassVar[type[Config]] = Config
   supports_symbolic_shapes: ClassVar[bool] = False
 
   def __post_init__(self):
@@ -194,7 +208,10 @@ class CudaSm100SplashAttention(attention_base.DotProductAttention):
     return out, residuals
 
   def _get_heuristics_config(self, ba: op_lib.BoundArguments):
-    return None  # the MMA tile is fixed at 128 x 128; there is nothing to tune per call
+    return Config()  # the MMA tile is fixed at 128 x 128; there is nothing to tune per call
+
+  def _get_autotuning_configs(self, ba: op_lib.BoundArguments) -> set[Config]:
+    return {Config()}
 
   def supported_on(self, device: jax.Device) -> bool:
     if device.platform != "gpu":
