@@ -155,9 +155,15 @@ class ClockSampler:
       return
     def pump():
       for line in self.proc.stdout:
-        self.rows.append([c.strip() for c in line.split(",")])
+        self.rows.append([time.time()] + [c.strip() for c in line.split(",")])
     self.thread = threading.Thread(target=pump, daemon=True)
     self.thread.start()
+
+  def mark(self):
+    """Call when the timed region starts: only samples that arrive after this are reported (the
+    sampler is started before the warm-up, because nvidia-smi can take longer to produce its first
+    line than a short timed region lasts)."""
+    self.t0 = time.time()
 
   def stop(self) -> dict:
     if self.proc is None:
@@ -171,7 +177,11 @@ class ClockSampler:
       self.thread.join(timeout=2)
     sm, smax, reasons = [], [], set()
     names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+    t0 = getattr(self, "t0", 0.0)
     for r in self.rows:
+      if r[0] < t0:
+        continue
+      r = r[1:]
       if len(r) < 7:
         continue
       try:
@@ -452,10 +462,11 @@ def run_single_gpu(args, w, wname, emit=True):
     return out, qd.grad, kd.grad, vd.grad
 
   sampler = ClockSampler(dev.index or 0)
+  sampler.start()
   for _ in range(args.warmup):
     step()
   torch.cuda.synchronize()
-  sampler.start()
+  sampler.mark()
   ms = timed_steps(step, args.steps, 0)
   clocks = sampler.stop()
   kernel.check_errors()
@@ -591,10 +602,11 @@ def run_fp8_prefill(args, w, wname, emit=True):
       return kernel(q, k, v, logits_scale=SCALE)
 
   sampler = ClockSampler(dev.index or 0)
+  sampler.start()
   for _ in range(args.warmup):
     step()
   torch.cuda.synchronize()
-  sampler.start()
+  sampler.mark()
   ms = timed_steps(step, args.steps, 0)
   clocks = sampler.stop()
   kernel.check_errors()
@@ -698,11 +710,12 @@ def run_context_parallel(args, w, wname):
     return t.item()
 
   sampler = ClockSampler(local)
+  sampler.start()
   for _ in range(args.warmup):
     step()
   dist.barrier()
   torch.cuda.synchronize()
-  sampler.start()
+  sampler.mark()
   ms = max_over_ranks(timed_steps(step, args.steps, 0, barrier=dist.barrier))
   clocks = sampler.stop()
   kernel.check_errors()
