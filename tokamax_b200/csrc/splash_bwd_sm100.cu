@@ -243,12 +243,14 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       tma_prefetch_desc(&tm_do);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      mbar_arrive_expect_tx(&bars->stat_full[0], kTileBytes);
+      // tiles are two 64-column halves; with at most 64 real columns the second is never read
+      const bool qk2 = p.d_qk > 64, v2 = p.d_v > 64;
+      mbar_arrive_expect_tx(&bars->stat_full[0], qk2 ? kTileBytes : kHalfBytes);
       tma_load_4d(q_smem, &tm_q, &bars->stat_full[0], 0, q_tile * kTile, head, batch);
-      tma_load_4d(q_smem + kHalfBytes, &tm_q, &bars->stat_full[0], 64, q_tile * kTile, head, batch);
-      mbar_arrive_expect_tx(&bars->stat_full[1], kTileBytes);
+      if (qk2) tma_load_4d(q_smem + kHalfBytes, &tm_q, &bars->stat_full[0], 64, q_tile * kTile, head, batch);
+      mbar_arrive_expect_tx(&bars->stat_full[1], v2 ? kTileBytes : kHalfBytes);
       tma_load_4d(do_smem, &tm_do, &bars->stat_full[1], 0, q_tile * kTile, head, batch);
-      tma_load_4d(do_smem + kHalfBytes, &tm_do, &bars->stat_full[1], 64, q_tile * kTile, head, batch);
+      if (v2) tma_load_4d(do_smem + kHalfBytes, &tm_do, &bars->stat_full[1], 64, q_tile * kTile, head, batch);
       uint32_t it = 0;
       bool ok = true;
       for (int e = ebeg; e < eend && ok; ++e) {
@@ -259,16 +261,18 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           if (!ok) break;
           uint8_t* dst = ring + s * kTileBytes;
           const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
-          mbar_arrive_expect_tx(&bars->ring_full[s], kTileBytes);
+          const bool two = kv == 0 ? qk2 : v2;
+          mbar_arrive_expect_tx(&bars->ring_full[s], two ? kTileBytes : kHalfBytes);
           tma_load_4d(dst, tm, &bars->ring_full[s], 0, col * kTile, kv_head, batch);
-          tma_load_4d(dst + kHalfBytes, tm, &bars->ring_full[s], 64, col * kTile, kv_head, batch);
+          if (two) tma_load_4d(dst + kHalfBytes, tm, &bars->ring_full[s], 64, col * kTile, kv_head, batch);
         }
       }
     }
   } else if (warp == 9) {
     if (lane == 0 && n_ent > 0) {
       constexpr uint32_t idesc_kk = make_idesc_bf16(kTile, kTile, false, false);
-      constexpr uint32_t idesc_mn = make_idesc_bf16(kTile, kHeadDim, false, true);
+      // N of dQ += dS K: dq's columns — 128, or 64 when q / k have at most 64
+      const uint32_t idesc_mn = make_idesc_bf16(kTile, p.d_qk <= 64 ? 64 : kHeadDim, false, true);
       const uint32_t q_addr = smem_u32(q_smem), do_addr = smem_u32(do_smem), ring_addr = smem_u32(ring);
       const uint32_t t_dp = tmem + 2 * kTile, t_dq = tmem + 3 * kTile;
       auto ss_kmajor = [&](uint32_t d, uint32_t a0, uint32_t b0, int nk) {
@@ -638,12 +642,14 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
+        const int last = p.d_qk <= 64 ? 1 : 3;  // 32-column chunks beyond dq's columns hold nothing
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
+          if (c > last) break;
           uint32_t v[32];
           tmem_ld32(t_dq + c * 32, v);
           tmem_ld_wait();
-          if (c == 3) {
+          if (c == last) {
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->dq_free);
@@ -662,12 +668,14 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       tma_prefetch_desc(&tm_do);
       tma_prefetch_desc(&tm_k);
       tma_prefetch_desc(&tm_v);
-      mbar_arrive_expect_tx(&bars->stat_full[0], kTileBytes);
+      // tiles are two 64-column halves; with at most 64 real columns the second is never read
+      const bool qk2 = p.d_qk > 64, v2 = p.d_v > 64;
+      mbar_arrive_expect_tx(&bars->stat_full[0], qk2 ? kTileBytes : kHalfBytes);
       tma_load_4d(k_smem, &tm_k, &bars->stat_full[0], 0, kv_tile * kTile, kv_head, batch);
-      tma_load_4d(k_smem + kHalfBytes, &tm_k, &bars->stat_full[0], 64, kv_tile * kTile, kv_head, batch);
-      mbar_arrive_expect_tx(&bars->stat_full[1], kTileBytes);
+      if (qk2) tma_load_4d(k_smem + kHalfBytes, &tm_k, &bars->stat_full[0], 64, kv_tile * kTile, kv_head, batch);
+      mbar_arrive_expect_tx(&bars->stat_full[1], v2 ? kTileBytes : kHalfBytes);
       tma_load_4d(v_smem, &tm_v, &bars->stat_full[1], 0, kv_tile * kTile, kv_head, batch);
-      tma_load_4d(v_smem + kHalfBytes, &tm_v, &bars->stat_full[1], 64, kv_tile * kTile, kv_head, batch);
+      if (v2) tma_load_4d(v_smem + kHalfBytes, &tm_v, &bars->stat_full[1], 64, kv_tile * kTile, kv_head, batch);
       uint32_t it = 0;
       bool ok = true;
       for (int g = 0; g < group && ok; ++g) {
@@ -681,9 +689,11 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             if (!ok) break;
             uint8_t* dst = ring + s * kTileBytes;
             const CUtensorMap* tm = which == 0 ? &tm_q : &tm_do;
-            mbar_arrive_expect_tx(&bars->ring_full[s], which == 0 ? kTileBytes + 2 * kTile * 4 : kTileBytes);
+            const bool two = which == 0 ? qk2 : v2;
+            const uint32_t tile_bytes = two ? kTileBytes : kHalfBytes;
+            mbar_arrive_expect_tx(&bars->ring_full[s], which == 0 ? tile_bytes + 2 * kTile * 4 : tile_bytes);
             tma_load_4d(dst, tm, &bars->ring_full[s], 0, qt * kTile, head, batch);
-            tma_load_4d(dst + kHalfBytes, tm, &bars->ring_full[s], 64, qt * kTile, head, batch);
+            if (two) tma_load_4d(dst + kHalfBytes, tm, &bars->ring_full[s], 64, qt * kTile, head, batch);
             if (which == 0) {  // the step's statistics ride on the Q slot's barrier
               float* sdst = stats + (s / 2) * 2 * kTile;
               bulk_load(sdst, p.nlse2 + stat_base + (int64_t)qt * kTile, kTile * 4, &bars->ring_full[s]);
@@ -696,7 +706,9 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   } else if (warp == kDkvMmaWarp) {
     if (lane == 0 && n_steps > 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(kTile, kTile, false, false);
-      constexpr uint32_t idesc_acc = make_idesc_bf16(kTile, kHeadDim, false, true);
+      // N of the accumulating MMAs = the gradient's columns: 128, or 64 when the tensor has at most 64
+      const uint32_t idesc_dv = make_idesc_bf16(kTile, p.d_v <= 64 ? 64 : kHeadDim, false, true);
+      const uint32_t idesc_dk = make_idesc_bf16(kTile, p.d_qk <= 64 ? 64 : kHeadDim, false, true);
       const uint32_t k_addr = smem_u32(k_smem), v_addr = smem_u32(v_smem), ds_addr = smem_u32(ds_smem);
       const uint32_t ring_addr = smem_u32(ring);
       const uint32_t t_st = tmem, t_dpt = tmem + kTile, t_dk = tmem + 2 * kTile, t_dv = tmem + 3 * kTile;
@@ -718,7 +730,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       const SmemDesc k_desc = make_smem_desc_sw128(k_addr, 16, 1024), v_desc = make_smem_desc_sw128(v_addr, 16, 1024);
       const SmemDesc ds_desc = make_smem_desc_sw128(ds_addr, 16, 1024);
       // fused form: the same two tiles seen MN-major (rows are the MMA's K dimension)
-      constexpr uint32_t idesc_dq = make_idesc_bf16(kTile, kHeadDim, true, true);
+      const uint32_t idesc_dq = make_idesc_bf16(kTile, p.d_qk <= 64 ? 64 : kHeadDim, true, true);
       const SmemDesc ds_mn_desc = make_smem_desc_sw128(ds_addr, kHalfBytes, 1024);
       const SmemDesc k_mn_desc = make_smem_desc_sw128(k_addr, kHalfBytes, 1024);
       bool ok = mbar_wait(&bars->stat_full[0], 0, ab, 0x3200u) && mbar_wait(&bars->stat_full[1], 0, ab, 0x3201u);
@@ -744,7 +756,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         const SmemDesc do_mn = make_smem_desc_sw128(do_slot, kHalfBytes, 1024);
 #pragma unroll
         for (int k = 0; k < 8; ++k)
-          umma_ts(t_dv, t_st + (k >> 1) * 32 + (k & 1) * 8, desc_at(do_mn, k * 2048), idesc_acc,
+          umma_ts(t_dv, t_st + (k >> 1) * 32 + (k & 1) * 8, desc_at(do_mn, k * 2048), idesc_dv,
                   (n > 0 || k > 0) ? 1u : 0u);
         if (more) {
           ok = ring_wait(2 * (n + 1), 0x3240u);
@@ -771,7 +783,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-          umma_ss(t_dk, desc_at(ds_desc, off), desc_at(q_mn, k * 2048), idesc_acc, (n > 0 || k > 0) ? 1u : 0u);
+          umma_ss(t_dk, desc_at(ds_desc, off), desc_at(q_mn, k * 2048), idesc_dk, (n > 0 || k > 0) ? 1u : 0u);
         }
         tc_commit(&bars->ds_free);
         tc_commit(&bars->ring_empty[(2 * n) % kBwdStages]);

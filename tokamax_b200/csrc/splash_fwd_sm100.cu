@@ -56,6 +56,7 @@ struct FwdParams {
   int64_t o_sb, o_sh, o_ss;
   int d_v;  // columns of v / o (<= 128; the tile's remaining columns are zeros and are not stored)
   int nk_qk;  // K = 16 slices of q k^T that hold real columns: ceil(d_qk / 16); the rest are zeros and are skipped
+  int d_qk;   // columns of q / k: at most 64 -> the second 64-column half of their tiles is never loaded or read
   float* lse;
   float* maxl;
   const int32_t* q_seg;
@@ -177,10 +178,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int i = 0; i < 2; ++i) {
         if (qt0 + i < p.n_q_tiles) {
           uint8_t* dst = q_smem + i * kTB;
-          mbar_arrive_expect_tx(&bars->q_full[i], kTB);
+          const bool two = !kFp8 && p.d_qk > 64;  // bf16 tiles are two 64-column halves
+          mbar_arrive_expect_tx(&bars->q_full[i], (kFp8 || two) ? kTB : kHalfBytes);
           tma_load_4d(dst, &tm_q, &bars->q_full[i], 0, (qt0 + i) * kTile, head, batch);
-          if constexpr (!kFp8)
-            tma_load_4d(dst + kHalfBytes, &tm_q, &bars->q_full[i], 64, (qt0 + i) * kTile, head, batch);
+          if (two) tma_load_4d(dst + kHalfBytes, &tm_q, &bars->q_full[i], 64, (qt0 + i) * kTile, head, batch);
         }
       }
       uint32_t it = 0;
@@ -194,10 +195,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (!ok) break;
           uint8_t* dst = kv_smem + s * kTB;
           const CUtensorMap* tm = kv == 0 ? &tm_k : &tm_v;
-          mbar_arrive_expect_tx(&bars->kv_full[s], kTB);
+          const bool two = !kFp8 && (kv == 0 ? p.d_qk : p.d_v) > 64;
+          mbar_arrive_expect_tx(&bars->kv_full[s], (kFp8 || two) ? kTB : kHalfBytes);
           tma_load_4d(dst, tm, &bars->kv_full[s], 0, col * kTile, kv_head, batch);
-          if constexpr (!kFp8)
-            tma_load_4d(dst + kHalfBytes, tm, &bars->kv_full[s], 64, col * kTile, kv_head, batch);
+          if (two) tma_load_4d(dst + kHalfBytes, tm, &bars->kv_full[s], 64, col * kTile, kv_head, batch);
         }
       }
     }
@@ -206,8 +207,11 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     if (lane == 0) {
       constexpr uint32_t idesc_qk =
           kFp8 ? make_idesc_e4m3(kTile, kTile, false, false) : make_idesc_bf16(kTile, kTile, false, false);
-      constexpr uint32_t idesc_pv = kFp8 ? make_idesc_e4m3(kTile, kHeadDim, false, true)
-                                         : make_idesc_bf16(kTile, kHeadDim, false, true);
+      // N of p v: the output's columns — 128, or 64 when v has at most 64 (half the MMA work; the
+      // V tile's second half is then neither loaded nor read)
+      const int n_pv = (!kFp8 && p.d_v <= 64) ? 64 : kHeadDim;
+      const uint32_t idesc_pv = kFp8 ? make_idesc_e4m3(kTile, kHeadDim, false, true)
+                                     : make_idesc_bf16(kTile, n_pv, false, true);
       const uint32_t q_addr = smem_u32(q_smem);
       const uint32_t kv_addr = smem_u32(kv_smem);
       bool ok = true;
@@ -635,6 +639,7 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   p.o_ss = a.o.stride[2];
   p.d_v = (int)Dv;
   p.nk_qk = (int)((D + 15) / 16);
+  p.d_qk = (int)D;
   p.lse = a.logsumexp;
   p.maxl = a.max_logits;
   p.q_seg = a.q_segment_ids;
