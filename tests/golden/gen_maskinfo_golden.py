@@ -1,8 +1,8 @@
 """Generates tests/golden/maskinfo_golden.npz by running the REFERENCE's own MaskInfo builder.
 
-Run in a checkout where the reference tree is present:
+Run where a checkout of the reference is present, pointing SPLASH_REFERENCE_ROOT at it:
 
-    python tests/golden/gen_maskinfo_golden.py
+    SPLASH_REFERENCE_ROOT=<path to primatrix/tokamax> python tests/golden/gen_maskinfo_golden.py
 
 For every case of maskinfo_cases.CASES the reference's ``process_mask`` and ``process_mask_dkv``
 (loaded unmodified through oracle/ref_loader.py) are called; each MaskInfo field is stored either
