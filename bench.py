@@ -222,7 +222,7 @@ def timed_steps(step_fn, steps: int, warmup: int, barrier=None) -> float:
 
 
 def pinned_copy_gbs(device, nbytes: int = 256 << 20) -> dict:
-  """Standalone host<->device copy rates of this box from pinned memory (GB/s), for reading `e2e`:
+  """Standalone host<->device copy rates of the machine from pinned memory (GB/s), for reading `e2e`:
   a slow end-to-end number on a fast kernel is the host link, not the pipeline."""
   host = torch.empty(nbytes, dtype=torch.uint8).pin_memory()
   dev_buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
