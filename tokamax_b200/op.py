@@ -26,6 +26,7 @@ from tokamax_b200 import splash_attention_kernel as splash
 from tokamax_b200 import splash_attention_mask as mask_lib
 
 AUTO = "auto"
+_LIVE_KERNELS: list = []
 
 
 @functools.lru_cache(maxsize=32)
@@ -45,8 +46,11 @@ def _kernel_for(kind: str, t: int, s: int, window: tuple | None, dense_key: byte
   config = None
   if soft_cap is not None:
     config = dataclasses.replace(splash.SplashConfig.get_default(), attn_logits_soft_cap=soft_cap)
-  return splash.make_splash_mha(mask, q_seq_shards=1, save_residuals=True, config=config,
-                                mask_value=float(np.finfo(np.float32).min), downcast_smem_data=False)
+  kernel = splash.make_splash_mha(mask, q_seq_shards=1, save_residuals=True, config=config,
+                                  mask_value=float(np.finfo(np.float32).min), downcast_smem_data=False)
+  _LIVE_KERNELS.append(kernel)
+  del _LIVE_KERNELS[:-64]  # the cache above holds 32; keep the list bounded the same way
+  return kernel
 
 
 class CudaSm100SplashAttention:
@@ -142,6 +146,15 @@ class CudaSm100SplashAttention:
       shape = tuple(batch) + (n, t)
       return out, (res["max_logits"].reshape(shape), res["logsumexp"].reshape(shape))
     return out
+
+
+def check_errors() -> None:
+  """Raises if any kernel object this module has built for static masks reported a device-side
+  fault (a bounded wait that ran out); see ``SplashAttentionKernel.check_errors``.  Kernel objects
+  for masks that are device tensors are built per call and are not tracked here."""
+  # functools.lru_cache keeps no public view of its values: the kernels register themselves
+  for kernel in list(_LIVE_KERNELS):
+    kernel.check_errors()
 
 
 IMPLEMENTATIONS: dict[str, Callable[..., Any]] = {"cuda_sm100": CudaSm100SplashAttention()}

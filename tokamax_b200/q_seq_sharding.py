@@ -64,3 +64,9 @@ class QSeqShardedSplashAttention:
     k = _SumGradOverGroup.apply(k, self.group)
     v = _SumGradOverGroup.apply(v, self.group)
     return self.attention(q, k, v, segment_ids, logits_scale=logits_scale, q_shard=rank)
+
+  def check_errors(self) -> None:
+    """Raises if the wrapped kernel reported a device-side fault (SplashAttentionKernel.check_errors)."""
+    check = getattr(self.attention, "check_errors", None)
+    if check is not None:
+      check()

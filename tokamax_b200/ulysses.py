@@ -285,6 +285,12 @@ class UlyssesSplashAttention:
     out = head_to_seq(o_h, self.group, engine, tags[3])
     return out.clone() if engine is not None else out  # the caller's tensor must outlive the buffer's next use
 
+  def check_errors(self) -> None:
+    """Raises if the wrapped kernel reported a device-side fault (SplashAttentionKernel.check_errors)."""
+    check = getattr(self.attention, "check_errors", None)
+    if check is not None:
+      check()
+
   def _gather_seq(self, ids: torch.Tensor) -> torch.Tensor:
     _, world = _world(self.group)
     if world == 1:
