@@ -332,28 +332,6 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-// 2^x for a pair of values on the FMA pipe instead of the SFU (ex2 runs at 4 per clock per
-// scheduler, which is what bounds the softmax of a 128 x 128 tile; FMAs run at 32).  Round x to the
-// nearest integer n with the 1.5 * 2^23 trick, evaluate 2^f, f = x - n in [-0.5, 0.5], with a
-// degree-3 polynomial (relative error 1.0e-4: fine for weights that are rounded to bf16 right
-// after, too coarse for anything kept in fp32), and add n to the exponent field.  x below -126 is
-// clamped (the result is then ~1e-38, i.e. nothing); x must stay below 127.
-__device__ __forceinline__ float2 ex2_fma2(float2 x) {
-  x.x = fmaxf(x.x, -126.0f);
-  x.y = fmaxf(x.y, -126.0f);
-  const float2 magic = make_float2(12582912.0f, 12582912.0f);
-  const float2 xf = __fadd2_rn(x, magic);
-  const float2 n = __fadd2_rn(xf, make_float2(-12582912.0f, -12582912.0f));
-  const float2 f = __ffma2_rn(n, make_float2(-1.0f, -1.0f), x);
-  float2 p = __ffma2_rn(f, make_float2(0.05500893f, 0.05500893f), make_float2(0.24221095f, 0.24221095f));
-  p = __ffma2_rn(p, f, make_float2(0.6932829f, 0.6932829f));
-  p = __ffma2_rn(p, f, make_float2(1.0f, 1.0f));
-  float2 r;
-  r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(xf.x) << 23));
-  r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(xf.y) << 23));
-  return r;
-}
-
 // tanh to ~1e-6 absolute: (e - 1) / (e + 1) with e = 2^(2 log2(e) y).  tanh.approx.f32 (relative
 // error 2^-11) is too coarse for logits that must hold 1e-3 after being multiplied by a cap of
 // tens.  Saturates cleanly: e = inf -> 1, e = 0 -> -1.

@@ -512,12 +512,7 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             const float2 xa = __ffma2_rn(make_float2(s[g * 32 + 2 * j], s[g * 32 + 2 * j + 1]), c2, nm2);
             const float2 xb = __ffma2_rn(make_float2(s[g * 32 + 2 * j + 2], s[g * 32 + 2 * j + 3]), c2, nm2);
             const float2 pa = make_float2(ex2(xa.x), ex2(xa.y));
-#ifdef SPLASH_FWD_FMA_EXP
-            // a quarter of the exponentials on the FMA pipe (every fourth pair)
-            const float2 pb = (j & 2) ? ex2_fma2(xb) : make_float2(ex2(xb.x), ex2(xb.y));
-#else
             const float2 pb = make_float2(ex2(xb.x), ex2(xb.y));
-#endif
             lsa = __fadd2_rn(lsa, pa);
             lsb = __fadd2_rn(lsb, pb);
             pk[j] = pack_bf16(pa.x, pa.y);
