@@ -855,7 +855,7 @@ def main():
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4", "c5"])
-  ap.add_argument("--exchange", default="nccl", choices=["auto", "nccl", "peer"],
+  ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer"],
                   help="Ulysses exchange: the library's own peer-store kernel over symmetric memory (peer), NCCL "
                        "all_to_all_single (nccl), or peer with nccl as the fallback if symmetric memory cannot be set up (auto)")
   ap.add_argument("--cp", default="ulysses", choices=["ulysses", "ring", "ring_zigzag"],
