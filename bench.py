@@ -137,7 +137,7 @@ class ClockSampler:
 
   FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-            "clocks_event_reasons.sw_power_cap")
+            "clocks_event_reasons.sw_power_cap,clocks.mem,clocks.max.mem")
 
   def __init__(self, index: int):
     self.index = index
@@ -175,7 +175,7 @@ class ClockSampler:
       self.proc.kill()
     if self.thread:
       self.thread.join(timeout=2)
-    sm, smax, reasons = [], [], set()
+    sm, smax, mem, mem_max, power, reasons = [], [], [], [], [], set()
     names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
     t0 = getattr(self, "t0", 0.0)
     for r in self.rows:
@@ -189,12 +189,21 @@ class ClockSampler:
         smax.append(float(r[1]))
       except ValueError:
         continue
+      try:
+        power.append(float(r[2]))
+        mem.append(float(r[7]))
+        mem_max.append(float(r[8]))
+      except (ValueError, IndexError):
+        pass
       for name, val in zip(names, r[3:7]):
         if val.lower().startswith("active"):
           reasons.add(name)
     return {
         "sm_mhz": float(np.median(sm)) if sm else None,
         "sm_max_mhz": float(max(smax)) if smax else None,
+        "mem_mhz": float(np.median(mem)) if mem else None,
+        "mem_max_mhz": float(max(mem_max)) if mem_max else None,
+        "power_w": float(np.median(power)) if power else None,
         "samples": len(sm),
         "reasons": sorted(reasons),
     }
