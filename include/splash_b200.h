@@ -260,13 +260,20 @@ int splash_fwd(const SplashFwdArgs* args, void* cuda_stream);
  * base.q / base.k / base.v are SPLASH_F8E4M3 (element strides multiples of 16), base.o is bf16.
  * Each scale array is fp32 [batch, heads, seq / 128]: the stored values of one 128-token tile of
  * one head times its scale are the real values.  Scales must be finite and >= 0.  Every other
- * field means what it means for splash_fwd; logsumexp / max_logits refer to the dequantised
- * logits. */
+ * field means what it means for splash_fwd (segment ids and sinks included; a soft cap and a fixed
+ * maximum are not taken); logsumexp / max_logits refer to the dequantised logits.
+ * flags: 0 keeps the probabilities in e4m3 for p v (fastest; output within a few percent of the
+ * bf16 forward: relative L2 <= 3e-2); SPLASH_FP8_P_F16 keeps them 16 bits wide — q k^T on the e4m3
+ * tiles, each V tile converted once to f16 in shared memory, p v as a 16-bit MMA — which meets the
+ * bf16 forward's bound (max-abs <= 1e-2). */
+typedef enum SplashFwdFp8Flags { SPLASH_FP8_P_F16 = 1 } SplashFwdFp8Flags;
+
 typedef struct SplashFwdFp8Args {
   SplashFwdArgs base;
   const float* q_scale;             /* [batch, q_heads, q_len / 128] */
   const float* k_scale;             /* [batch, kv_heads, kv_len / 128] */
   const float* v_scale;             /* [batch, kv_heads, kv_len / 128] */
+  uint32_t flags;                   /* SplashFwdFp8Flags */
 } SplashFwdFp8Args;
 
 int splash_fwd_fp8(const SplashFwdFp8Args* args, void* cuda_stream);

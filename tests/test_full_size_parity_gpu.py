@@ -135,15 +135,16 @@ def test_long_context_causal_row_blocks():
     assert _rel(q.grad[0, head, rs], rdq[0]) <= GRAD_REL
 
 
-def test_fp8_prefill_full_size_last_rows():
+@pytest.mark.parametrize("p_format", ["e4m3", "f16"])
+def test_fp8_prefill_full_size_last_rows(p_format):
   """B=2, S=32768, Hq=32, Hkv=8, causal, e4m3 inputs with per-128-token scales, forward only.  The
   last 2048 query rows of one kv-head group against the oracle on the dequantised tensors, at the
-  bounds tests/test_fp8_gpu.py states for this variant."""
+  bounds tests/test_fp8_gpu.py states for each variant (probabilities in e4m3 / kept 16 bits wide)."""
   b, hq, hkv, s, rows = 2, 32, 8, 32768, 2048
   q, k, v, _ = _device_inputs(5000, b, hq, hkv, s)
   qq, kq, vq = (fp8.quantize_e4m3(t) for t in (q, k, v))
   kernel = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1)
-  o, res = fp8.splash_fwd_fp8(kernel, qq, kq, vq, logits_scale=SCALE, save_residuals=True)
+  o, res = fp8.splash_fwd_fp8(kernel, qq, kq, vq, logits_scale=SCALE, save_residuals=True, p_format=p_format)
   kernel.check_errors()
   bi, kv_head = 1, 6
   group = hq // hkv
@@ -152,9 +153,12 @@ def test_fp8_prefill_full_size_last_rows():
   deq = lambda t, hs: fp8.dequantize_e4m3(fp8.Fp8Tensor(t.data[bi:bi + 1, hs], t.scale[bi:bi + 1, hs]), torch.float32)[0].cpu()
   qe, ke, ve = deq(qq, heads)[:, rs], deq(kq, slice(kv_head, kv_head + 1)), deq(vq, slice(kv_head, kv_head + 1))
   dense = np.arange(s - rows, s)[:, None] >= np.arange(s)[None, :]
-  _, lse, mx = attention_ref.attention_reference(qe, ke, ve, dense, scale=SCALE)
+  ref_exact, lse, mx = attention_ref.attention_reference(qe, ke, ve, dense, scale=SCALE)
   assert (res["logsumexp"][bi, heads, rs].cpu() - lse).abs().max().item() <= 1e-3
   assert (res["max_logits"][bi, heads, rs].cpu() - mx).abs().max().item() <= 1e-3
+  if p_format == "f16":
+    assert (o[bi, heads, rs].float().cpu() - ref_exact).abs().max().item() <= O_ATOL
+    return
   ref, _, _ = attention_ref.attention_reference(*(x.to(torch.bfloat16) for x in (qe, ke, ve)), dense, scale=SCALE)
   err = o[bi, heads, rs].float().cpu() - ref
   assert (err.norm() / ref.norm()).item() <= 3e-2

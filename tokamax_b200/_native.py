@@ -144,6 +144,7 @@ class SplashFwdFp8Args(C.Structure):
       ("q_scale", C.c_void_p),
       ("k_scale", C.c_void_p),
       ("v_scale", C.c_void_p),
+      ("flags", C.c_uint32),
   ]
 
 
@@ -170,6 +171,7 @@ class SplashBwdArgs(C.Structure):
 
 
 BWD_FUSED_DQ = 1  # SplashBwdFlags.SPLASH_BWD_FUSED_DQ
+FP8_P_F16 = 1  # SplashFwdFp8Flags.SPLASH_FP8_P_F16
 
 
 class SplashExchangeArgs(C.Structure):

@@ -92,14 +92,16 @@ struct FwdBarriers {
   uint64_t s_full[2];
   uint64_t p_full[2];
   uint64_t o_done[2];
+  uint64_t vc_full[2];   // e4m3 with f16 P: a V tile has been converted to f16
+  uint64_t vc_empty[2];  //                  the p v MMAs that read it have completed
   uint32_t tmem_base;
   uint32_t abort_flag;
   uint32_t early_exit;
 };
 
-constexpr int fwd_smem_bytes(bool fp8) {
-  return (2 + kFwdStages) * (fp8 ? kFp8TileBytes : kTileBytes) + 1024 /*barriers*/ +
-         1024 /*alignment slack*/;
+constexpr int fwd_smem_bytes(bool fp8, bool p16 = false) {
+  return (2 + kFwdStages) * (fp8 ? kFp8TileBytes : kTileBytes) + (p16 ? 2 * kTileBytes : 0) /*f16 V tiles*/ +
+         1024 /*barriers*/ + 1024 /*alignment slack*/;
 }
 
 __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float d) {
@@ -113,7 +115,28 @@ __device__ __forceinline__ uint32_t pack_e4m3x4(float a, float b, float c, float
   return r;
 }
 
-template <bool kFp8, bool kSoftCap>
+__device__ __forceinline__ uint32_t pack_f16(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// four e4m3 values (one 32-bit word, lowest byte first) -> four f16 values, exactly
+__device__ __forceinline__ void e4m3x4_to_f16x4(uint32_t in, uint32_t& out01, uint32_t& out23) {
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "mov.b32 {lo, hi}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, lo;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %1, hi;\n\t}\n"
+      : "=r"(out01), "=r"(out23)
+      : "r"(in));
+}
+
+// kFp8: e4m3 q / k / v with one scale per 128-token tile.  kP16 (with kFp8): the probabilities stay
+// 16 bits wide — q k^T runs on the e4m3 tiles as they are, each V tile is converted once to f16 in
+// shared memory (exact: e4m3 values are f16 values) by the two otherwise idle warps, and p v runs as
+// an f16 MMA.  That variant meets the bf16 kernel's output bound; the all-e4m3 one does not (P
+// rounded to 3 mantissa bits) but spends half the tensor time on p v.
+template <bool kFp8, bool kSoftCap, bool kP16 = false>
 __global__ void __launch_bounds__(kFwdThreads, 1)
 splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                   const __grid_constant__ CUtensorMap tm_v, const FwdParams p) {
@@ -122,8 +145,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* q_smem = smem;                                  // 2 tiles
+  static_assert(!kP16 || kFp8, "the f16-P variant is a variant of the e4m3 forward");
   uint8_t* kv_smem = smem + 2 * kTB;                       // ring
-  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(smem + (2 + kFwdStages) * kTB);
+  uint8_t* vc_smem = smem + (2 + kFwdStages) * kTB;        // kP16: two f16 images of V tiles
+  FwdBarriers* bars = reinterpret_cast<FwdBarriers*>(smem + (2 + kFwdStages) * kTB + (kP16 ? 2 * kTileBytes : 0));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -145,10 +170,14 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       mbar_init(&bars->s_full[i], 1);
       mbar_init(&bars->p_full[i], 4);  // one arrival per softmax warp
       mbar_init(&bars->o_done[i], 1);
+      mbar_init(&bars->vc_full[i], 2);   // one arrival per converting warp
+      mbar_init(&bars->vc_empty[i], 1);
     }
     for (int s = 0; s < kFwdStages; ++s) {
       mbar_init(&bars->kv_full[s], 1);
-      mbar_init(&bars->kv_empty[s], 1);
+      // K tiles sit in the even slots and are released by the MMAs that read them; V tiles sit in the
+      // odd slots and, in the f16-P variant, are released by the two warps that convert them
+      mbar_init(&bars->kv_empty[s], (kP16 && (s & 1)) ? 2 : 1);
     }
     mbar_fence_init();
   }
@@ -168,7 +197,43 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
   if (warp >= 8) {
    setmaxnreg_dec<kIssueRegs>();
    if (warp >= 10) {
-    // idle warps: only there to complete the third warpgroup for the register hand-over
+    // Without kP16 these two warps are idle: only there to complete the third warpgroup for the
+    // register hand-over.  With it they turn each e4m3 V tile (128 kv rows x 128 bytes, 16-byte
+    // chunks swizzled by row & 7 as TMA wrote them) into the f16 tile the p v MMA reads MN-major:
+    // two halves of 64 columns, rows of 128 bytes, the same swizzle — the layout a bf16 V tile has.
+    if constexpr (kP16) {
+      static_assert(kFwdStages % 2 == 0, "V tiles must keep to the odd ring slots");
+      const int t = (warp - 10) * 32 + lane;
+      uint32_t n = 0;
+      for (int e = ebeg; e < eend; ++e, ++n) {
+        const uint32_t it = 2 * n + 1, s = it % kFwdStages, j = n & 1u;
+        bool ok = mbar_wait(&bars->kv_full[s], (it / kFwdStages) & 1u, ab, 0x600u + s);
+        if (ok) ok = mbar_wait(&bars->vc_empty[j], ((n >> 1) & 1u) ^ 1u, ab, 0x610u + j);
+        if (!__all_sync(0xffffffffu, ok)) break;
+        const uint8_t* raw = kv_smem + s * kTB;
+        uint8_t* dst = vc_smem + j * kTileBytes;
+#pragma unroll 4
+        for (int idx = t; idx < kTile * 8; idx += 64) {
+          const int row = idx >> 3, c = idx & 7, x = row & 7;
+          const uint4 in = *reinterpret_cast<const uint4*>(raw + row * 128 + ((c ^ x) << 4));
+          uint4 lo, hi;
+          e4m3x4_to_f16x4(in.x, lo.x, lo.y);
+          e4m3x4_to_f16x4(in.y, lo.z, lo.w);
+          e4m3x4_to_f16x4(in.z, hi.x, hi.y);
+          e4m3x4_to_f16x4(in.w, hi.z, hi.w);
+          uint8_t* base = dst + (c >> 2) * kHalfBytes + row * 128;
+          const int c2 = (c & 3) * 2;
+          *reinterpret_cast<uint4*>(base + ((c2 ^ x) << 4)) = lo;
+          *reinterpret_cast<uint4*>(base + (((c2 + 1) ^ x) << 4)) = hi;
+        }
+        fence_proxy_async_smem();  // the MMA reads shared memory through the async proxy
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(&bars->vc_full[j]);
+          mbar_arrive(&bars->kv_empty[s]);
+        }
+      }
+    }
    } else if (warp == 8) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
@@ -210,9 +275,11 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // N of p v: the output's columns — 128, or 64 when v has at most 64 (half the MMA work; the
       // V tile's second half is then neither loaded nor read)
       const int n_pv = (!kFp8 && p.d_v <= 64) ? 64 : kHeadDim;
+      // (kind::f16 with format code 0 for A and B is f16 x f16: the same bits as the e4m3 descriptor)
       const uint32_t idesc_pv = kFp8 ? make_idesc_e4m3(kTile, kHeadDim, false, true)
                                      : make_idesc_bf16(kTile, n_pv, false, true);
       const uint32_t q_addr = smem_u32(q_smem);
+      const uint32_t vc_addr = smem_u32(vc_smem);
       const uint32_t kv_addr = smem_u32(kv_smem);
       bool ok = true;
       for (int i = 0; i < 2 && ok; ++i)
@@ -245,8 +312,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // K=16 slices 2 KiB apart; e4m3: the 128 columns fit one 128-byte row, K=32 slices 4 KiB
       // apart, P packed four values per TMEM column.
       auto issue_pv = [&](int i, uint32_t slot, bool acc) {
-        const uint32_t b0 = kv_addr + slot * kTB;
-        if constexpr (kFp8) {
+        const uint32_t b0 = kP16 ? vc_addr + slot * kTileBytes : kv_addr + slot * kTB;
+        if constexpr (kFp8 && !kP16) {
           const SmemDesc db = make_smem_desc_sw128(b0, 16, 1024);
 #pragma unroll
           for (int k = 0; k < 4; ++k)
@@ -281,7 +348,11 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           if (has_next) nxt = entries[ebeg + n + 1];
           const uint32_t itv = 2 * n + 1, itk = 2 * n + 2;
           const uint32_t vslot = itv % kFwdStages, kslot = itk % kFwdStages;
-          ok = mbar_wait(&bars->kv_full[vslot], (itv / kFwdStages) & 1u, ab, 0x310u + vslot);
+          const uint32_t vc = n & 1u;  // kP16: which f16 image holds this step's V
+          if constexpr (kP16)
+            ok = mbar_wait(&bars->vc_full[vc], (n >> 1) & 1u, ab, 0x340u + vc);
+          else
+            ok = mbar_wait(&bars->kv_full[vslot], (itv / kFwdStages) & 1u, ab, 0x310u + vslot);
           if (ok && has_next)
             ok = mbar_wait(&bars->kv_full[kslot], (itk / kFwdStages) & 1u, ab, 0x320u + kslot);
           if (!ok) break;
@@ -292,10 +363,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
               if (!ok) break;
               ++pcnt[i];
               mma_issue_fence();
-              issue_pv(i, vslot, started[i]);
+              issue_pv(i, kP16 ? vc : vslot, started[i]);
               started[i] = true;
             }
-            if (i == 1) tc_commit(&bars->kv_empty[vslot]);
+            if (i == 1) tc_commit(kP16 ? &bars->vc_empty[vc] : &bars->kv_empty[vslot]);
             if (has_next && ((nxt.y >> (2 * i)) & 3)) issue_qk(i, kslot);
           }
           if (ok && has_next) tc_commit(&bars->kv_empty[kslot]);
@@ -339,7 +410,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int off = 16; off > 0; off >>= 1) vm = fmaxf(vm, __shfl_xor_sync(0xffffffffu, vm, off));
       v_ref = vm > 0.f ? vm : 1.f;
     }
-    constexpr float kThreshold = kFp8 ? kFp8RescaleThreshold : kRescaleThreshold;
+    // e4m3 P must stay below 448; f16 P (times 2^6) below 65504; bf16 P has the range of fp32
+    constexpr float kThreshold = (kFp8 && !kP16) ? kFp8RescaleThreshold : kRescaleThreshold;
 
     float m_used = -INFINITY;  // scaled (log2) units
     float m_true = kMaskedLogit;
@@ -480,7 +552,26 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       }
 
       float ls0 = 0.f, ls1 = 0.f;
-      if constexpr (kFp8) {
+      if constexpr (kP16) {
+        // as the e4m3 branch below, but P stays 16 bits wide (f16: 11 significant bits; the factor
+        // 2^6 keeps the small weights out of the subnormals, 2^(6+8) is the largest value written)
+        const float r = fmaxf(__fdividef(vs, v_ref), 5.9604645e-8f);
+        const float m_sub = m_used - kFp8PShift - __log2f(r);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint32_t pk[16];
+#pragma unroll
+          for (int j = 0; j < 16; ++j) {
+            const float p0 = ex2(fmaf(s[g * 32 + 2 * j], c, -m_sub));
+            const float p1 = ex2(fmaf(s[g * 32 + 2 * j + 1], c, -m_sub));
+            ls0 += p0;
+            ls1 += p1;
+            pk[j] = pack_f16(p0, p1);
+          }
+          tmem_st16(t_s + g * 16, pk);
+        }
+        l += (ls0 + ls1) * __fdividef(0.015625f, r);
+      } else if constexpr (kFp8) {
         // P * 2^shift * r with r = v scale / largest v scale in (0, 1]; r is floored so that a
         // tile of zeros (scale 0) still counts in l.
         const float r = fmaxf(__fdividef(vs, v_ref), 5.9604645e-8f);
@@ -588,10 +679,12 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
 // host launcher
 // ------------------------------------------------------------------------------------------
 static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const float* k_scale,
-                             const float* v_scale, bool fp8, cudaStream_t stream) {
+                             const float* v_scale, bool fp8, bool p16, cudaStream_t stream) {
   int st;
   const bool soft_cap = a.soft_cap != 0.f;
   if (soft_cap && (fp8 || !(a.soft_cap > 0.f))) return fp8 ? SPLASH_ERR_UNSUPPORTED : SPLASH_ERR_INVALID_ARGUMENT;
+  // a fixed maximum below the true one would push the narrow P formats of the e4m3 forward out of range
+  if (fp8 && a.max_logit_value != nullptr) return SPLASH_ERR_UNSUPPORTED;
   if (fp8) {
     if ((st = check_e4m3_tensor(a.q)) || (st = check_e4m3_tensor(a.k)) || (st = check_e4m3_tensor(a.v)))
       return st;
@@ -680,13 +773,13 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   dim3 grid((unsigned)(p.n_rows * p.n_groups), 1u, 1u);
   // The dynamic shared-memory attribute is per device and per kernel variant: set once, under a
   // lock (calls may come from several threads).
-  const int variant = fp8 ? 1 : (soft_cap ? 2 : 0);
-  const int smem = fp8 ? fwd_smem_bytes(true) : fwd_smem_bytes(false);
-  const void* fn = fp8 ? (const void*)splash_fwd_kernel<true, false>
+  const int variant = fp8 ? (p16 ? 3 : 1) : (soft_cap ? 2 : 0);
+  const int smem = fwd_smem_bytes(fp8, fp8 && p16);
+  const void* fn = fp8 ? (p16 ? (const void*)splash_fwd_kernel<true, false, true> : (const void*)splash_fwd_kernel<true, false>)
                        : (soft_cap ? (const void*)splash_fwd_kernel<false, true> : (const void*)splash_fwd_kernel<false, false>);
   {
     static std::mutex attr_mu;
-    static bool attr_done[64][3] = {};
+    static bool attr_done[64][4] = {};
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return SPLASH_ERR_CUDA;
     std::lock_guard<std::mutex> lock(attr_mu);
@@ -696,7 +789,9 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
       attr_done[dev][variant] = true;
     }
   }
-  if (fp8)
+  if (fp8 && p16)
+    splash_fwd_kernel<true, false, true><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
+  else if (fp8)
     splash_fwd_kernel<true, false><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
   else if (soft_cap)
     splash_fwd_kernel<false, true><<<grid, kFwdThreads, smem, stream>>>(tm_q, tm_k, tm_v, p);
@@ -706,11 +801,12 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
 }
 
 int launch_fwd(const SplashFwdArgs& a, cudaStream_t stream) {
-  return launch_fwd_common(a, nullptr, nullptr, nullptr, false, stream);
+  return launch_fwd_common(a, nullptr, nullptr, nullptr, false, false, stream);
 }
 
 int launch_fwd_fp8(const SplashFwdFp8Args& a, cudaStream_t stream) {
-  return launch_fwd_common(a.base, a.q_scale, a.k_scale, a.v_scale, true, stream);
+  if (a.flags & ~(uint32_t)SPLASH_FP8_P_F16) return SPLASH_ERR_INVALID_ARGUMENT;
+  return launch_fwd_common(a.base, a.q_scale, a.k_scale, a.v_scale, true, (a.flags & SPLASH_FP8_P_F16) != 0, stream);
 }
 
 }  // namespace sb
