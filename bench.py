@@ -599,12 +599,37 @@ def run_single_gpu(args, w, wname, emit=True):
                      "peak_source": sub["roofline"]["peak_source"], "config": sub["config"],
                      "kernel_ms": sub["roofline"].get("kernel_ms")}
       torch.cuda.empty_cache()
+    other["wide_head_dims_forward"] = wide_head_dim_forward(dev)
     line["other_workloads"] = other
   if not args.no_cpu_baseline:
     line["cpu_baseline"] = cpu_baseline(w)
   if emit:
     print(json.dumps(line), flush=True)
   return line
+
+
+def wide_head_dim_forward(dev, steps: int = 5) -> dict:
+  """Forward only at the head dims above 128 the reference's splash microbenchmarks quote —
+  (q k, v) = (192, 128) and (256, 256); causal, batch 1, 32 q heads, 8 kv heads, S = 8192 — in mask-
+  counted TFLOP/s (2 * d_qk + 2 * d_v FLOPs per live pair).  The backward is not built at these sizes."""
+  from tokamax_b200 import splash_attention_kernel as splash
+  from tokamax_b200 import splash_attention_mask as mask_lib
+
+  s, hq, hkv = 8192, 32, 8
+  kernel = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1)
+  peak, _, _ = measured_peaks()
+  out = {}
+  for d_qk, d_v in ((192, 128), (256, 256)):
+    g = torch.Generator(device=dev).manual_seed(7000 + d_qk)
+    q, k, v = (torch.randn(1, h, s, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+               for h, d in ((hq, d_qk), (hkv, d_qk), (hkv, d_v)))
+    with torch.no_grad():
+      ms = timed_steps(lambda: kernel(q, k, v, logits_scale=1 / math.sqrt(d_qk)), steps, 3)
+    flops = hq * (s * (s + 1) // 2) * (2 * d_qk + 2 * d_v)
+    out[f"{d_qk}_{d_v}"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac_of_peak": flops / ms / 1e9 / peak}
+  kernel.check_errors()
+  out["config"] = {"batch": 1, "q_heads": hq, "kv_heads": hkv, "seq": s, "mask": "causal", "pass": "forward"}
+  return out
 
 
 def run_fp8_prefill(args, w, wname, emit=True):

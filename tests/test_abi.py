@@ -69,10 +69,10 @@ def test_forward_rejects_bad_tensors_before_touching_the_gpu():
   for t in (a.q, a.k, a.v, a.o):
     t.data = 4096
     t.dtype = 0
-    for i, s in enumerate((1, 2, 256, 192)):
+    for i, s in enumerate((1, 2, 256, 320)):
       t.size[i] = s
-    t.stride[0], t.stride[1], t.stride[2], t.stride[3] = 2 * 256 * 192, 256 * 192, 192, 1
-  assert lib.splash_fwd(C.byref(a), None) == -2  # head_dim 192: unsupported, not invalid
+    t.stride[0], t.stride[1], t.stride[2], t.stride[3] = 2 * 256 * 320, 256 * 320, 320, 1
+  assert lib.splash_fwd(C.byref(a), None) == -2  # head_dim 320: unsupported, not invalid
   for t in (a.q, a.k, a.v, a.o):
     t.size[3] = 60
   assert lib.splash_fwd(C.byref(a), None) == -1  # head_dim 60: rows are not a multiple of 16 bytes
@@ -82,5 +82,5 @@ def test_forward_rejects_bad_tensors_before_touching_the_gpu():
   a.q.dtype = 1
   assert lib.splash_fwd(C.byref(a), None) == -2  # fp32 inputs
   a.q.dtype = 0
-  a.q.stride[2] = 188
+  a.q.stride[2] = 316
   assert lib.splash_fwd(C.byref(a), None) == -1  # row stride not a multiple of 16 bytes

@@ -339,7 +339,7 @@ def test_unsupported_and_invalid_arguments():
   q = torch.zeros(2, s, D, dtype=torch.bfloat16, device=dev)
   with pytest.raises(NotImplementedError):
     kernel(q.float(), q.float(), q.float())
-  wide = torch.zeros(2, s, 256, dtype=torch.bfloat16, device=dev)
+  wide = torch.zeros(2, s, 320, dtype=torch.bfloat16, device=dev)
   with pytest.raises(NotImplementedError):
     kernel(wide, wide, wide)
   with pytest.raises(ValueError):
@@ -374,6 +374,49 @@ def test_head_dims_below_128_are_read_in_place(d_qk, d_v):
   assert (res["logsumexp"].cpu() - rlse).abs().max().item() <= LSE_ATOL
   assert qd.grad.shape == q.shape and kd.grad.shape == k.shape and vd.grad.shape == v.shape
   assert _rel(qd.grad, rdq) <= GRAD_REL and _rel(kd.grad, rdk) <= GRAD_REL and _rel(vd.grad, rdv) <= GRAD_REL
+
+
+@pytest.mark.parametrize("d_qk,d_v", [(192, 128), (256, 256), (128, 256), (136, 200)])
+@pytest.mark.parametrize("kind", ["causal", "local_segments", "table"])
+def test_head_dims_above_128_forward(d_qk, d_v, kind):
+  """The reference's (192, 128) and (256, 256) head dims (splash_attention_kernel_test.py:233-237)
+  and two ragged ones, forward only: output, logsumexp and max_logits against the oracle; the
+  backward raises."""
+  b, hq, hkv, s = 2, 4, 2, 640  # five q tiles: the last schedule row holds one tile only
+  g = torch.Generator().manual_seed(d_qk * 3 + d_v)
+  mk = lambda h, d: torch.randn(b, h, s, d, generator=g).to(torch.bfloat16)
+  q, k, v = mk(hq, d_qk), mk(hkv, d_qk), mk(hkv, d_v)
+  seg = None
+  sinks = None
+  if kind == "causal":
+    mask = mask_lib.CausalMask((s, s))
+    sinks = torch.tensor([0.3, -0.7, 1.5, 0.0])
+  elif kind == "local_segments":
+    mask = mask_lib.LocalMask((s, s), (200, 50), 0)
+    ids = np.zeros((b, s), np.int32)
+    ids[0, 300:] = 1
+    ids[1, 100:450] = 1
+    ids[1, 450:] = 2
+    seg = (ids, ids)
+  else:
+    mask = mask_lib.make_random_mask((s, s), 0.6, 11) | np.eye(s, dtype=np.bool_)
+  kernel = splash.make_splash_mha(mask, q_seq_shards=1, save_residuals=True)
+  dev = torch.device("cuda:0")
+  qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+  scale = 1 / math.sqrt(d_qk)
+  seg_dev = None if seg is None else splash.SegmentIds(*(torch.from_numpy(x).to(dev) for x in seg))
+  out, res = kernel(qd, kd, vd, seg_dev, None if sinks is None else sinks.to(dev), logits_scale=scale)
+  kernel.check_errors()
+  assert out.shape == (b, hq, s, d_v)
+  dense = _dense(mask)
+  for row in range(b):
+    seg_row = None if seg is None else (seg[0][row], seg[1][row])
+    ro, rlse, rmax = attention_ref.attention_reference(q[row], k[row], v[row], dense, seg_row, scale=scale, sinks=sinks)
+    assert ((out[row].float().cpu() - ro).abs() <= 1e-2 + 4e-3 * ro.abs()).all()
+    assert (res["logsumexp"][row].cpu() - rlse).abs().max().item() <= LSE_ATOL
+    assert (res["max_logits"][row].cpu() - rmax).abs().max().item() <= LSE_ATOL
+  with pytest.raises(NotImplementedError):
+    out.sum().backward()
 
 
 def test_small_head_dim_outputs_stay_inside_their_columns():

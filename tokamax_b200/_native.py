@@ -19,6 +19,7 @@ LIB_PATH = os.path.join(_LIB_DIR, "libsplash_b200.so")
 
 SOURCES = (
     "splash_fwd_sm100.cu",
+    "splash_fwd_wide_sm100.cu",
     "splash_bwd_sm100.cu",
     "splash_host.cu",
     "schedule_builder.cc",

@@ -51,11 +51,11 @@ __device__ __forceinline__ RowInterval mask_fn_interval(const SplashMaskFn& fn, 
 struct CtaWork {
   int row, group;
 };
-__device__ __forceinline__ CtaWork cta_work(const int32_t* row_order, int n_rows, int n_groups,
-                                            int chunk_groups, bool fallback_reversed) {
+__device__ __forceinline__ CtaWork cta_work_at(unsigned block, const int32_t* row_order, int n_rows, int n_groups,
+                                               int chunk_groups, bool fallback_reversed) {
   const unsigned per_chunk = (unsigned)n_rows * (unsigned)chunk_groups;
-  const unsigned chunk = blockIdx.x / per_chunk;
-  const unsigned rem = blockIdx.x - chunk * per_chunk;
+  const unsigned chunk = block / per_chunk;
+  const unsigned rem = block - chunk * per_chunk;
   const unsigned first = chunk * (unsigned)chunk_groups;
   const unsigned here = min((unsigned)chunk_groups, (unsigned)n_groups - first);
   const unsigned pos = rem / here;
@@ -63,6 +63,10 @@ __device__ __forceinline__ CtaWork cta_work(const int32_t* row_order, int n_rows
   w.group = (int)(first + (rem - pos * here));
   w.row = row_order ? row_order[pos] : (fallback_reversed ? n_rows - 1 - (int)pos : (int)pos);
   return w;
+}
+__device__ __forceinline__ CtaWork cta_work(const int32_t* row_order, int n_rows, int n_groups,
+                                            int chunk_groups, bool fallback_reversed) {
+  return cta_work_at(blockIdx.x, row_order, n_rows, n_groups, chunk_groups, fallback_reversed);
 }
 // Groups per chunk so that `bytes_per_group` of streamed operands of one chunk fill about half
 // of a 126 MB L2, in whole multiples of `align` (heads sharing a kv head stay together).

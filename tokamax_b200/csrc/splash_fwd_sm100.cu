@@ -33,57 +33,9 @@
 #include <mutex>
 
 #include "splash_common.cuh"
+#include "splash_fwd_params.cuh"
 
 namespace sb {
-
-constexpr int kFwdStages = 4;
-constexpr int kFwdThreads = 384;  // 3 warpgroups: softmax 0, softmax 1, {TMA, MMA, 2 idle warps}
-constexpr int kSoftmaxRegs = 224;  // setmaxnreg targets: 2*128*224 + 128*56 <= 64K registers
-constexpr int kIssueRegs = 56;
-constexpr float kRescaleThreshold = 8.0f;  // log2 units
-// Lower bound of the running maximum (log2 units).  A row whose entries so far are all masked
-// would otherwise take the scaled masked logit as its maximum and turn its masked entries into
-// exp2(rounding error of a 1e29-sized product); with the floor they stay exactly zero, l stays 0,
-// and a row that never meets a live key ends as zeros with logsumexp = mask_value.
-constexpr float kLogitFloor = -1.0e6f;
-constexpr float kMinScaleLog2 = 1.0e-20f;  // keeps kMaskedLogit * scale far below kLogitFloor
-constexpr float kFp8RescaleThreshold = 2.0f;  // e4m3 P must stay below 448 = 2^8.8
-constexpr float kFp8PShift = 6.0f;            // P is stored as 2^6 * exp2(s - m) * (v scale ratio <= 1)
-constexpr int kFp8TileBytes = kTile * kHeadDim;  // 16 KiB
-
-struct FwdParams {
-  __nv_bfloat16* o;
-  int64_t o_sb, o_sh, o_ss;
-  int d_v;  // columns of v / o (<= 128; the tile's remaining columns are zeros and are not stored)
-  int nk_qk;  // K = 16 slices of q k^T that hold real columns: ceil(d_qk / 16); the rest are zeros and are skipped
-  int d_qk;   // columns of q / k: at most 64 -> the second 64-column half of their tiles is never loaded or read
-  float* lse;
-  float* maxl;
-  const int32_t* q_seg;
-  const int32_t* kv_seg;
-  const int32_t* q_sequence;
-  const int32_t* row_ptr;
-  const int4* entries;
-  const int32_t* row_order;    // launch order of the rows (longest first) or nullptr
-  const int32_t* row_end;      // per batch row [batch, n_rows] or nullptr
-  int64_t entries_per_batch;   // 0: one list shared by all batch rows
-  const int8_t* pmb;
-  int pm_bq, pm_bkv;
-  SplashMaskFn fn;
-  int q_len, kv_len, q_heads, kv_heads, n_q_tiles, n_rows;
-  int n_groups, chunk_groups;  // (batch, q head) pairs; how many of them share a launch chunk
-  float scale, scale_log2, mask_value;
-  uint32_t* err;
-  // e4m3 variant only: one scale per (batch, head, 128-token tile)
-  const float* q_scale;
-  const float* k_scale;
-  const float* v_scale;
-  int n_kv_tiles;
-  const float* sinks;            // [q_heads] or nullptr
-  const float* max_logit_value;  // [q_heads] or nullptr
-  // soft-cap variant: logits = cap * tanh(scale * q k^T / cap)
-  float soft_cap, softcap_a;     // cap; scale / cap
-};
 
 struct FwdBarriers {
   uint64_t q_full[2];
@@ -699,9 +651,12 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   // Head dims: the MMA tile is 128 wide.  bf16 tensors with fewer columns (a multiple of 8, so rows
   // stay 16-byte aligned) are read in place — the TMA boxes reach past the row's end and the part
   // outside the tensor arrives as zeros, which change neither q k^T nor p v — and only the real
-  // columns of the output are stored.  Larger head dims are not built; e4m3 takes 128 only.
+  // columns of the output are stored.  Head dims above 128 (up to 256) go to the forward that works
+  // on two 128-column panels (splash_fwd_wide_sm100.cu); e4m3 takes 128 only.
   const int64_t Dv = a.v.size[3];
-  if (D > kHeadDim || Dv > kHeadDim || (fp8 && (D != kHeadDim || Dv != kHeadDim))) return SPLASH_ERR_UNSUPPORTED;
+  constexpr int64_t kMaxWideDim = 2 * kHeadDim;
+  if (D > kMaxWideDim || Dv > kMaxWideDim || (fp8 && (D != kHeadDim || Dv != kHeadDim))) return SPLASH_ERR_UNSUPPORTED;
+  const bool wide = D > kHeadDim || Dv > kHeadDim;
   if (D % 8 != 0 || Dv % 8 != 0 || a.k.size[3] != D) return SPLASH_ERR_INVALID_ARGUMENT;
   if (a.k.size[0] != B || a.v.size[0] != B || a.o.size[0] != B) return SPLASH_ERR_INVALID_ARGUMENT;
   if (a.v.size[1] != Hkv || a.v.size[2] != Skv || a.o.size[1] != Hq || a.o.size[2] != Sq ||
@@ -768,7 +723,9 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
 
   // The q heads of one kv head stream the same K / V (2 tensors of Skv x 128 elements).
   p.n_groups = (int)(Hq * B);
-  p.chunk_groups = chunk_groups_for(2 * Skv * kHeadDim * (fp8 ? 1 : 2) / (Hq / Hkv), p.n_groups, Hq / Hkv);
+  const int64_t kv_row_bytes = fp8 ? 2 * kHeadDim : 2 * ((D > kHeadDim ? D : kHeadDim) + (Dv > kHeadDim ? Dv : kHeadDim));
+  p.chunk_groups = chunk_groups_for(Skv * kv_row_bytes / (Hq / Hkv), p.n_groups, Hq / Hkv);
+  if (wide) return launch_fwd_wide(tm_q, tm_k, tm_v, p, soft_cap, stream);
   if ((int64_t)p.n_rows * p.n_groups > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
   dim3 grid((unsigned)(p.n_rows * p.n_groups), 1u, 1u);
   // The dynamic shared-memory attribute is per device and per kernel variant: set once, under a

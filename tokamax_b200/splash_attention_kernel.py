@@ -36,6 +36,7 @@ partial = functools.partial
 
 _TILE = 128
 _HEAD_DIM = 128
+_MAX_HEAD_DIM = 256  # forward only above _HEAD_DIM
 
 
 def get_kernel_name(is_mqa: bool, save_residuals: bool, is_segmented: bool, phase: str) -> str:
@@ -345,6 +346,10 @@ class _SplashFunction(torch.autograd.Function):
   @staticmethod
   def backward(ctx, d_o, _dlse, _dmax):
     q, k, v, o, lse, q_seg, kv_seg, sinks = ctx.saved_tensors
+    if q.shape[-1] > _HEAD_DIM or v.shape[-1] > _HEAD_DIM:
+      raise NotImplementedError(
+          f"the backward for head dims above {_HEAD_DIM} is not built on B200 (forward only), got "
+          f"{q.shape[-1]} / {v.shape[-1]}")
     dq, dk, dv, neg_di = splash_backward(ctx.kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale, ctx.shard)
     dsinks = None
     if sinks is not None:
@@ -542,12 +547,13 @@ class SplashAttentionKernel:
     # The MMA tiles are 128 wide.  Smaller head dims (multiples of 8; q / k and v may differ) are
     # read in place: the kernels' TMA boxes reach past the end of a row and get zeros there, which
     # change neither q k^T nor p v, and only the real columns of outputs and gradients are stored.
-    # No copy is made, but the MMAs still run at the full tile width.  Larger ones are not built.
+    # No copy is made.  Head dims above 128, up to 256 (the reference's (192, 128) and (256, 256)),
+    # run a forward that works on two 128-column panels; their backward is not built and raises.
     d_qk, d_v = q.shape[-1], v.shape[-1]
     if k.shape[-1] != d_qk:
       raise ValueError(f"q and k head dims differ: {d_qk} vs {k.shape[-1]}")
-    if d_qk > _HEAD_DIM or d_v > _HEAD_DIM:
-      raise NotImplementedError(f"head dims above {_HEAD_DIM} are not built on B200, got {d_qk} / {d_v}")
+    if d_qk > _MAX_HEAD_DIM or d_v > _MAX_HEAD_DIM:
+      raise NotImplementedError(f"head dims above {_MAX_HEAD_DIM} are not built on B200, got {d_qk} / {d_v}")
     if d_qk % 8 or d_v % 8:
       raise NotImplementedError(f"head dims must be multiples of 8 (16-byte rows), got {d_qk} / {d_v}")
     q_seg = kv_seg = None
