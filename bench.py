@@ -909,7 +909,7 @@ def main():
   ap.add_argument("--steps", type=int, default=30)
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-  ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4", "c5"])
+  ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4", "c5", "wide"])
   ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer"],
                   help="Ulysses exchange: the library's own peer-store kernel over symmetric memory (peer), NCCL "
                        "all_to_all_single (nccl), or peer with nccl as the fallback if symmetric memory cannot be set up (auto)")
@@ -929,6 +929,13 @@ def main():
   wname = args.workload
   if wname == "auto":
     wname = "c2" if world == 1 else "c4"
+  if wname == "wide":  # forward at head dims (192, 128) and (256, 256): a side line, not a headline workload
+    if args.impl != "ours" or world != 1 or not torch.cuda.is_available():
+      raise SystemExit("--workload wide is a single-GPU run of this build's forward")
+    print(json.dumps({"metric": "splash forward TFLOP/s (masked FLOPs), head dims above 128", "unit": "TFLOP/s",
+                      "n_gpus": 1, "steps": args.steps, "dtype": "bf16", "data": "synthetic",
+                      **wide_head_dim_forward(torch.device("cuda", 0), max(args.steps, 1))}), flush=True)
+    return
   w = WORKLOADS[wname]
   if args.impl == "reference":
     run_reference(args, w, wname)
