@@ -378,19 +378,17 @@ def test_head_dims_below_128_are_read_in_place(d_qk, d_v):
 
 @pytest.mark.parametrize("d_qk,d_v", [(192, 128), (256, 256), (128, 256), (136, 200)])
 @pytest.mark.parametrize("kind", ["causal", "local_segments", "table"])
-def test_head_dims_above_128_forward(d_qk, d_v, kind):
+def test_head_dims_above_128(d_qk, d_v, kind):
   """The reference's (192, 128) and (256, 256) head dims (splash_attention_kernel_test.py:233-237)
-  and two ragged ones, forward only: output, logsumexp and max_logits against the oracle; the
-  backward raises."""
-  b, hq, hkv, s = 2, 4, 2, 640  # five q tiles: the last schedule row holds one tile only
+  and two ragged ones, with grouped q heads: output, logsumexp, max_logits and the three gradients
+  against the oracle."""
+  b, hq, hkv, s = 2, 4, 2, 640  # five q tiles: the last schedule row of the forward holds one tile only
   g = torch.Generator().manual_seed(d_qk * 3 + d_v)
   mk = lambda h, d: torch.randn(b, h, s, d, generator=g).to(torch.bfloat16)
-  q, k, v = mk(hq, d_qk), mk(hkv, d_qk), mk(hkv, d_v)
+  q, k, v, do = mk(hq, d_qk), mk(hkv, d_qk), mk(hkv, d_v), mk(hq, d_v)
   seg = None
-  sinks = None
   if kind == "causal":
     mask = mask_lib.CausalMask((s, s))
-    sinks = torch.tensor([0.3, -0.7, 1.5, 0.0])
   elif kind == "local_segments":
     mask = mask_lib.LocalMask((s, s), (200, 50), 0)
     ids = np.zeros((b, s), np.int32)
@@ -405,18 +403,44 @@ def test_head_dims_above_128_forward(d_qk, d_v, kind):
   qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
   scale = 1 / math.sqrt(d_qk)
   seg_dev = None if seg is None else splash.SegmentIds(*(torch.from_numpy(x).to(dev) for x in seg))
-  out, res = kernel(qd, kd, vd, seg_dev, None if sinks is None else sinks.to(dev), logits_scale=scale)
+  out, res = kernel(qd, kd, vd, seg_dev, logits_scale=scale)
+  out.backward(do.to(dev))
   kernel.check_errors()
   assert out.shape == (b, hq, s, d_v)
-  dense = _dense(mask)
-  for row in range(b):
-    seg_row = None if seg is None else (seg[0][row], seg[1][row])
-    ro, rlse, rmax = attention_ref.attention_reference(q[row], k[row], v[row], dense, seg_row, scale=scale, sinks=sinks)
-    assert ((out[row].float().cpu() - ro).abs() <= 1e-2 + 4e-3 * ro.abs()).all()
-    assert (res["logsumexp"][row].cpu() - rlse).abs().max().item() <= LSE_ATOL
-    assert (res["max_logits"][row].cpu() - rmax).abs().max().item() <= LSE_ATOL
-  with pytest.raises(NotImplementedError):
-    out.sum().backward()
+  ro, rlse, rmax, rdq, rdk, rdv = attention_ref.fwd_bwd(q, k, v, do, _dense(mask), seg, scale=scale)
+  assert ((out.float().cpu() - ro).abs() <= 1e-2 + 4e-3 * ro.abs()).all()
+  assert (res["logsumexp"].cpu() - rlse).abs().max().item() <= LSE_ATOL
+  assert (res["max_logits"].cpu() - rmax).abs().max().item() <= LSE_ATOL
+  assert qd.grad.shape == q.shape and kd.grad.shape == k.shape and vd.grad.shape == v.shape
+  assert _rel(vd.grad, rdv) <= GRAD_REL, ("dv", _rel(vd.grad, rdv))
+  assert _rel(qd.grad, rdq) <= GRAD_REL, ("dq", _rel(qd.grad, rdq))
+  assert _rel(kd.grad, rdk) <= GRAD_REL, ("dk", _rel(kd.grad, rdk))
+
+
+def test_head_dims_above_128_sinks_and_repeatability():
+  """Forward with sinks at (256, 256), and the backward twice: bit-identical gradients."""
+  b, hq, hkv, s, d = 1, 4, 2, 384, 256
+  g = torch.Generator().manual_seed(5)
+  mk = lambda h: torch.randn(b, h, s, d, generator=g).to(torch.bfloat16)
+  q, k, v, do = mk(hq), mk(hkv), mk(hkv), mk(hq)
+  sinks = torch.tensor([0.3, -0.7, 1.5, 0.0])
+  mask = mask_lib.CausalMask((s, s))
+  kernel = splash.make_splash_mha(mask, q_seq_shards=1, save_residuals=True)
+  dev = torch.device("cuda:0")
+  scale = 1 / math.sqrt(d)
+  grads = []
+  for _ in range(2):
+    qd, kd, vd = (t.to(dev).requires_grad_(True) for t in (q, k, v))
+    out, res = kernel(qd, kd, vd, None, sinks.to(dev), logits_scale=scale)
+    out.backward(do.to(dev))
+    grads.append((qd.grad.clone(), kd.grad.clone(), vd.grad.clone()))
+  kernel.check_errors()
+  ro, rlse, rmax = attention_ref.attention_reference(q[0], k[0], v[0], _dense(mask), None, scale=scale, sinks=sinks)
+  assert ((out[0].float().cpu() - ro).abs() <= 1e-2 + 4e-3 * ro.abs()).all()
+  assert (res["logsumexp"][0].cpu() - rlse).abs().max().item() <= LSE_ATOL
+  assert (res["max_logits"][0].cpu() - rmax).abs().max().item() <= LSE_ATOL
+  for a, c in zip(*grads):
+    assert torch.equal(a, c)
 
 
 def test_small_head_dim_outputs_stay_inside_their_columns():

@@ -21,6 +21,7 @@ SOURCES = (
     "splash_fwd_sm100.cu",
     "splash_fwd_wide_sm100.cu",
     "splash_bwd_sm100.cu",
+    "splash_bwd_wide_sm100.cu",
     "splash_host.cu",
     "schedule_builder.cc",
     "maskinfo_builder.cc",

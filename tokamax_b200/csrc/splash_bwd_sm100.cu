@@ -29,15 +29,12 @@
 #include <mutex>
 
 #include "splash_common.cuh"
+#include "splash_bwd_params.cuh"
 
 namespace sb {
 
 constexpr int kBwdStages = 4;
 constexpr int kDqStages = 5;  // K/V ring of the dq kernel: 2.5 steps of look-ahead
-constexpr int kBwdThreads = 384;  // 8 compute warps + TMA warp + MMA warp + 2 idle warps that
-                                  // complete the third warpgroup for the register hand-over
-constexpr int kComputeRegs = 224;
-constexpr int kIssueRegs = 56;
 
 // ------------------------------------------------------------------------------------------
 // delta = rowsum(o * do)
@@ -62,37 +59,44 @@ __global__ void __launch_bounds__(256) splash_delta_kernel(const DeltaParams p) 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane & 15, half = lane >> 4;
   const int64_t row0 = (int64_t)blockIdx.x * kDeltaRowsPerBlock + warp * 8 + half;
-  uint4 a[4], g[4];
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  // one pass per 128 columns (a second one only for head dims above 128)
+  for (int c0 = 0; c0 < p.d_v; c0 += kHeadDim) {
+    uint4 a[4], g[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int64_t row = row0 + 2 * i;
-    a[i] = make_uint4(0u, 0u, 0u, 0u);
-    g[i] = a[i];
-    if (row < p.n_rows && sub * 8 < p.d_v) {
-      const int q = (int)(row % p.q_len);
-      const int64_t bh = row / p.q_len;
-      const int h = (int)(bh % p.q_heads);
-      const int64_t b = bh / p.q_heads;
-      a[i] = __ldg(reinterpret_cast<const uint4*>(p.o + b * p.o_sb + h * p.o_sh + (int64_t)q * p.o_ss) + sub);
-      g[i] = __ldg(reinterpret_cast<const uint4*>(p.d_o + b * p.do_sb + h * p.do_sh + (int64_t)q * p.do_ss) + sub);
+    for (int i = 0; i < 4; ++i) {
+      const int64_t row = row0 + 2 * i;
+      a[i] = make_uint4(0u, 0u, 0u, 0u);
+      g[i] = a[i];
+      if (row < p.n_rows && c0 + sub * 8 < p.d_v) {
+        const int q = (int)(row % p.q_len);
+        const int64_t bh = row / p.q_len;
+        const int h = (int)(bh % p.q_heads);
+        const int64_t b = bh / p.q_heads;
+        a[i] = __ldg(reinterpret_cast<const uint4*>(p.o + b * p.o_sb + h * p.o_sh + (int64_t)q * p.o_ss + c0) + sub);
+        g[i] = __ldg(reinterpret_cast<const uint4*>(p.d_o + b * p.do_sb + h * p.do_sh + (int64_t)q * p.do_ss + c0) + sub);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t aw[4] = {a[i].x, a[i].y, a[i].z, a[i].w}, gw[4] = {g[i].x, g[i].y, g[i].z, g[i].w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&aw[j]);
+        const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(&gw[j]);
+        acc[i] = fmaf(__bfloat162float(x.x), __bfloat162float(y.x), acc[i]);
+        acc[i] = fmaf(__bfloat162float(x.y), __bfloat162float(y.y), acc[i]);
+      }
     }
   }
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
-    const uint32_t aw[4] = {a[i].x, a[i].y, a[i].z, a[i].w}, gw[4] = {g[i].x, g[i].y, g[i].z, g[i].w};
-    float acc = 0.f;
+    float sum = acc[i];
 #pragma unroll
-    for (int j = 0; j < 4; ++j) {
-      const __nv_bfloat162 x = *reinterpret_cast<const __nv_bfloat162*>(&aw[j]);
-      const __nv_bfloat162 y = *reinterpret_cast<const __nv_bfloat162*>(&gw[j]);
-      acc = fmaf(__bfloat162float(x.x), __bfloat162float(y.x), acc);
-      acc = fmaf(__bfloat162float(x.y), __bfloat162float(y.y), acc);
-    }
-#pragma unroll
-    for (int off = 8; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
+    for (int off = 8; off > 0; off >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, off);
     const int64_t row = row0 + 2 * i;
     if (sub == 0 && row < p.n_rows) {
-      p.delta[row] = -acc;
+      p.delta[row] = -sum;
       // Rows that never met a live key carry the mask value as logsumexp; -inf keeps their
       // probabilities at exactly zero instead of overflowing the product to +inf.
       const float lse = p.lse[row];
@@ -104,38 +108,6 @@ __global__ void __launch_bounds__(256) splash_delta_kernel(const DeltaParams p) 
 // ------------------------------------------------------------------------------------------
 // shared pieces of the two MMA kernels
 // ------------------------------------------------------------------------------------------
-struct BwdParams {
-  // outputs (dq kernel: dq; dkv kernel: dk, dv)
-  __nv_bfloat16* out0;
-  int64_t out0_sb, out0_sh, out0_ss;
-  __nv_bfloat16* out1;
-  int64_t out1_sb, out1_sh, out1_ss;
-  const float* nlse2;  // [B, Hq, Sq]  -logsumexp * log2(e)
-  const float* delta;  // [B, Hq, Sq]  -sum_d(o * do)
-  const int32_t* q_seg;
-  const int32_t* kv_seg;
-  const int32_t* q_sequence;
-  const int32_t* row_ptr;
-  const int4* entries;
-  const int32_t* row_order;    // launch order of the rows (longest first) or nullptr
-  const int32_t* row_end;      // per batch row [batch, n_rows] or nullptr
-  int64_t entries_per_batch;   // 0: one list shared by all batch rows
-  const int8_t* pmb;
-  int pm_bq, pm_bkv;
-  SplashMaskFn fn;
-  int q_len, kv_len, q_heads, kv_heads, n_rows;
-  int d_qk, d_v;               // real columns of q / k / dq / dk and of v / o / do / dv (<= 128)
-  int nk_qk, nk_v;             // K = 16 slices with real columns in contractions over d_qk / d_v
-  int n_groups, chunk_groups;  // (batch, head) pairs of the grid; how many share a launch chunk
-  // soft-cap variants: logits = cap * tanh(scale * q k^T / cap); dS gains the factor 1 - tanh^2
-  float soft_cap, softcap_a;   // cap; scale / cap
-  float scale, scale_log2;
-  uint32_t* err;
-  // fused form only: fp32 dQ image, one 128 x 128 tile per (batch, q head, q tile), each tile
-  // stored as [col / 4][row][col % 4] so that one warp's vector red covers 512 contiguous bytes
-  float* dq_acc;
-};
-
 struct BwdBarriers {
   uint64_t stat_full[2];              // stationary operand tiles
   uint64_t ring_full[kDqStages];
@@ -151,31 +123,6 @@ struct BwdBarriers {
 };
 
 constexpr int kDqSmemBytes = (2 + kDqStages) * kTileBytes + 1024 + 1024;
-
-// Column offset (32-bit TMEM columns) at which compute warpgroup w stores its 32 packed bf16
-// columns: inside the 64 fp32 columns it has itself read, so the two warpgroups never race.
-__device__ __forceinline__ uint32_t packed_col(int w) { return (uint32_t)(w * 64); }
-// TMEM column of the A operand for K-slice k (16 values) of a tile written that way.
-__device__ __forceinline__ uint32_t packed_a_col(int k) {
-  return (uint32_t)((k >> 2) * 64 + (k & 3) * 8);
-}
-
-// 32 columns of a row, starting at column `col0` of a tensor that has `cols` columns: chunks of
-// eight that lie beyond the tensor's last column (head dims below 128) are not stored.
-__device__ __forceinline__ void store_row_half(__nv_bfloat16* dst, const uint32_t (&v)[32],
-                                               float mul, int col0 = 0, int cols = kHeadDim) {
-  uint4* d4 = reinterpret_cast<uint4*>(dst);
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    if (col0 + 8 * j >= cols) break;
-    uint4 w;
-    w.x = pack_bf16(__uint_as_float(v[8 * j + 0]) * mul, __uint_as_float(v[8 * j + 1]) * mul);
-    w.y = pack_bf16(__uint_as_float(v[8 * j + 2]) * mul, __uint_as_float(v[8 * j + 3]) * mul);
-    w.z = pack_bf16(__uint_as_float(v[8 * j + 4]) * mul, __uint_as_float(v[8 * j + 5]) * mul);
-    w.w = pack_bf16(__uint_as_float(v[8 * j + 6]) * mul, __uint_as_float(v[8 * j + 7]) * mul);
-    d4[j] = w;
-  }
-}
 
 // ------------------------------------------------------------------------------------------
 // dq kernel
@@ -1069,7 +1016,9 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   const int64_t Hkv = a.k.size[1], Skv = a.k.size[2];
   // head dims below 128 are read in place (zero-extended by the TMA boxes), see splash_fwd
   const int64_t Dv = a.v.size[3];
-  if (D > kHeadDim || Dv > kHeadDim) return SPLASH_ERR_UNSUPPORTED;
+  // head dims above 128 (up to 256): three passes over 128-column panels, splash_bwd_wide_sm100.cu
+  if (D > 2 * kHeadDim || Dv > 2 * kHeadDim) return SPLASH_ERR_UNSUPPORTED;
+  const bool wide = D > kHeadDim || Dv > kHeadDim;
   if (D % 8 != 0 || Dv % 8 != 0) return SPLASH_ERR_INVALID_ARGUMENT;
   auto same3 = [](const SplashTensor& x, const SplashTensor& y) {
     return x.size[0] == y.size[0] && x.size[1] == y.size[1] && x.size[2] == y.size[2];
@@ -1084,7 +1033,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     return SPLASH_ERR_INVALID_ARGUMENT;
   if (a.logsumexp == nullptr || a.error_record == nullptr || a.workspace == nullptr)
     return SPLASH_ERR_INVALID_ARGUMENT;
-  const bool fused = (a.flags & SPLASH_BWD_FUSED_DQ) != 0;
+  const bool fused = (a.flags & SPLASH_BWD_FUSED_DQ) != 0 && !wide;  // the wide passes are separate by construction
   if (a.workspace_bytes < (fused ? bwd_fused_workspace_bytes(B, Hq, Sq) : bwd_workspace_bytes(B, Hq, Sq)))
     return SPLASH_ERR_INVALID_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0) return SPLASH_ERR_INVALID_ARGUMENT;
@@ -1176,6 +1125,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.soft_cap = a.soft_cap;
   p.softcap_a = soft_cap ? a.scale / a.soft_cap : 0.f;
   p.dq_acc = fused ? dq_acc : nullptr;
+  if (wide) return launch_bwd_wide(tm_q, tm_do, tm_k, tm_v, p, a, soft_cap, mask, stream);
 
   // dq (split form)
   p.out0 = static_cast<__nv_bfloat16*>(a.dq.data);

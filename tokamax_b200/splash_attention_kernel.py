@@ -36,7 +36,7 @@ partial = functools.partial
 
 _TILE = 128
 _HEAD_DIM = 128
-_MAX_HEAD_DIM = 256  # forward only above _HEAD_DIM
+_MAX_HEAD_DIM = 256  # above _HEAD_DIM: the kernels that work on two 128-column panels
 
 
 def get_kernel_name(is_mqa: bool, save_residuals: bool, is_segmented: bool, phase: str) -> str:
@@ -346,10 +346,6 @@ class _SplashFunction(torch.autograd.Function):
   @staticmethod
   def backward(ctx, d_o, _dlse, _dmax):
     q, k, v, o, lse, q_seg, kv_seg, sinks = ctx.saved_tensors
-    if q.shape[-1] > _HEAD_DIM or v.shape[-1] > _HEAD_DIM:
-      raise NotImplementedError(
-          f"the backward for head dims above {_HEAD_DIM} is not built on B200 (forward only), got "
-          f"{q.shape[-1]} / {v.shape[-1]}")
     dq, dk, dv, neg_di = splash_backward(ctx.kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale, ctx.shard)
     dsinks = None
     if sinks is not None:
@@ -372,7 +368,8 @@ def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg
   d_o = _usable(d_o)
   dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
   lib = _native.lib()
-  fused = not kernel.repeatable_dq
+  # head dims above 128 run three separate passes (dq, dk, dv), each repeatable bit for bit
+  fused = not kernel.repeatable_dq and q.shape[-1] <= _HEAD_DIM and v.shape[-1] <= _HEAD_DIM
   size_fn = lib.splash_bwd_fused_workspace_bytes if fused else lib.splash_bwd_workspace_bytes
   ws_bytes = size_fn(q.shape[0], q.shape[1], q.shape[2])
   workspace = torch.empty(ws_bytes, dtype=torch.uint8, device=q.device)
@@ -548,7 +545,7 @@ class SplashAttentionKernel:
     # read in place: the kernels' TMA boxes reach past the end of a row and get zeros there, which
     # change neither q k^T nor p v, and only the real columns of outputs and gradients are stored.
     # No copy is made.  Head dims above 128, up to 256 (the reference's (192, 128) and (256, 256)),
-    # run a forward that works on two 128-column panels; their backward is not built and raises.
+    # run kernels that work on two 128-column panels.
     d_qk, d_v = q.shape[-1], v.shape[-1]
     if k.shape[-1] != d_qk:
       raise ValueError(f"q and k head dims differ: {d_qk} vs {k.shape[-1]}")
