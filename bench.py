@@ -599,7 +599,7 @@ def run_single_gpu(args, w, wname, emit=True):
                      "peak_source": sub["roofline"]["peak_source"], "config": sub["config"],
                      "kernel_ms": sub["roofline"].get("kernel_ms")}
       torch.cuda.empty_cache()
-    other["wide_head_dims_forward"] = wide_head_dim_forward(dev)
+    other["wide_head_dims"] = wide_head_dims(dev)
     line["other_workloads"] = other
   if not args.no_cpu_baseline:
     line["cpu_baseline"] = cpu_baseline(w)
@@ -608,27 +608,39 @@ def run_single_gpu(args, w, wname, emit=True):
   return line
 
 
-def wide_head_dim_forward(dev, steps: int = 5) -> dict:
-  """Forward only at the head dims above 128 the reference's splash microbenchmarks quote —
-  (q k, v) = (192, 128) and (256, 256); causal, batch 1, 32 q heads, 8 kv heads, S = 8192 — in mask-
-  counted TFLOP/s (2 * d_qk + 2 * d_v FLOPs per live pair).  The backward is not built at these sizes."""
+def wide_head_dims(dev, steps: int = 5) -> dict:
+  """The head dims above 128 the reference's splash microbenchmarks quote — (q k, v) = (192, 128) and
+  (256, 256); causal, batch 1, 32 q heads, 8 kv heads, S = 8192 — forward and backward in mask-counted
+  TFLOP/s (forward 2 * d_qk + 2 * d_v FLOPs per live pair, backward 2 * (3 * d_qk + 2 * d_v))."""
   from tokamax_b200 import splash_attention_kernel as splash
   from tokamax_b200 import splash_attention_mask as mask_lib
 
   s, hq, hkv = 8192, 32, 8
   kernel = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1)
   peak, _, _ = measured_peaks()
+  live = hq * (s * (s + 1) // 2)
   out = {}
   for d_qk, d_v in ((192, 128), (256, 256)):
     g = torch.Generator(device=dev).manual_seed(7000 + d_qk)
-    q, k, v = (torch.randn(1, h, s, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
-               for h, d in ((hq, d_qk), (hkv, d_qk), (hkv, d_v)))
+    q, k, v, do = (torch.randn(1, h, s, d, generator=g, device=dev, dtype=torch.float32).to(torch.bfloat16)
+                   for h, d in ((hq, d_qk), (hkv, d_qk), (hkv, d_v), (hq, d_v)))
+    scale = 1 / math.sqrt(d_qk)
     with torch.no_grad():
-      ms = timed_steps(lambda: kernel(q, k, v, logits_scale=1 / math.sqrt(d_qk)), steps, 3)
-    flops = hq * (s * (s + 1) // 2) * (2 * d_qk + 2 * d_v)
-    out[f"{d_qk}_{d_v}"] = {"ms": ms, "tflops": flops / ms / 1e9, "frac_of_peak": flops / ms / 1e9 / peak}
+      ms_f = timed_steps(lambda: kernel(q, k, v, logits_scale=scale), steps, 3)
+
+    def fwd_bwd():
+      qd, kd, vd = (t.detach().requires_grad_(True) for t in (q, k, v))
+      kernel(qd, kd, vd, logits_scale=scale).backward(do)
+
+    ms_fb = timed_steps(fwd_bwd, steps, 3)
+    f_fwd, f_bwd = live * (2 * d_qk + 2 * d_v), live * 2 * (3 * d_qk + 2 * d_v)
+    out[f"{d_qk}_{d_v}"] = {
+        "fwd_ms": ms_f, "fwd_tflops": f_fwd / ms_f / 1e9, "fwd_frac_of_peak": f_fwd / ms_f / 1e9 / peak,
+        "bwd_ms": ms_fb - ms_f, "bwd_tflops": f_bwd / (ms_fb - ms_f) / 1e9,
+        "bwd_frac_of_peak": f_bwd / (ms_fb - ms_f) / 1e9 / peak,
+        "fwd_bwd_ms": ms_fb, "fwd_bwd_tflops": (f_fwd + f_bwd) / ms_fb / 1e9}
   kernel.check_errors()
-  out["config"] = {"batch": 1, "q_heads": hq, "kv_heads": hkv, "seq": s, "mask": "causal", "pass": "forward"}
+  out["config"] = {"batch": 1, "q_heads": hq, "kv_heads": hkv, "seq": s, "mask": "causal"}
   return out
 
 
@@ -929,12 +941,12 @@ def main():
   wname = args.workload
   if wname == "auto":
     wname = "c2" if world == 1 else "c4"
-  if wname == "wide":  # forward at head dims (192, 128) and (256, 256): a side line, not a headline workload
+  if wname == "wide":  # head dims (192, 128) and (256, 256): a side line, not a headline workload
     if args.impl != "ours" or world != 1 or not torch.cuda.is_available():
       raise SystemExit("--workload wide is a single-GPU run of this build's forward")
-    print(json.dumps({"metric": "splash forward TFLOP/s (masked FLOPs), head dims above 128", "unit": "TFLOP/s",
+    print(json.dumps({"metric": "splash TFLOP/s (masked FLOPs), head dims above 128", "unit": "TFLOP/s",
                       "n_gpus": 1, "steps": args.steps, "dtype": "bf16", "data": "synthetic",
-                      **wide_head_dim_forward(torch.device("cuda", 0), max(args.steps, 1))}), flush=True)
+                      **wide_head_dims(torch.device("cuda", 0), max(args.steps, 1))}), flush=True)
     return
   w = WORKLOADS[wname]
   if args.impl == "reference":

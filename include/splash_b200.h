@@ -15,8 +15,8 @@
  *   - Asynchronous kernel faults (a bounded wait that ran out) are reported through a
  *     caller-provided 4-word device error record, read back with splash_read_error.
  *   - Tensors are (batch, heads, seq, head_dim) with element strides; head_dim must be
- *     contiguous (stride 1), a multiple of 8 and at most 128 (forward: at most 256; q / k and
- *     v / o may differ), and every other stride a multiple of 8 elements (16 bytes), so the
+ *     contiguous (stride 1), a multiple of 8 and at most 256 (q / k and v / o may differ; the
+ *     e4m3 forward takes 128 only), and every other stride a multiple of 8 elements (16 bytes), so the
  *     reference's [heads, seq, dim] layout, the Op layout [batch, seq, heads, dim] and the
  *     head-sharded layout the context-parallel exchange produces are all consumed without copies.
  */

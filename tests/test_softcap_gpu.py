@@ -23,13 +23,17 @@ def _rel(a, ref):
   return ((a.float().cpu() - ref).norm() / ref.norm().clamp_min(1e-20)).item()
 
 
-@pytest.mark.parametrize("cap,scale", [(30.0, 1 / math.sqrt(D)), (8.0, 0.35), (2.0, 1 / math.sqrt(D))])
+@pytest.mark.parametrize("cap,scale,dims", [(30.0, 1 / math.sqrt(D), (D, D)), (8.0, 0.35, (D, D)),
+                                            (2.0, 1 / math.sqrt(D), (D, D)), (8.0, 0.2, (192, 128)),
+                                            (4.0, 1 / 16, (256, 256))])
 @pytest.mark.parametrize("kind", ["causal", "local_segments"])
-def test_soft_cap_forward_backward(cap, scale, kind):
+def test_soft_cap_forward_backward(cap, scale, dims, kind):
+  """(128, 128), and the head dims above 128 that run the two-panel kernels."""
   b, hq, hkv, s = 1, 4, 2, 512
-  g = torch.Generator().manual_seed(int(cap * 10) + len(kind))
+  d_qk, d_v = dims
+  g = torch.Generator().manual_seed(int(cap * 10) + len(kind) + d_qk)
   mk = lambda *shape: torch.randn(*shape, generator=g).to(torch.bfloat16)
-  q, k, v, do = mk(b, hq, s, D), mk(b, hkv, s, D), mk(b, hkv, s, D), mk(b, hq, s, D)
+  q, k, v, do = mk(b, hq, s, d_qk), mk(b, hkv, s, d_qk), mk(b, hkv, s, d_v), mk(b, hq, s, d_v)
   seg = None
   if kind == "causal":
     mask = mask_lib.CausalMask((s, s))
