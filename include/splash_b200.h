@@ -142,8 +142,10 @@ void splash_maskinfo_free(SplashMaskInfoOut* out);
  *   kind 1 (dq)     : one row per q tile;          entry = kv tile.
  *   kind 2 (dkv)    : one row per kv tile;         entry = q tile.
  * Entry layout (4 x int32): [0] tile index along the walked axis, [1] state of sub-tile 0 in
- * bits 0-1 and of sub-tile 1 in bits 2-3 (0 skip, 1 partial, 2 full), [2]/[3] partial-block id
- * of sub-tile 0/1 (-1 if none).
+ * bits 0-1 and of sub-tile 1 in bits 2-3 (0 skip, 1 partial, 2 full); bits 4 / 5, written by
+ * splash_segment_schedule only: sub-tile 0 / 1 lies inside one segment (every token of its q tile
+ * and of its kv tile carries the same id), so the kernels need not compare ids element by element;
+ * [2]/[3] partial-block id of sub-tile 0/1 (-1 if none).
  * ---------------------------------------------------------------------------------------- */
 typedef struct SplashScheduleOut {
   int32_t* row_ptr;   /* [n_rows + 1] */
@@ -183,7 +185,8 @@ typedef struct SplashDeviceSchedule {
  * overlap contribute nothing, so they can be dropped before the kernels run.  This call filters
  * a schedule per batch row: it computes the [min, max] segment id of every 128-token tile and
  * writes, for each batch row, the entries that can still hold an unmasked pair (sub-tile states
- * are lowered to 0 where they cannot).  Results are unchanged; only skipped work differs.
+ * are lowered to 0 where they cannot) and marks the sub-tiles that lie inside one segment (entry
+ * bits 4 / 5).  Results are unchanged; only skipped work differs.
  *
  * `in` is a schedule of `kind` (0 forward, 1 dq, 2 dkv, as in splash_schedule_build) with
  * n_entries filled in.  `out` receives device pointers into `workspace`

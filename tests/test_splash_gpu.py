@@ -203,25 +203,34 @@ def test_segment_aware_schedule_matches_brute_force(kind):
   tiles = seg.numpy().reshape(batch, nt, 128)
   lo, hi = tiles.min(-1), tiles.max(-1)
   overlap = lambda b, qt, kt: not (hi[b, qt] < lo[b, kt] or lo[b, qt] > hi[b, kt])
+  # bits 4 / 5: the sub-tile lies inside one segment (the kernels then skip the id comparison)
+  one = lambda b, qt, kt: int(lo[b, qt] == hi[b, qt] == lo[b, kt] == hi[b, kt])
   for b in range(batch):
     for r in range(n_rows):
       want = []
       for e in range(row_ptr[r], row_ptr[r + 1]):
         x, st = int(entries[e, 0]), int(entries[e, 1])
         s0, s1 = st & 3, (st >> 2) & 3
+        u0 = u1 = 0
         if kind == 0:
           s0 = s0 if s0 and overlap(b, 2 * r, x) else 0
           s1 = s1 if s1 and 2 * r + 1 < nt and overlap(b, 2 * r + 1, x) else 0
+          u0 = one(b, 2 * r, x) if s0 else 0
+          u1 = one(b, 2 * r + 1, x) if s1 else 0
         elif kind == 1:
           s0, s1 = (s0 if s0 and overlap(b, r, x) else 0), 0
+          u0 = one(b, r, x) if s0 else 0
         else:
           s0, s1 = (s0 if s0 and overlap(b, x, r) else 0), 0
+          u0 = one(b, x, r) if s0 else 0
         if s0 or s1:
-          want.append((x, s0 | (s1 << 2)))
+          want.append((x, s0 | (s1 << 2) | (u0 << 4) | (u1 << 5)))
       got = [(int(a[0]), int(a[1])) for a in got_entries[b, row_ptr[r]:row_end[b, r]]]
       assert got == want, (b, r)
   assert out.entries_per_batch == n_ent and (row_end <= row_ptr[1:][None]).all()
   assert (row_end.astype(np.int64) - row_ptr[:-1][None]).sum() < batch * n_ent  # something was dropped
+  assert any(int(e[1]) & 0x30 for b in range(batch) for r in range(n_rows)
+             for e in got_entries[b, row_ptr[r]:row_end[b, r]])  # and some tiles lie inside one segment
 
 
 @pytest.mark.parametrize("bq,bkv", [(256, 128), (128, 256), (512, 512)])

@@ -1,5 +1,6 @@
 // Segment-aware schedules: drop, per batch row, the 128x128 tiles whose q and kv segment-id
-// ranges cannot contain an equal pair.  Two small HBM-bound kernels: tile ranges, then a
+// ranges cannot contain an equal pair, and mark the tiles that lie inside one segment (all ids of
+// the q tile and of the kv tile equal), for which the kernels skip the per-element comparison.  Two small HBM-bound kernels: tile ranges, then a
 // per-row stream compaction of the schedule entries.  Results of attention are unchanged (the
 // dropped tiles are fully masked by the segment mask); only skipped work differs.
 #include "splash_common.cuh"
@@ -50,6 +51,8 @@ splash_segment_ranges_kernel(const int32_t* __restrict__ q_seg, const int32_t* _
 }
 
 __device__ __forceinline__ bool ranges_overlap(int2 a, int2 b) { return !(a.y < b.x || a.x > b.y); }
+// every token of both tiles carries one and the same id: the segment mask keeps the whole tile
+__device__ __forceinline__ bool same_segment(int2 a, int2 b) { return a.x == a.y && b.x == b.y && a.x == b.x; }
 
 // One block per (schedule row, batch row): keeps the entries that can still hold an unmasked
 // pair, in order, at the start of the row's slot of the per-batch copy.
@@ -74,18 +77,23 @@ splash_segment_filter_kernel(const int32_t* __restrict__ row_ptr, const int4* __
     if (e < eend) {
       ent = entries[e];
       int s0 = ent.y & 3, s1 = (ent.y >> 2) & 3;
+      int u0 = 0, u1 = 0;  // SPLASH_ENTRY_ONE_SEGMENT_*: the kernels skip the per-element id comparison
       if (kind == 0) {  // row = pair of q tiles, entry = kv tile
         const int2 k = kr[ent.x];
         if (s0 && !ranges_overlap(qr[2 * row], k)) s0 = 0;
         if (s1 && (2 * row + 1 >= n_q_tiles || !ranges_overlap(qr[2 * row + 1], k))) s1 = 0;
+        u0 = s0 && same_segment(qr[2 * row], k);
+        u1 = s1 && same_segment(qr[2 * row + 1], k);
       } else if (kind == 1) {  // row = q tile, entry = kv tile
         if (s0 && !ranges_overlap(qr[row], kr[ent.x])) s0 = 0;
         s1 = 0;
+        u0 = s0 && same_segment(qr[row], kr[ent.x]);
       } else {  // row = kv tile, entry = q tile
         if (s0 && !ranges_overlap(qr[ent.x], kr[row])) s0 = 0;
         s1 = 0;
+        u0 = s0 && same_segment(qr[ent.x], kr[row]);
       }
-      ent.y = s0 | (s1 << 2);
+      ent.y = s0 | (s1 << 2) | (u0 << 4) | (u1 << 5);
       if (s0 == 0) ent.z = -1;
       if (s1 == 0) ent.w = -1;
       keep = (s0 | s1) != 0;

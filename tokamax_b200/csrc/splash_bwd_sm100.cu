@@ -350,7 +350,7 @@ splash_dq_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           }
         }
       }
-      if (has_seg) {
+      if (has_seg && !((ent.y >> 4) & 1)) {  // (bit set: the whole tile lies inside one segment)
         const int4* sg4 = reinterpret_cast<const int4*>(kv_seg_row + kv0);
 #pragma unroll
         for (int g = 0; g < 16; ++g) {
@@ -831,7 +831,7 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             }
           }
         }
-        if (has_seg) {
+        if (has_seg && !((ent.y >> 4) & 1)) {  // (bit set: the whole tile lies inside one segment)
           const int4* sg4 = reinterpret_cast<const int4*>(q_seg_row + q0);
 #pragma unroll
           for (int t = 0; t < 8; ++t) {

@@ -341,7 +341,7 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             }
           }
         }
-        if (has_seg) {
+        if (has_seg && !((ent.y >> 4) & 1)) {  // (bit set: the whole tile lies inside one segment)
           const int4* sg4 = reinterpret_cast<const int4*>(other_seg + c0);
 #pragma unroll
           for (int t = 0; t < 16; ++t) {

@@ -354,7 +354,7 @@ splash_fwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           }
         }
       }
-      if (has_seg) {
+      if (has_seg && !((ent.y >> (4 + i)) & 1)) {  // (bit set: the whole tile lies inside one segment)
         const int4* sg4 = reinterpret_cast<const int4*>(kv_seg_row + kv0);
 #pragma unroll
         for (int g = 0; g < kWideHalf / 4; ++g) {
