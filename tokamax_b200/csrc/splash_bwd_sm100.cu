@@ -49,6 +49,9 @@ struct DeltaParams {
   int q_heads, q_len;
   int d_v;  // columns of o / do
   int64_t n_rows;
+  // fused backward: the fp32 dQ image (one 128 x 128 tile per 128 rows, [col / 4][row][col % 4])
+  // that the reds of the dkv kernel add into; this pass clears it on the way.  nullptr: none.
+  float* dq_image;
 };
 
 // 64 rows per block: a warp takes eight rows, half a warp per row (16 lanes x 16 bytes = one row of
@@ -59,6 +62,19 @@ __global__ void __launch_bounds__(256) splash_delta_kernel(const DeltaParams p) 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int sub = lane & 15, half = lane >> 4;
   const int64_t row0 = (int64_t)blockIdx.x * kDeltaRowsPerBlock + warp * 8 + half;
+  if (p.dq_image != nullptr) {
+    // The block's 64 rows are half of one image tile (q_len is a multiple of 128): for each of the
+    // 32 four-column groups a run of 64 rows x 16 bytes.  256 threads x 8 stores of 16 bytes.
+    const int64_t first = (int64_t)blockIdx.x * kDeltaRowsPerBlock;
+    float* tile = p.dq_image + (first / kTile) * (int64_t)(kTile * kHeadDim) + (first % kTile) * 4;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int idx = i * 256 + threadIdx.x;  // 0 .. 2047: (column group, row) of the half tile
+      const int cg = idx >> 6, r = idx & 63;
+      *reinterpret_cast<uint4*>(tile + (int64_t)cg * (kTile * 4) + r * 4) = zero;
+    }
+  }
   float acc[4] = {0.f, 0.f, 0.f, 0.f};
   // one pass per 128 columns (a second one only for head dims above 128)
   for (int c0 = 0; c0 < p.d_v; c0 += kHeadDim) {
@@ -1055,10 +1071,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   float* delta = static_cast<float*>(a.workspace);
   float* nlse2 = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + bwd_workspace_bytes(B, Hq, Sq) / 2);
   float* dq_acc = reinterpret_cast<float*>(static_cast<uint8_t*>(a.workspace) + bwd_workspace_bytes(B, Hq, Sq));
-  if (fused && (mask & 1u)) {  // the image the reds add into starts at zero
-    if (cudaMemsetAsync(dq_acc, 0, (size_t)B * Hq * Sq * kHeadDim * sizeof(float), stream) != cudaSuccess)
-      return SPLASH_ERR_CUDA;
-  }
+  // (fused form: the image the reds add into starts at zero; the di pass clears it while it streams)
   if (mask & 1u) {
     DeltaParams dp;
     dp.o = static_cast<const __nv_bfloat16*>(a.o.data);
@@ -1076,6 +1089,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     dp.q_len = (int)Sq;
     dp.d_v = (int)Dv;
     dp.n_rows = B * Hq * Sq;
+    dp.dq_image = fused ? dq_acc : nullptr;
     const unsigned blocks = (unsigned)((dp.n_rows + kDeltaRowsPerBlock - 1) / kDeltaRowsPerBlock);
     splash_delta_kernel<<<blocks, 256, 0, stream>>>(dp);
     if (cudaGetLastError() != cudaSuccess) return SPLASH_ERR_CUDA;
