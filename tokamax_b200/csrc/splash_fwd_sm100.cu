@@ -42,6 +42,7 @@ struct FwdBarriers {
   uint64_t kv_full[kFwdStages];
   uint64_t kv_empty[kFwdStages];
   uint64_t s_full[2];
+  uint64_t p_half[2];    // the first 64 key columns of P are in TMEM (the first half of the p v MMAs may go)
   uint64_t p_full[2];
   uint64_t o_done[2];
   uint64_t vc_full[2];   // e4m3 with f16 P: a V tile has been converted to f16
@@ -120,7 +121,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
     for (int i = 0; i < 2; ++i) {
       mbar_init(&bars->q_full[i], 1);
       mbar_init(&bars->s_full[i], 1);
-      mbar_init(&bars->p_full[i], 4);  // one arrival per softmax warp
+      mbar_init(&bars->p_half[i], 4);  // one arrival per softmax warp
+      mbar_init(&bars->p_full[i], 4);
       mbar_init(&bars->o_done[i], 1);
       mbar_init(&bars->vc_full[i], 2);   // one arrival per converting warp
       mbar_init(&bars->vc_empty[i], 1);
@@ -263,18 +265,23 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       // 8 kv rows x 128 B per core group (SBO 1024).  bf16: 64-column halves 16 KiB apart (LBO),
       // K=16 slices 2 KiB apart; e4m3: the 128 columns fit one 128-byte row, K=32 slices 4 KiB
       // apart, P packed four values per TMEM column.
-      auto issue_pv = [&](int i, uint32_t slot, bool acc) {
+      // `half` 0 / 1: the K slices over the first / last 64 key columns of P (the softmax warps hand
+      // P over in two halves, so that the first MMAs run while the second half is still being made)
+      auto issue_pv = [&](int i, uint32_t slot, bool acc, int half) {
         const uint32_t b0 = kP16 ? vc_addr + slot * kTileBytes : kv_addr + slot * kTB;
         if constexpr (kFp8 && !kP16) {
           const SmemDesc db = make_smem_desc_sw128(b0, 16, 1024);
 #pragma unroll
-          for (int k = 0; k < 4; ++k)
+          for (int kk = 0; kk < 2; ++kk) {
+            const int k = half * 2 + kk;
             umma_ts_f8(tmem + 2 * kTile + i * kTile, tmem + i * kTile + k * 8, desc_at(db, k * 4096), idesc_pv,
                        (acc || k > 0) ? 1u : 0u);
+          }
         } else {
           const SmemDesc db = make_smem_desc_sw128(b0, kHalfBytes, 1024);
 #pragma unroll
-          for (int k = 0; k < 8; ++k) {
+          for (int kk = 0; kk < 4; ++kk) {
+            const int k = half * 4 + kk;
             umma_ts(tmem + 2 * kTile + i * kTile, tmem + i * kTile + k * 8, desc_at(db, k * 2048), idesc_pv,
                     (acc || k > 0) ? 1u : 0u);
           }
@@ -311,11 +318,15 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           mma_issue_fence();
           for (int i = 0; i < 2 && ok; ++i) {
             if ((cur.y >> (2 * i)) & 3) {
+              ok = mbar_wait(&bars->p_half[i], pcnt[i] & 1u, ab, 0x350u + i);
+              if (!ok) break;
+              mma_issue_fence();
+              issue_pv(i, kP16 ? vc : vslot, started[i], 0);
               ok = mbar_wait(&bars->p_full[i], pcnt[i] & 1u, ab, 0x330u + i);
               if (!ok) break;
               ++pcnt[i];
               mma_issue_fence();
-              issue_pv(i, kP16 ? vc : vslot, started[i]);
+              issue_pv(i, kP16 ? vc : vslot, true, 1);
               started[i] = true;
             }
             if (i == 1) tc_commit(kP16 ? &bars->vc_empty[vc] : &bars->kv_empty[vslot]);
@@ -521,6 +532,12 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             pk[j] = pack_f16(p0, p1);
           }
           tmem_st16(t_s + g * 16, pk);
+          if (g == 1) {  // the first 64 key columns are in place
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->p_half[i]);
+          }
         }
         l += (ls0 + ls1) * __fdividef(0.015625f, r);
       } else if constexpr (kFp8) {
@@ -542,6 +559,12 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             pk[j] = pack_e4m3x4(p0, p1, p2, p3);
           }
           tmem_st16(t_s + g * 16, pk);
+          if (g == 0) {  // the first 64 key columns are in place
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->p_half[i]);
+          }
         }
         l += (ls0 + ls1) * __fdividef(0.015625f, r);  // back to exp2(s - m) units (2^-6 / r)
       } else {
@@ -562,6 +585,12 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
             pk[j + 1] = pack_bf16(pb.x, pb.y);
           }
           tmem_st16(t_s + g * 16, pk);
+          if (g == 1) {  // the first 64 key columns are in place
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&bars->p_half[i]);
+          }
         }
         ls0 = lsa.x + lsb.x;
         ls1 = lsa.y + lsb.y;
