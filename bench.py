@@ -790,7 +790,7 @@ def run_context_parallel(args, w, wname):
     cp.check_errors()  # the ring runs its own per-pair kernels
 
   # exchange alone: the 4 + 4 all-to-alls of one step (q, k, v, o forward; do, dq, dk, dv backward)
-  def exchanges():
+  def exchanges(skip=()):
     engine = getattr(cp, "engine", None)
     run = (lambda t, s2h, tag: ulysses._run_exchange(t, None, s2h, engine, tag))  # pylint: disable=protected-access
     for name, t in (("q", q), ("k", k), ("v", v), ("do", do)):
@@ -798,8 +798,13 @@ def run_context_parallel(args, w, wname):
     qh = torch.empty((w["batch"], w["q_heads"] // world, w["seq"], D), dtype=q.dtype, device=dev)
     kh = torch.empty((w["batch"], w["kv_heads"] // world, w["seq"], D), dtype=q.dtype, device=dev)
     for name, t in (("o", qh), ("dq", qh), ("dk", kh), ("dv", kh)):
-      run(t, False, "bench." + name)
+      if name not in skip:
+        run(t, False, "bench." + name)
   a2a_ms = None if ring_mode else max_over_ranks(timed_steps(exchanges, 3, 1, barrier=dist.barrier))
+  # "fused": the output's exchange runs inside the forward kernel; what stays in line with the kernels
+  exposed_ms = a2a_ms
+  if not ring_mode and getattr(cp, "fused", False):
+    exposed_ms = max_over_ranks(timed_steps(lambda: exchanges(skip=("o",)), 3, 1, barrier=dist.barrier))
   sent = 2 * (2 * ulysses.exchange_bytes_sent(q.shape, 2, world) + 2 * ulysses.exchange_bytes_sent(k.shape, 2, world))
 
   # end to end: each rank's sequence shard starts and ends in pinned host memory.  Copies run on two
@@ -904,7 +909,9 @@ def run_context_parallel(args, w, wname):
                "nvlink_nominal_gbs_per_direction": 900.0,
                "single_gpu_ms_per_step": single_ms,
                "scaling_efficiency": None if single_ms is None else single_ms / (world * ms),
-               "exposed_a2a_ms_per_step": a2a_ms,  # the exchanges run in line with the kernels: all of it is exposed
+               # the exchanges run in line with the kernels, so all of their time is exposed; with
+               # --exchange fused the output's exchange is part of the forward kernel and is left out
+               "exposed_a2a_ms_per_step": exposed_ms,
                },
         "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak_sustained, "unit": "TFLOP/s",
                      "frac": value / world / peak_sustained, "peak_source": f"{peak_src} bf16 sustained, per GPU",
@@ -922,7 +929,7 @@ def main():
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4", "c5", "wide"])
-  ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer"],
+  ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer", "fused"],
                   help="Ulysses exchange: the library's own peer-store kernel over symmetric memory (peer), NCCL "
                        "all_to_all_single (nccl), or peer with nccl as the fallback if symmetric memory cannot be set up (auto)")
   ap.add_argument("--cp", default="ulysses", choices=["ulysses", "ring", "ring_zigzag"],

@@ -230,6 +230,25 @@ int splash_dynamic_schedule(const int32_t* states, int64_t q_len, int64_t kv_len
  * accumulation, plus logsumexp and max_logits (natural log, fp32 [batch, q_heads, q_len]).
  * q head h reads kv head h / (q_heads / kv_heads) (:675-682).
  * ---------------------------------------------------------------------------------------- */
+/* Optional second destination of an output, for context parallelism (the Ulysses exchange fused
+ * into the kernel that produces the tensor): besides its ordinary destination, every row of the
+ * output is also stored — plain 16-byte stores over NVLink, no TMA, no multicast — into the buffer
+ * of the rank that owns that row in the sequence-sharded layout [batch, all heads, rows_per_peer,
+ * head_dim].  Sequence row s of local head h goes to rank s / rows_per_peer, at
+ *   ptrs[rank] + base_bytes + 2 * (batch * stride_b + (head0 + h) * stride_h + (s % rows_per_peer) * stride_s).
+ * `ptrs` is a device array with one entry per rank: the address at which that rank's buffer is mapped
+ * in this process (symmetric memory / IPC; this rank's own buffer included).  The caller orders the
+ * kernel between two barriers across the ranks: receive buffers free before, all stores landed after.
+ * ptrs == NULL: no second destination.  The reference has no counterpart (its context-parallel
+ * wrapper is ring attention, ring_attention_kernel.py:68-293). */
+typedef struct SplashPeerOutput {
+  const uint64_t* ptrs;
+  int64_t base_bytes;
+  int64_t rows_per_peer;
+  int64_t stride_b, stride_h, stride_s;  /* elements */
+  int32_t head0;
+} SplashPeerOutput;
+
 typedef struct SplashFwdArgs {
   SplashTensor q, k, v, o;          /* bf16 */
   float* logsumexp;                 /* may be NULL */
@@ -254,6 +273,9 @@ typedef struct SplashFwdArgs {
   /* attn_logits_soft_cap (splash_attention_kernel.py:202-296, base.py:92-94): logits become
    * cap * tanh(scale * q k^T / cap) before masking.  0 = off.  bf16 inputs only. */
   float soft_cap;
+  /* Second destination of `o` in other ranks' memory; bf16 kernels with head dims up to 128 only
+   * (SPLASH_ERR_UNSUPPORTED otherwise). */
+  SplashPeerOutput o_peer;
 } SplashFwdArgs;
 
 int splash_fwd(const SplashFwdArgs* args, void* cuda_stream);

@@ -519,3 +519,40 @@ def test_seq_minor_layouts_give_the_head_dim_minor_result():
   assert torch.equal(out, ref)
   for got, want in ((qb.grad, qa.grad), (kb.grad, ka.grad), (vb.grad, va.grad)):
     assert got.shape == want.transpose(-1, -2).shape and torch.equal(got.transpose(-1, -2), want)
+
+
+def test_forward_peer_output_rows_land_in_their_owners_buffers():
+  """`SplashFwdArgs.o_peer` on one GPU: two local buffers stand in for the receive buffers of two
+  ranks.  Every output row must arrive, bit for bit, in the buffer of the rank that owns it, at this
+  rank's head block, and nothing else may be touched."""
+  import ctypes as C
+
+  b, hq, hkv, s, d, world, rank = 2, 4, 2, 512, 128, 2, 1
+  dev = torch.device("cuda:0")
+  g = torch.Generator().manual_seed(91)
+  mk = lambda h: torch.randn(b, h, s, d, generator=g).to(torch.bfloat16).to(dev)
+  q, k, v = mk(hq), mk(hkv), mk(hkv)
+  kernel = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1)
+  s_loc, h_all = s // world, hq * world
+  # receive buffers [B, all heads, S / world, D] of the two "ranks", with a guard band in front
+  guard = 64
+  bufs = [torch.full((guard + b * h_all * s_loc * d,), 7.0, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+  ptrs = torch.tensor([t.data_ptr() for t in bufs], dtype=torch.int64, device=dev)
+  po = _native.SplashPeerOutput()
+  po.ptrs, po.base_bytes, po.rows_per_peer = ptrs.data_ptr(), guard * 2, s_loc
+  po.stride_b, po.stride_h, po.stride_s, po.head0 = h_all * s_loc * d, s_loc * d, d, rank * hq
+  _, _, _, o, _, _, _ = splash.splash_forward(kernel, q, k, v, None, None, 0.09, None, None, 0, o_peer=po)
+  torch.cuda.synchronize()
+  kernel.check_errors()
+  plain = kernel(q, k, v, logits_scale=0.09)
+  assert torch.equal(o, plain)
+  for peer in range(world):
+    assert (bufs[peer][:guard] == 7.0).all()
+    got = bufs[peer][guard:].view(b, h_all, s_loc, d)
+    assert torch.equal(got[:, rank * hq:(rank + 1) * hq], o[:, :, peer * s_loc:(peer + 1) * s_loc])
+    other = torch.cat([got[:, :rank * hq], got[:, (rank + 1) * hq:]], dim=1)
+    assert (other == 7.0).all()
+  # arguments that cannot be right are refused before anything is launched
+  po.rows_per_peer = 200
+  with pytest.raises(_native.SplashError):
+    splash.splash_forward(kernel, q, k, v, None, None, 0.09, None, None, 0, o_peer=po)

@@ -66,7 +66,7 @@ def _worker(rank, world, port, queue, exchange="nccl"):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("exchange", ["nccl", "peer"])
+@pytest.mark.parametrize("exchange", ["nccl", "peer", "fused"])
 def test_ulysses_matches_single_gpu_bitwise(exchange):
   world = 2
   ctx = mp.get_context("spawn")

@@ -121,6 +121,18 @@ class SplashDeviceSchedule(C.Structure):
   ]
 
 
+class SplashPeerOutput(C.Structure):
+  _fields_ = [
+      ("ptrs", C.c_void_p),
+      ("base_bytes", C.c_int64),
+      ("rows_per_peer", C.c_int64),
+      ("stride_b", C.c_int64),
+      ("stride_h", C.c_int64),
+      ("stride_s", C.c_int64),
+      ("head0", C.c_int32),
+  ]
+
+
 class SplashFwdArgs(C.Structure):
   _fields_ = [
       ("q", SplashTensor), ("k", SplashTensor), ("v", SplashTensor), ("o", SplashTensor),
@@ -137,6 +149,7 @@ class SplashFwdArgs(C.Structure):
       ("sinks", C.c_void_p),
       ("max_logit_value", C.c_void_p),
       ("soft_cap", C.c_float),
+      ("o_peer", SplashPeerOutput),
   ]
 
 

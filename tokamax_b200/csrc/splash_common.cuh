@@ -78,6 +78,23 @@ inline int chunk_groups_for(int64_t bytes_per_group, int64_t n_groups, int64_t a
   return (int)g;
 }
 
+// Address of row `s` of local head `h` in the rank that owns it (see SplashPeerOutput).
+__device__ __forceinline__ __nv_bfloat16* peer_row(const SplashPeerOutput& po, int batch, int h, int s) {
+  const int64_t peer = s / po.rows_per_peer;
+  const int64_t local = s - peer * po.rows_per_peer;
+  uint8_t* base = reinterpret_cast<uint8_t*>(po.ptrs[peer]) + po.base_bytes;
+  return reinterpret_cast<__nv_bfloat16*>(base) + (int64_t)batch * po.stride_b + (int64_t)(po.head0 + h) * po.stride_h +
+         local * po.stride_s;
+}
+inline int check_peer_output(const SplashPeerOutput& po, int64_t rows, int64_t head_dim) {
+  if (po.ptrs == nullptr) return SPLASH_OK;
+  if (po.rows_per_peer <= 0 || rows % po.rows_per_peer != 0 || po.head0 < 0 || po.base_bytes < 0 ||
+      po.base_bytes % 16 != 0 || po.stride_s < head_dim || po.stride_b % 8 != 0 || po.stride_h % 8 != 0 ||
+      po.stride_s % 8 != 0)
+    return SPLASH_ERR_INVALID_ARGUMENT;
+  return SPLASH_OK;
+}
+
 // Host-side helpers (defined in splash_host.cu).
 int make_tile_tensor_map(CUtensorMap* out, const SplashTensor& t, int box_rows);
 int check_bf16_tensor(const SplashTensor& t);

@@ -24,6 +24,7 @@ constexpr int kFp8TileBytes = kTile * kHeadDim;  // 16 KiB
 struct FwdParams {
   __nv_bfloat16* o;
   int64_t o_sb, o_sh, o_ss;
+  SplashPeerOutput o_peer;  // second destination of o in other ranks' memory (ptrs == nullptr: none)
   int d_v;  // columns of v / o (<= 128; the tile's remaining columns are zeros and are not stored)
   int nk_qk;  // K = 16 slices of q k^T that hold real columns: ceil(d_qk / 16); the rest are zeros and are skipped
   int d_qk;   // columns of q / k: at most 64 -> the second 64-column half of their tiles is never loaded or read

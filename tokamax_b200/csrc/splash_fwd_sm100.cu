@@ -613,6 +613,8 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       __nv_bfloat16* orow = p.o + (int64_t)batch * p.o_sb + (int64_t)head * p.o_sh +
                             (int64_t)q_row * p.o_ss;
       uint4* o4 = reinterpret_cast<uint4*>(orow);
+      // context parallelism: the row also goes to the rank that owns it in the sequence-sharded layout
+      uint4* peer4 = p.o_peer.ptrs ? reinterpret_cast<uint4*>(peer_row(p.o_peer, batch, head, q_row)) : nullptr;
       // e4m3: O accumulated P * 2^shift * (v scale / v_ref) times the stored V values
       const bool live = l > 0.f;  // a row that met a live key, or has a sink
       const float inv = live ? (kFp8 ? v_ref * 0.015625f / l : 1.0f / l) : 0.f;
@@ -633,7 +635,10 @@ splash_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
           w.y = pack_bf16(__uint_as_float(v[8 * j + 2]) * inv, __uint_as_float(v[8 * j + 3]) * inv);
           w.z = pack_bf16(__uint_as_float(v[8 * j + 4]) * inv, __uint_as_float(v[8 * j + 5]) * inv);
           w.w = pack_bf16(__uint_as_float(v[8 * j + 6]) * inv, __uint_as_float(v[8 * j + 7]) * inv);
-          if ((g * 4 + j) * 8 < p.d_v) o4[g * 4 + j] = w;
+          if ((g * 4 + j) * 8 < p.d_v) {
+            o4[g * 4 + j] = w;
+            if (peer4) peer4[g * 4 + j] = w;
+          }
         }
       }
       const int64_t stat = ((int64_t)batch * p.q_heads + head) * p.q_len + q_row;
@@ -675,6 +680,8 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
       return st;
   }
   if ((st = check_bf16_tensor(a.o))) return st;
+  if ((st = check_peer_output(a.o_peer, a.q.size[2], a.v.size[3]))) return st;
+  if (a.o_peer.ptrs != nullptr && (fp8 || a.q.size[3] > kHeadDim || a.v.size[3] > kHeadDim)) return SPLASH_ERR_UNSUPPORTED;
   const int64_t B = a.q.size[0], Hq = a.q.size[1], Sq = a.q.size[2], D = a.q.size[3];
   const int64_t Hkv = a.k.size[1], Skv = a.k.size[2];
   // Head dims: the MMA tile is 128 wide.  bf16 tensors with fewer columns (a multiple of 8, so rows
@@ -714,6 +721,7 @@ static int launch_fwd_common(const SplashFwdArgs& a, const float* q_scale, const
   p.o_sb = a.o.stride[0];
   p.o_sh = a.o.stride[1];
   p.o_ss = a.o.stride[2];
+  p.o_peer = a.o_peer;
   p.d_v = (int)Dv;
   p.nk_qk = (int)((D + 15) / 16);
   p.d_qk = (int)D;

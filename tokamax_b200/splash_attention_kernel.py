@@ -297,44 +297,57 @@ def _mask_fn_struct(mask_function_rule) -> _native.SplashMaskFn:
   return fn
 
 
+def splash_forward(kernel, q, k, v, q_seg, kv_seg, scale, sinks, max_logit, shard=0, o_peer=None):
+  """One `splash_fwd` call on batched ``[B, H, S, D]`` bf16 tensors.
+
+  Returns ``(q, k, v, o, logsumexp, max_logits, sinks_f32)``: the operands as the kernel read them
+  (copies where a tensor could not be read in place) and the results.  ``o_peer``: an optional
+  `_native.SplashPeerOutput`, the second destination of ``o`` in other ranks' memory.
+  """
+  _require_cuda(q)
+  tables = kernel._tables(q.device, q.shape[0], shard)  # pylint: disable=protected-access
+  q, k, v = _usable(q), _usable(k), _usable(v)
+  b, hq, sq, d = q.shape
+  if v.shape[-1] == d:
+    o = torch.empty_like(q)  # keeps q's (dense) stride order, e.g. [B,T,H,D] storage stays [B,T,H,D]
+  else:
+    o = torch.empty((b, hq, sq, v.shape[-1]), dtype=q.dtype, device=q.device)
+  lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
+  max_logits = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
+  args = _native.SplashFwdArgs()
+  args.q, args.k, args.v, args.o = map(_tensor_desc, (q, k, v, o))
+  args.logsumexp = lse.data_ptr()
+  args.max_logits = max_logits.data_ptr()
+  args.q_segment_ids = q_seg.data_ptr() if q_seg is not None else None
+  args.kv_segment_ids = kv_seg.data_ptr() if kv_seg is not None else None
+  args.q_sequence = tables.q_sequence.data_ptr() if tables.q_sequence is not None else None
+  keep = []
+  args.sched = tables.fwd
+  if q_seg is not None and not tables.fwd.row_end:  # device-built schedules are not filtered further
+    args.sched, ws = _segment_schedule(tables.fwd, 0, q_seg, kv_seg, q.shape[2], k.shape[2])
+    keep.append(ws)
+  args.mask_fn = _mask_fn_struct(kernel.mask_function_rule)
+  args.scale = scale
+  args.mask_value = max(kernel.mask_value, -3.0e38)
+  args.error_record = tables.error_record.data_ptr()
+  sinks_f32 = None if sinks is None else sinks.detach().to(torch.float32).contiguous()
+  args.sinks = None if sinks_f32 is None else sinks_f32.data_ptr()
+  args.soft_cap = float(kernel.config.attn_logits_soft_cap or 0.0)
+  args.max_logit_value = None if max_logit is None else max_logit.data_ptr()
+  if o_peer is not None:
+    args.o_peer = o_peer
+  stream = torch.cuda.current_stream(q.device).cuda_stream
+  with torch.cuda.device(q.device):
+    _native.check(_native.lib().splash_fwd(C.byref(args), C.c_void_p(stream)), "splash_fwd")
+  return q, k, v, o, lse, max_logits, sinks_f32
+
+
 class _SplashFunction(torch.autograd.Function):
   """forward = splash_fwd, backward = splash_bwd (reference custom_vjp: kernel.py:998-1108)."""
 
   @staticmethod
   def forward(ctx, q, k, v, q_seg, kv_seg, kernel, scale, sinks, max_logit, shard=0):
-    _require_cuda(q)
-    tables = kernel._tables(q.device, q.shape[0], shard)  # pylint: disable=protected-access
-    q, k, v = _usable(q), _usable(k), _usable(v)
-    b, hq, sq, d = q.shape
-    if v.shape[-1] == d:
-      o = torch.empty_like(q)  # keeps q's (dense) stride order, e.g. [B,T,H,D] storage stays [B,T,H,D]
-    else:
-      o = torch.empty((b, hq, sq, v.shape[-1]), dtype=q.dtype, device=q.device)
-    lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
-    max_logits = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
-    args = _native.SplashFwdArgs()
-    args.q, args.k, args.v, args.o = map(_tensor_desc, (q, k, v, o))
-    args.logsumexp = lse.data_ptr()
-    args.max_logits = max_logits.data_ptr()
-    args.q_segment_ids = q_seg.data_ptr() if q_seg is not None else None
-    args.kv_segment_ids = kv_seg.data_ptr() if kv_seg is not None else None
-    args.q_sequence = tables.q_sequence.data_ptr() if tables.q_sequence is not None else None
-    keep = []
-    args.sched = tables.fwd
-    if q_seg is not None and not tables.fwd.row_end:  # device-built schedules are not filtered further
-      args.sched, ws = _segment_schedule(tables.fwd, 0, q_seg, kv_seg, q.shape[2], k.shape[2])
-      keep.append(ws)
-    args.mask_fn = _mask_fn_struct(kernel.mask_function_rule)
-    args.scale = scale
-    args.mask_value = max(kernel.mask_value, -3.0e38)
-    args.error_record = tables.error_record.data_ptr()
-    sinks_f32 = None if sinks is None else sinks.detach().to(torch.float32).contiguous()
-    args.sinks = None if sinks_f32 is None else sinks_f32.data_ptr()
-    args.soft_cap = float(kernel.config.attn_logits_soft_cap or 0.0)
-    args.max_logit_value = None if max_logit is None else max_logit.data_ptr()
-    stream = torch.cuda.current_stream(q.device).cuda_stream
-    with torch.cuda.device(q.device):
-      _native.check(_native.lib().splash_fwd(C.byref(args), C.c_void_p(stream)), "splash_fwd")
+    q, k, v, o, lse, max_logits, sinks_f32 = splash_forward(kernel, q, k, v, q_seg, kv_seg, scale, sinks, max_logit, shard)
     ctx.save_for_backward(q, k, v, o, lse, q_seg, kv_seg, sinks_f32)
     ctx.sinks_dtype = None if sinks is None else sinks.dtype
     ctx.kernel = kernel
@@ -510,7 +523,9 @@ class SplashAttentionKernel:
       raise NotImplementedError(f"only bfloat16 inputs are built on B200, got {q.dtype}")
 
   def __call__(self, q, k, v, segment_ids: SegmentIds | None = None, sinks=None, *,
-               max_logit_value=None, logits_scale: float = 1.0, q_shard: int = 0, **overrides):
+               max_logit_value=None, logits_scale: float = 1.0, q_shard: int = 0, _function=None, **overrides):
+    # `_function`: what runs on the checked arguments in place of the plain autograd function (the
+    # context-parallel wrapper passes one whose forward also stores the output into its peers).
     kw = dict(self.kwargs, **overrides)
     save_residuals = kw.get("save_residuals", False)
     self._reject_unsupported(q, k, sinks, max_logit_value)
@@ -575,8 +590,8 @@ class SplashAttentionKernel:
       if tuple(value.shape) not in ((), (1,), (hq,)):
         raise ValueError(f"max_logit_value should have shape (), (1,) or ({hq},), got {tuple(value.shape)}")
       max_logit = value.reshape(-1).expand(hq).contiguous()
-    o, lse, max_logits = _SplashFunction.apply(q, k, v, q_seg, kv_seg, self, float(logits_scale), sinks,
-                                               max_logit, int(q_shard))
+    apply = _function if _function is not None else _SplashFunction.apply
+    o, lse, max_logits = apply(q, k, v, q_seg, kv_seg, self, float(logits_scale), sinks, max_logit, int(q_shard))
     if not batched:
       o, lse, max_logits = o[0], lse[0], max_logits[0]
     if save_residuals:

@@ -125,7 +125,10 @@ class PeerExchange:
       self._buffers[key] = (t, handle, base)
     return self._buffers[key]
 
-  def exchange(self, x: torch.Tensor, seq_to_head: bool, tag: str) -> torch.Tensor:
+  def exchange(self, x: torch.Tensor, seq_to_head: bool, tag: str, barriers: tuple[bool, bool] = (True, True)) -> torch.Tensor:
+    """``barriers``: whether this call runs the barrier before / after its copy kernel.  Exchanges
+    issued back to back (q, k, v of one call) share one pair: the first keeps the barrier in front,
+    the last the one behind, and nothing reads a received tensor before that last barrier."""
     import ctypes as C  # pylint: disable=g-import-not-at-top
     from tokamax_b200 import _native  # pylint: disable=g-import-not-at-top
 
@@ -150,31 +153,33 @@ class PeerExchange:
     args.dst_base_bytes = base
     stream = torch.cuda.current_stream(x.device).cuda_stream
     with torch.cuda.device(x.device):
-      self._barrier(x.device)  # every rank's earlier readers of its receive buffer are behind this point
+      if barriers[0]:
+        self._barrier(x.device)  # every rank's earlier readers of its receive buffers are behind this point
       _native.check(_native.lib().splash_exchange_push(C.byref(args), C.c_void_p(stream)), "splash_exchange_push")
-      self._barrier(x.device)  # every rank's stores have landed
+      if barriers[1]:
+        self._barrier(x.device)  # every rank's stores have landed
     return out
 
 
-def _run_exchange(x, group, seq_to_head: bool, engine, tag):
+def _run_exchange(x, group, seq_to_head: bool, engine, tag, barriers=(True, True)):
   if engine is None or dist.get_world_size(group) == 1:
     return _exchange(x, group, seq_to_head)
-  return engine.exchange(x, seq_to_head, tag)
+  return engine.exchange(x, seq_to_head, tag, barriers)
 
 
 class _SeqToHead(torch.autograd.Function):
 
   @staticmethod
-  def forward(ctx, x, group, engine=None, tag=None):
+  def forward(ctx, x, group, engine=None, tag=None, barriers=(True, True)):
     ctx.group, ctx.engine, ctx.tag = group, engine, tag
-    return _run_exchange(x, group, True, engine, tag)
+    return _run_exchange(x, group, True, engine, tag, barriers)
 
   @staticmethod
   def backward(ctx, g):
     out = _run_exchange(g, ctx.group, False, ctx.engine, None if ctx.tag is None else ctx.tag + ".grad")
     if ctx.engine is not None:
       out = out.clone()  # handed to the caller as a .grad: must outlive the buffer's next use
-    return out, None, None, None
+    return out, None, None, None, None
 
 
 class _HeadToSeq(torch.autograd.Function):
@@ -189,14 +194,59 @@ class _HeadToSeq(torch.autograd.Function):
     return _run_exchange(g, ctx.group, True, ctx.engine, None if ctx.tag is None else ctx.tag + ".grad"), None, None, None
 
 
-def seq_to_head(x: torch.Tensor, group=None, engine: PeerExchange | None = None, tag: str | None = None) -> torch.Tensor:
+def seq_to_head(x: torch.Tensor, group=None, engine: PeerExchange | None = None, tag: str | None = None,
+                barriers: tuple[bool, bool] = (True, True)) -> torch.Tensor:
   """Differentiable all-to-all: sequence shard of all heads -> all of the sequence for H/P heads."""
-  return _SeqToHead.apply(x, group, engine, tag)
+  return _SeqToHead.apply(x, group, engine, tag, barriers)
 
 
 def head_to_seq(x: torch.Tensor, group=None, engine: PeerExchange | None = None, tag: str | None = None) -> torch.Tensor:
   """Differentiable inverse of :func:`seq_to_head`."""
   return _HeadToSeq.apply(x, group, engine, tag)
+
+
+class _AttentionIntoPeers(torch.autograd.Function):
+  """Splash attention on this rank's heads whose forward kernel also stores every output row into
+  the receive buffer of the rank that owns it in the sequence-sharded layout (`SplashFwdArgs.o_peer`:
+  plain 16-byte stores over NVLink from the kernel's epilogue, spread over the whole kernel), so the
+  head -> sequence exchange of the output costs one barrier instead of a transfer.  Returns the
+  sequence shard ``[B, H, S/P, D]``; the backward pass brings dO in by the copy kernel and runs the
+  ordinary backward on the saved head shard.
+
+  The receive buffers must be free when this runs: the caller has exchanged q / k / v through the
+  same engine just before, and the barriers of those exchanges lie behind every rank's last read.
+  """
+
+  @staticmethod
+  def forward(ctx, q, k, v, q_seg, kv_seg, kernel, scale, sinks, max_logit, shard, engine, tag):
+    from tokamax_b200 import _native  # pylint: disable=g-import-not-at-top
+    from tokamax_b200 import splash_attention_kernel as splash  # pylint: disable=g-import-not-at-top
+
+    if sinks is not None or max_logit is not None or shard:
+      raise NotImplementedError("sinks, a fixed maximum and q shards are not taken by the fused exchange")
+    rank, world = _world(engine.group)
+    b, h_loc, s_all = q.shape[:3]
+    s_loc = s_all // world
+    out, handle, base = engine._buffer(tag, (b, h_loc * world, s_loc, v.shape[3]), q.dtype, q.device)  # pylint: disable=protected-access
+    po = _native.SplashPeerOutput()
+    po.ptrs, po.base_bytes, po.rows_per_peer = int(handle.buffer_ptrs_dev), base, s_loc
+    po.stride_b, po.stride_h, po.stride_s, po.head0 = out.stride(0), out.stride(1), out.stride(2), rank * h_loc
+    q, k, v, o, lse, max_logits, _ = splash.splash_forward(kernel, q, k, v, q_seg, kv_seg, scale, None, None, 0, o_peer=po)
+    with torch.cuda.device(q.device):
+      engine._barrier(q.device)  # every rank's kernel has finished: all rows have landed  # pylint: disable=protected-access
+    ctx.save_for_backward(q, k, v, o, lse, q_seg, kv_seg)
+    ctx.kernel, ctx.scale, ctx.engine, ctx.tag = kernel, scale, engine, tag
+    ctx.mark_non_differentiable(lse, max_logits)
+    return out.clone(), lse, max_logits  # the caller's tensor must outlive the buffer's next use
+
+  @staticmethod
+  def backward(ctx, g, _dlse, _dmax):
+    from tokamax_b200 import splash_attention_kernel as splash  # pylint: disable=g-import-not-at-top
+
+    q, k, v, o, lse, q_seg, kv_seg = ctx.saved_tensors
+    d_o = ctx.engine.exchange(g, True, ctx.tag + ".grad")
+    dq, dk, dv, _ = splash.splash_backward(ctx.kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale, 0)
+    return (dq, dk, dv) + (None,) * 9
 
 
 class _ReleaseOnBackward(torch.autograd.Function):
@@ -229,8 +279,11 @@ class UlyssesSplashAttention:
     attention: a ``SplashAttentionKernel`` built for the FULL (unsharded) mask, or any callable
       ``(q, k, v, segment_ids, *, logits_scale) -> out`` over ``[batch, heads, seq, dim]``.
     group: process group spanning the context-parallel ranks (default: the world).
-    exchange: "nccl" (default: one ``all_to_all_single`` per tensor) or "peer" (:class:`PeerExchange`:
-      own copy kernel over symmetric memory; CUDA + NVLink peers only).
+    exchange: "nccl" (default: one ``all_to_all_single`` per tensor), "peer" (:class:`PeerExchange`:
+      own copy kernel over symmetric memory; CUDA + NVLink peers only) or "fused" ("peer", and the
+      forward kernel itself stores the output into the ranks that own its rows, so the output's
+      exchange is hidden under the kernel; needs a ``SplashAttentionKernel`` with head dims up to 128,
+      falls back to "peer" otherwise).
 
   Call with the local sequence shards ``q [B, Hq, S/P, D]``, ``k, v [B, Hkv, S/P, D]``; rank ``r``
   holds tokens ``[r*S/P, (r+1)*S/P)``.  ``P`` must divide the q-head count, and either divide the
@@ -240,11 +293,12 @@ class UlyssesSplashAttention:
   """
 
   def __init__(self, attention: Callable, group=None, exchange: str = "nccl"):
-    if exchange not in ("nccl", "peer"):
-      raise ValueError(f"exchange must be 'nccl' or 'peer', got {exchange!r}")
+    if exchange not in ("nccl", "peer", "fused"):
+      raise ValueError(f"exchange must be 'nccl', 'peer' or 'fused', got {exchange!r}")
     self.attention = attention
     self.group = group
-    self.engine = PeerExchange(group) if exchange == "peer" else None
+    self.engine = PeerExchange(group) if exchange in ("peer", "fused") else None
+    self.fused = exchange == "fused"
 
   @staticmethod
   def kv_heads_for_ranks(q_heads: int, kv_heads: int, world: int) -> list[int] | None:
@@ -275,15 +329,27 @@ class UlyssesSplashAttention:
       tags = tuple(f"{name}{slot}" for name in ("q", "k", "v", "o"))
       if needs_grad:
         q = _ReleaseOnBackward.apply(q, engine, slot)
-    q_h = seq_to_head(q, self.group, engine, tags[0])
-    k_h = seq_to_head(k, self.group, engine, tags[1])
-    v_h = seq_to_head(v, self.group, engine, tags[2])
+    # the three pushes share one pair of barriers (nothing reads q_h / k_h / v_h before the last one)
+    q_h = seq_to_head(q, self.group, engine, tags[0], (True, False))
+    k_h = seq_to_head(k, self.group, engine, tags[1], (False, False))
+    v_h = seq_to_head(v, self.group, engine, tags[2], (False, True))
     seg_full = None
     if segment_ids is not None:
       seg_full = base.SegmentIds(self._gather_seq(segment_ids.q), self._gather_seq(segment_ids.kv))
+    if engine is not None and self.fused and self._can_fuse(q_h, v_h):
+      into_peers = lambda *args: _AttentionIntoPeers.apply(*args, engine, tags[3])
+      return self.attention(q_h, k_h, v_h, seg_full, logits_scale=logits_scale, _function=into_peers)
     o_h = self.attention(q_h, k_h, v_h, seg_full, logits_scale=logits_scale)
     out = head_to_seq(o_h, self.group, engine, tags[3])
     return out.clone() if engine is not None else out  # the caller's tensor must outlive the buffer's next use
+
+  def _can_fuse(self, q_h, v_h) -> bool:
+    from tokamax_b200 import splash_attention_kernel as splash  # pylint: disable=g-import-not-at-top
+
+    a = self.attention
+    return (isinstance(a, splash.SplashAttentionKernel) and q_h.shape[-1] <= 128 and v_h.shape[-1] <= 128 and
+            q_h.dim() == 4 and not a.kwargs.get("save_residuals", False) and a.q_seq_shards == 1 and
+            a.config.max_logit_const is None)
 
   def check_errors(self) -> None:
     """Raises if the wrapped kernel reported a device-side fault (SplashAttentionKernel.check_errors)."""
