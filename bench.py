@@ -749,7 +749,7 @@ def run_context_parallel(args, w, wname):
     if args.exchange == "auto":
       # every rank must take the same branch: agree on whether the peer engine came up everywhere
       try:
-        cp = ulysses.UlyssesSplashAttention(kernel, exchange="peer")
+        cp = ulysses.UlyssesSplashAttention(kernel, exchange="fused")
         cp.engine.exchange(torch.zeros(1, world, 128, D, dtype=torch.bfloat16, device=dev), True, "probe")
         ok_here = 1.0
       except Exception as e:  # pylint: disable=broad-except
@@ -757,7 +757,7 @@ def run_context_parallel(args, w, wname):
       flag = torch.tensor([ok_here], device=dev)
       dist.all_reduce(flag, op=dist.ReduceOp.MIN)
       if flag.item() == 1.0:
-        exchange_used = "peer"
+        exchange_used = "fused"
       else:
         exchange_used = "nccl (peer exchange unavailable" + (f": {why})" if ok_here == 0.0 else " on another rank)")
         cp = ulysses.UlyssesSplashAttention(kernel, exchange="nccl")

@@ -122,3 +122,23 @@ def test_op_soft_cap_matches_oracle():
                                               mask_lib.make_causal_mask((t, t)), scale=0.3, attn_logits_soft_cap=5.0)
   ref = o.permute(1, 0, 2)[None]
   assert ((out.float().cpu() - ref).abs() <= 1e-2 + 4e-3 * ref.abs()).all()
+
+
+@pytest.mark.parametrize("d_qk,d_v", [(192, 128), (256, 256), (64, 64)])
+def test_op_head_dims_other_than_128(d_qk, d_v):
+  """[B, T, N, H] strided views at the reference's other head dims (its kernel test draws (64, 64),
+  (192, 128) and (256, 256)): output and the three gradients against the oracle."""
+  dev = torch.device("cuda:0")
+  b, t, n, kh = 2, 384, 4, 2
+  g = torch.Generator().manual_seed(d_qk + d_v)
+  mk = lambda heads, d: torch.randn(b, t, heads, d, generator=g).to(torch.bfloat16)
+  q, k, v, do = mk(n, d_qk), mk(kh, d_qk), mk(kh, d_v), mk(n, d_v)
+  scale = d_qk ** -0.5
+  ref_o, ref_dq, ref_dk, ref_dv = _oracle_grads(q, k, v, do, mask_lib.make_causal_mask((t, t)), scale)
+  qd, kd, vd = (x.to(dev).requires_grad_(True) for x in (q, k, v))
+  out = op.dot_product_attention(qd, kd, vd, is_causal=True, implementation="cuda_sm100")  # AUTO scale = d_qk ** -0.5
+  out.backward(do.to(dev))
+  assert out.shape == (b, t, n, d_v)
+  rel = lambda a, r: ((a.float().cpu() - r).norm() / r.norm()).item()
+  assert ((out.float().cpu() - ref_o).abs() <= 1e-2 + 4e-3 * ref_o.abs()).all()
+  assert rel(qd.grad, ref_dq) <= 1e-2 and rel(kd.grad, ref_dk) <= 1e-2 and rel(vd.grad, ref_dv) <= 1e-2

@@ -98,8 +98,8 @@ def _check_inputs(q, k, v, *, bias, logits_dtype, dropout_mask, dropout_rate, pa
   for name in ("q_start", "q_end", "k_start", "k_end"):
     if getattr(mask, name) is not None:
       raise NotImplementedError(f"mask.{name} is not supported.")
-  if q.shape[-1] != 128 or v.shape[-1] != 128:
-    raise NotImplementedError("head_dim 128 only through the custom call")
+  if q.shape[-1] > 256 or v.shape[-1] > 256 or q.shape[-1] % 8 or v.shape[-1] % 8:
+    raise NotImplementedError("head dims must be multiples of 8, at most 256")
   if q.shape[-3] % 128 or k.shape[-3] % 128:
     raise NotImplementedError("sequence lengths must be multiples of 128")
 

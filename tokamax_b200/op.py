@@ -81,8 +81,8 @@ class CudaSm100SplashAttention:
     s, k_heads = key.shape[-3], key.shape[-2]
     if list(key.shape[:-3]) != batch or list(value.shape[:-3]) != batch:
       raise ValueError("batch dimensions of query, key and value differ")
-    if h > 128 or value.shape[-1] > 128:
-      raise NotImplementedError(f"head dims above 128 are not built on B200, got {h} / {value.shape[-1]}")
+    if h > 256 or value.shape[-1] > 256:
+      raise NotImplementedError(f"head dims above 256 are not built on B200, got {h} / {value.shape[-1]}")
     if t % 128 or s % 128:
       raise NotImplementedError("sequence lengths must be multiples of 128")
     scale = h ** -0.5 if logits_scale == AUTO else float(logits_scale)
