@@ -20,9 +20,11 @@
 // dq / dk passes multiplies the stationary panels with the held ones.  In the dk / dv passes the
 // tile is transposed (threads own kv rows, columns are query rows), so logsumexp and di come per
 // column and the mask function is evaluated per element, as in the 128-wide dkv kernel.
-// Shared memory: 4 stationary + 2 held + 1 passing panel of 32 KiB.  Nothing of step n+1 is loaded
-// before step n has released its slots, so loads and MMAs alternate rather than overlap: this
-// backward is built for coverage of the reference's head dims, not tuned.
+// Shared memory: 4 stationary + 2 held + 1 passing panel of 32 KiB (dv pass: 2 + 2 + 2).  A step's
+// first passing panel is loaded while the previous step is still in its element-wise phase (dq / dk:
+// dP of a step is issued ahead of its S, whose held panels arrive later; dv: both Q panels of the
+// next step), the held panels only once the previous output MMAs have released them.  Built for
+// coverage of the reference's head dims rather than tuned: S is computed in all three passes.
 #include <mutex>
 
 #include "splash_common.cuh"
@@ -38,8 +40,8 @@ struct WideBwdBarriers {
   uint64_t stat_full;
   uint64_t held_full[2];
   uint64_t held_empty[2];
-  uint64_t pass_full;
-  uint64_t pass_empty;
+  uint64_t pass_full[2];
+  uint64_t pass_empty[2];
   uint64_t s_full;
   uint64_t dp_full;
   uint64_t ds_full;   // P (dv pass) or dS written back; one arrival per compute warp
@@ -69,7 +71,10 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
   uint8_t* a1_smem = smem;                      // 2 panels: Q (dq pass) or K
   uint8_t* a2_smem = smem + 2 * kTileBytes;     // 2 panels: dO (dq pass) or V; unused in the dv pass
   uint8_t* held_smem = smem + 4 * kTileBytes;   // 2 panels
-  uint8_t* pass_smem = smem + 6 * kTileBytes;   // 1 panel
+  // passing panels: one slot behind the held ones; the dv pass has no second stationary operand and
+  // takes that operand's two panels as two slots instead, so a whole step's Q panels are prefetched
+  constexpr uint32_t kPassSlots = kPass == kWideDv ? 2u : 1u;
+  uint8_t* pass_smem = kPass == kWideDv ? a2_smem : smem + 6 * kTileBytes;
   WideBwdBarriers* bars = reinterpret_cast<WideBwdBarriers*>(smem + 7 * kTileBytes);
 
   const int warp = threadIdx.x >> 5;
@@ -102,8 +107,10 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_init(&bars->held_full[i], 1);
       mbar_init(&bars->held_empty[i], 1);
     }
-    mbar_init(&bars->pass_full, 1);
-    mbar_init(&bars->pass_empty, 1);
+    for (int i = 0; i < 2; ++i) {
+      mbar_init(&bars->pass_full[i], 1);
+      mbar_init(&bars->pass_empty[i], 1);
+    }
     mbar_init(&bars->s_full, 1);
     mbar_init(&bars->dp_full, 1);
     mbar_init(&bars->ds_full, 8);
@@ -159,14 +166,15 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
           load_panel(held_smem + hp * kTileBytes, tm_held, &bars->held_full[hp], cols, hp * kHeadDim, col * kTile, head, batch);
         }
       };
-      auto load_pass = [&](int col, int head) {
-        for (int pp = 0; pp < n_pass && ok; ++pp) {
-          const uint32_t it = n * (uint32_t)n_pass + pp;
-          ok = mbar_wait(&bars->pass_empty, (it & 1u) ^ 1u, ab, 0xC10u);
+      auto load_pass = [&](int col, int head, int first, int last) {  // passing panels first .. last - 1
+        for (int pp = first; pp < last && ok; ++pp) {
+          const uint32_t it = n * (uint32_t)n_pass + pp, slot = it % kPassSlots;
+          ok = mbar_wait(&bars->pass_empty[slot], ((it / kPassSlots) & 1u) ^ 1u, ab, 0xC10u + slot);
           if (!ok) break;
           const int cols = panel_cols(d_pass, pp);
-          mbar_arrive_expect_tx(&bars->pass_full, wide_panel_bytes(cols));
-          load_panel(pass_smem, tm_pass, &bars->pass_full, cols, pp * kHeadDim, col * kTile, head, batch);
+          mbar_arrive_expect_tx(&bars->pass_full[slot], wide_panel_bytes(cols));
+          load_panel(pass_smem + slot * kTileBytes, tm_pass, &bars->pass_full[slot], cols, pp * kHeadDim, col * kTile,
+                     head, batch);
         }
       };
       for (int g = 0; g < heads_here && ok; ++g) {
@@ -174,12 +182,16 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int head = kPass == kWideDq ? kv_head : kv_head * group + g;
         for (int e = ebeg; e < eend && ok; ++e, ++n) {
           const int col = entries[e].x;
+          // In the order the issuer takes them (the slots free up in that order too).  dq / dk: the
+          // first passing panel was free since the previous step's dP, so it is in flight long before
+          // the held panels, which wait for the previous step's output MMAs.
           if (kPass == kWideDv) {
-            load_pass(col, head);
+            load_pass(col, head, 0, n_pass);
             load_held(col, head);
           } else {
+            load_pass(col, head, 0, 1);
             load_held(col, head);
-            load_pass(col, head);
+            load_pass(col, head, 1, n_pass);
           }
         }
       }
@@ -203,32 +215,33 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       };
       bool ok = mbar_wait(&bars->stat_full, 0, ab, 0xD00u);
       for (uint32_t n = 0; n < (uint32_t)n_steps && ok; ++n) {
+        // passing panel pp of this step into an accumulating MMA with stationary panel a0 + pp
+        auto mma_passing = [&](uint32_t d, uint32_t a0, int dim, int pp) {
+          const uint32_t it = n * (uint32_t)n_pass + pp, slot = it % kPassSlots;
+          if (!mbar_wait(&bars->pass_full[slot], (it / kPassSlots) & 1u, ab, 0xD20u + slot)) return false;
+          mma_issue_fence();
+          ss_kmajor(d, a0 + pp * kTileBytes, pass_addr + slot * kTileBytes, panel_cols(dim, pp), pp > 0);
+          tc_commit(&bars->pass_empty[slot]);
+          return true;
+        };
         if (kPass != kWideDv) {
+          // dP = sum over panels (stationary do or v) (passing v or do)^T: its first panel was loaded
+          // during the previous step; the dP columns are free since that step's ds_full
+          // (with two passing panels the first goes ahead of S, so that the second can load under S;
+          // with one, S goes first and the element-wise phase starts on it while dP runs)
+          if (npv > 1) ok = mma_passing(t_dp, a2_addr, p.d_v, 0);
+          if (!ok) break;
           for (int hp = 0; hp < n_held && ok; ++hp) ok = mbar_wait(&bars->held_full[hp], n & 1u, ab, 0xD10u + hp);
           if (!ok) break;
           mma_issue_fence();
           for (int pp = 0; pp < npk; ++pp)  // S = sum over panels (stationary q or k) (held k or q)^T
             ss_kmajor(t_s, a1_addr + pp * kTileBytes, held_addr + pp * kTileBytes, panel_cols(p.d_qk, pp), pp > 0);
           tc_commit(&bars->s_full);
-          for (int vp = 0; vp < npv && ok; ++vp) {  // dP = sum over panels (stationary do or v) (passing v or do)^T
-            const uint32_t it = n * (uint32_t)npv + vp;
-            ok = mbar_wait(&bars->pass_full, it & 1u, ab, 0xD20u);
-            if (!ok) break;
-            mma_issue_fence();
-            ss_kmajor(t_dp, a2_addr + vp * kTileBytes, pass_addr, panel_cols(p.d_v, vp), vp > 0);
-            tc_commit(&bars->pass_empty);
-          }
+          for (int vp = npv > 1 ? 1 : 0; vp < npv && ok; ++vp) ok = mma_passing(t_dp, a2_addr, p.d_v, vp);
           if (!ok) break;
           tc_commit(&bars->dp_full);
         } else {
-          for (int pp = 0; pp < npk && ok; ++pp) {  // S^T = sum over panels k (passing q)^T
-            const uint32_t it = n * (uint32_t)npk + pp;
-            ok = mbar_wait(&bars->pass_full, it & 1u, ab, 0xD20u);
-            if (!ok) break;
-            mma_issue_fence();
-            ss_kmajor(t_s, a1_addr + pp * kTileBytes, pass_addr, panel_cols(p.d_qk, pp), pp > 0);
-            tc_commit(&bars->pass_empty);
-          }
+          for (int pp = 0; pp < npk && ok; ++pp) ok = mma_passing(t_s, a1_addr, p.d_qk, pp);  // S^T = sum k (passing q)^T
           if (!ok) break;
           tc_commit(&bars->s_full);
           for (int hp = 0; hp < n_held && ok; ++hp) ok = mbar_wait(&bars->held_full[hp], n & 1u, ab, 0xD10u + hp);
