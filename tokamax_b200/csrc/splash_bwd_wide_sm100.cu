@@ -38,13 +38,13 @@ constexpr int kWideBwdSmemBytes = 7 * kTileBytes + 1024 /*barriers*/ + 1024 /*al
 
 struct WideBwdBarriers {
   uint64_t stat_full;
-  uint64_t held_full[2];
-  uint64_t held_empty[2];
+  uint64_t held_full[3];
+  uint64_t held_empty[3];
   uint64_t pass_full[2];
   uint64_t pass_empty[2];
-  uint64_t s_full;
+  uint64_t s_full[2];   // dv pass: S alternates between two TMEM buffers; dq / dk: [0] only
   uint64_t dp_full;
-  uint64_t ds_full;   // P (dv pass) or dS written back; one arrival per compute warp
+  uint64_t ds_full[2];  // P (dv pass, per S buffer) or dS written back; one arrival per compute warp
   uint64_t acc_done;
   uint32_t tmem_base;
   uint32_t abort_flag;
@@ -70,7 +70,10 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
                                              ~static_cast<uintptr_t>(1023));
   uint8_t* a1_smem = smem;                      // 2 panels: Q (dq pass) or K
   uint8_t* a2_smem = smem + 2 * kTileBytes;     // 2 panels: dO (dq pass) or V; unused in the dv pass
-  uint8_t* held_smem = smem + 4 * kTileBytes;   // 2 panels
+  // held panels: a ring of two slots (a step's panels), or of three in the dv pass, which has the
+  // panel behind them to spare: a panel of the next step's dO is then loaded under this step
+  constexpr uint32_t kHeldSlots = kPass == kWideDv ? 3u : 2u;
+  uint8_t* held_smem = smem + 4 * kTileBytes;
   // passing panels: one slot behind the held ones; the dv pass has no second stationary operand and
   // takes that operand's two panels as two slots instead, so a whole step's Q panels are prefetched
   constexpr uint32_t kPassSlots = kPass == kWideDv ? 2u : 1u;
@@ -103,7 +106,7 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
     bars->early_exit = *reinterpret_cast<volatile uint32_t*>(p.err);
     bars->abort_flag = 0;
     mbar_init(&bars->stat_full, 1);
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 3; ++i) {
       mbar_init(&bars->held_full[i], 1);
       mbar_init(&bars->held_empty[i], 1);
     }
@@ -111,9 +114,11 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       mbar_init(&bars->pass_full[i], 1);
       mbar_init(&bars->pass_empty[i], 1);
     }
-    mbar_init(&bars->s_full, 1);
+    mbar_init(&bars->s_full[0], 1);
+    mbar_init(&bars->s_full[1], 1);
     mbar_init(&bars->dp_full, 1);
-    mbar_init(&bars->ds_full, 8);
+    mbar_init(&bars->ds_full[0], 8);
+    mbar_init(&bars->ds_full[1], 8);
     mbar_init(&bars->acc_done, 1);
     mbar_fence_init();
   }
@@ -159,11 +164,15 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
       bool ok = true;
       auto load_held = [&](int col, int head) {
         for (int hp = 0; hp < n_held && ok; ++hp) {
-          ok = mbar_wait(&bars->held_empty[hp], (n & 1u) ^ 1u, ab, 0xC00u + hp);
+          const uint32_t it = n * (uint32_t)n_held + hp;
+          const uint32_t slot = kHeldSlots == 2 ? (uint32_t)hp : it % kHeldSlots;
+          const uint32_t phase = kHeldSlots == 2 ? (n & 1u) : ((it / kHeldSlots) & 1u);
+          ok = mbar_wait(&bars->held_empty[slot], phase ^ 1u, ab, 0xC00u + slot);
           if (!ok) break;
           const int cols = panel_cols(d_held, hp);
-          mbar_arrive_expect_tx(&bars->held_full[hp], wide_panel_bytes(cols));
-          load_panel(held_smem + hp * kTileBytes, tm_held, &bars->held_full[hp], cols, hp * kHeadDim, col * kTile, head, batch);
+          mbar_arrive_expect_tx(&bars->held_full[slot], wide_panel_bytes(cols));
+          load_panel(held_smem + slot * kTileBytes, tm_held, &bars->held_full[slot], cols, hp * kHeadDim, col * kTile,
+                     head, batch);
         }
       };
       auto load_pass = [&](int col, int head, int first, int last) {  // passing panels first .. last - 1
@@ -214,51 +223,79 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         }
       };
       bool ok = mbar_wait(&bars->stat_full, 0, ab, 0xD00u);
-      for (uint32_t n = 0; n < (uint32_t)n_steps && ok; ++n) {
-        // passing panel pp of this step into an accumulating MMA with stationary panel a0 + pp
-        auto mma_passing = [&](uint32_t d, uint32_t a0, int dim, int pp) {
+      // The dv pass has no dP, so its TMEM columns serve as a second S buffer: S^T of step n+1 is
+      // issued (on the prefetched Q panels) before the output MMAs of step n, and runs while the
+      // compute warps turn S^T(n) into P^T(n).  s_buf(n): S buffer of step n; its barriers complete
+      // once per use.
+      // slot and barrier phase of held panel hp of step n.  With two slots and a step that may hold
+      // two panels the ring degenerates to slot = hp, once per step (kept free of arithmetic: the
+      // issuing thread is alone in its warp and pays for every instruction between two MMAs).
+      auto held_slot = [&](uint32_t n, int hp) -> uint32_t {
+        if (kHeldSlots == 2) return (uint32_t)hp;
+        return (n * (uint32_t)n_held + hp) % kHeldSlots;
+      };
+      auto held_phase = [&](uint32_t n, int hp) -> uint32_t {
+        if (kHeldSlots == 2) return n & 1u;
+        return ((n * (uint32_t)n_held + hp) / kHeldSlots) & 1u;
+      };
+      auto wait_held = [&](uint32_t n) {
+        bool good = true;
+        for (int hp = 0; hp < n_held && good; ++hp)
+          good = mbar_wait(&bars->held_full[held_slot(n, hp)], held_phase(n, hp), ab, 0xD10u + hp);
+        return good;
+      };
+      auto s_buf = [&](uint32_t n) { return kPass == kWideDv ? (n & 1u) : 0u; };
+      auto s_use = [&](uint32_t n) { return kPass == kWideDv ? (n >> 1) : n; };
+      // passing panel pp of step n into an accumulating MMA with stationary panel a0 + pp
+      auto mma_passing = [&](uint32_t n, uint32_t d, uint32_t a0, int dim, int pp) {
           const uint32_t it = n * (uint32_t)n_pass + pp, slot = it % kPassSlots;
           if (!mbar_wait(&bars->pass_full[slot], (it / kPassSlots) & 1u, ab, 0xD20u + slot)) return false;
           mma_issue_fence();
           ss_kmajor(d, a0 + pp * kTileBytes, pass_addr + slot * kTileBytes, panel_cols(dim, pp), pp > 0);
           tc_commit(&bars->pass_empty[slot]);
           return true;
-        };
+      };
+      auto dv_scores = [&](uint32_t n) {  // S^T(n) = sum over panels k (passing q)^T
+        bool good = true;
+        for (int pp = 0; pp < npk && good; ++pp) good = mma_passing(n, t_s + s_buf(n) * kTile, a1_addr, p.d_qk, pp);
+        if (good) tc_commit(&bars->s_full[s_buf(n)]);
+        return good;
+      };
+      if (kPass == kWideDv && ok) ok = dv_scores(0);
+      for (uint32_t n = 0; n < (uint32_t)n_steps && ok; ++n) {
         if (kPass != kWideDv) {
           // dP = sum over panels (stationary do or v) (passing v or do)^T: its first panel was loaded
           // during the previous step; the dP columns are free since that step's ds_full
           // (with two passing panels the first goes ahead of S, so that the second can load under S;
           // with one, S goes first and the element-wise phase starts on it while dP runs)
-          if (npv > 1) ok = mma_passing(t_dp, a2_addr, p.d_v, 0);
+          if (npv > 1) ok = mma_passing(n, t_dp, a2_addr, p.d_v, 0);
           if (!ok) break;
-          for (int hp = 0; hp < n_held && ok; ++hp) ok = mbar_wait(&bars->held_full[hp], n & 1u, ab, 0xD10u + hp);
+          ok = wait_held(n);
           if (!ok) break;
           mma_issue_fence();
           for (int pp = 0; pp < npk; ++pp)  // S = sum over panels (stationary q or k) (held k or q)^T
-            ss_kmajor(t_s, a1_addr + pp * kTileBytes, held_addr + pp * kTileBytes, panel_cols(p.d_qk, pp), pp > 0);
-          tc_commit(&bars->s_full);
-          for (int vp = npv > 1 ? 1 : 0; vp < npv && ok; ++vp) ok = mma_passing(t_dp, a2_addr, p.d_v, vp);
+            ss_kmajor(t_s, a1_addr + pp * kTileBytes, held_addr + held_slot(n, pp) * kTileBytes, panel_cols(p.d_qk, pp), pp > 0);
+          tc_commit(&bars->s_full[0]);
+          for (int vp = npv > 1 ? 1 : 0; vp < npv && ok; ++vp) ok = mma_passing(n, t_dp, a2_addr, p.d_v, vp);
           if (!ok) break;
           tc_commit(&bars->dp_full);
         } else {
-          for (int pp = 0; pp < npk && ok; ++pp) ok = mma_passing(t_s, a1_addr, p.d_qk, pp);  // S^T = sum k (passing q)^T
-          if (!ok) break;
-          tc_commit(&bars->s_full);
-          for (int hp = 0; hp < n_held && ok; ++hp) ok = mbar_wait(&bars->held_full[hp], n & 1u, ab, 0xD10u + hp);
+          if (n + 1 < (uint32_t)n_steps) ok = dv_scores(n + 1);
+          ok = ok && wait_held(n);
           if (!ok) break;
         }
-        ok = mbar_wait(&bars->ds_full, n & 1u, ab, 0xD30u);
+        ok = mbar_wait(&bars->ds_full[s_buf(n)], s_use(n) & 1u, ab, 0xD30u);
         if (!ok) break;
         mma_issue_fence();
         // out[:, panel] (+)= (packed P or dS in the S columns) (held panel read MN-major)
         for (int hp = 0; hp < n_held; ++hp) {
           const uint32_t idesc_mn = make_idesc_bf16(kTile, panel_cols(d_held, hp) > 64 ? kHeadDim : 64, false, true);
-          const SmemDesc db = make_smem_desc_sw128(held_addr + hp * kTileBytes, kHalfBytes, 1024);
+          const SmemDesc db = make_smem_desc_sw128(held_addr + held_slot(n, hp) * kTileBytes, kHalfBytes, 1024);
 #pragma unroll
           for (int k = 0; k < 8; ++k)
-            umma_ts(t_out + hp * kHeadDim, t_s + packed_a_col(k), desc_at(db, k * 2048), idesc_mn,
+            umma_ts(t_out + hp * kHeadDim, t_s + s_buf(n) * kTile + packed_a_col(k), desc_at(db, k * 2048), idesc_mn,
                     (n > 0 || k > 0) ? 1u : 0u);
-          tc_commit(&bars->held_empty[hp]);
+          tc_commit(&bars->held_empty[held_slot(n, hp)]);
         }
       }
       tc_commit(&bars->acc_done);
@@ -301,15 +338,18 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
         const int4 ent = entries[e];
         const int st = ent.y & 3;
         const int c0 = ent.x * kTile + w * 64;  // first column: a key (dq pass) or a query row
-        ok = mbar_wait(&bars->s_full, n & 1u, ab, 0xE00u);
+        const uint32_t sb = kPass == kWideDv ? (n & 1u) : 0u;               // S buffer of this step
+        const uint32_t s_phase = (kPass == kWideDv ? (n >> 1) : n) & 1u;   // and how often it was used
+        const uint32_t t_sn = t_s + sb * kTile;
+        ok = mbar_wait(&bars->s_full[sb], s_phase, ab, 0xE00u);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
         float pr[64];
         {
           uint32_t v0[32], v1[32];
-          tmem_ld32(t_s + lane_addr + w * 64, v0);
-          tmem_ld32(t_s + lane_addr + w * 64 + 32, v1);
+          tmem_ld32(t_sn + lane_addr + w * 64, v0);
+          tmem_ld32(t_sn + lane_addr + w * 64 + 32, v1);
           tmem_ld_wait();
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
@@ -419,11 +459,11 @@ splash_bwd_wide_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_co
             pk[2 * t + 1] = pack_bf16(d2, d3);
           }
         }
-        tmem_st32(t_s + lane_addr + packed_col(w), pk);
+        tmem_st32(t_sn + lane_addr + packed_col(w), pk);
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bars->ds_full);
+        if (lane == 0) mbar_arrive(&bars->ds_full[sb]);
       }
     }
 
