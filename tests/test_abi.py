@@ -84,3 +84,41 @@ def test_forward_rejects_bad_tensors_before_touching_the_gpu():
   a.q.dtype = 0
   a.q.stride[2] = 316
   assert lib.splash_fwd(C.byref(a), None) == -1  # row stride not a multiple of 16 bytes
+
+
+def test_ctypes_structs_have_the_layout_the_c_header_gives_them(tmp_path):
+  """sizeof and the offset of the last field of every args struct, as a C compiler sees the header,
+  against the ctypes mirrors the Python layer fills."""
+  import shutil
+  import subprocess
+
+  cc = shutil.which("gcc") or shutil.which("cc")
+  if cc is None:
+    pytest.skip("needs a C compiler")
+  root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+  structs = {
+      "SplashTensor": "stride", "SplashMaskFn": None, "SplashDeviceSchedule": "row_order", "SplashPeerOutput": "head0",
+      "SplashFwdArgs": "o_peer", "SplashFwdFp8Args": "flags", "SplashBwdArgs": "flags", "SplashExchangeArgs": "dst_base_bytes",
+  }
+  lines = ['#include <stddef.h>', '#include <stdio.h>', '#include "splash_b200.h"', "int main(void) {"]
+  for name, last in structs.items():
+    lines.append(f'  printf("{name} %zu %zu\\n", sizeof({name}), ' +
+                 (f"offsetof({name}, {last})" if last else "(size_t)0") + ");")
+  lines += ["  return 0;", "}"]
+  src = tmp_path / "layout.c"
+  src.write_text("\n".join(lines))
+  exe = tmp_path / "layout"
+  subprocess.run([cc, "-std=c99", "-I", os.path.join(root, "include"), str(src), "-o", str(exe)], check=True)
+  out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split("\n")
+  seen = 0
+  for line in out:
+    if not line.strip():
+      continue
+    name, size, offset = line.split()
+    mirror = getattr(_native, name)
+    assert C.sizeof(mirror) == int(size), name
+    last = structs[name]
+    if last:
+      assert getattr(mirror, last).offset == int(offset), (name, last)
+    seen += 1
+  assert seen == len(structs)
