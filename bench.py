@@ -801,10 +801,13 @@ def run_context_parallel(args, w, wname):
       if name not in skip:
         run(t, False, "bench." + name)
   a2a_ms = None if ring_mode else max_over_ranks(timed_steps(exchanges, 3, 1, barrier=dist.barrier))
-  # "fused": the output's exchange runs inside the forward kernel; what stays in line with the kernels
+  # "fused": the kernels store the output (and, with the fused backward, the gradients) straight into
+  # the ranks that own the rows — o, dk, dv from the epilogues of long kernels, dq from the cast pass —
+  # so only the input exchanges (q, k, v, do) stay in line with the kernels
   exposed_ms = a2a_ms
   if not ring_mode and getattr(cp, "fused", False):
-    exposed_ms = max_over_ranks(timed_steps(lambda: exchanges(skip=("o",)), 3, 1, barrier=dist.barrier))
+    inside = ("o",) if kernel.repeatable_dq else ("o", "dq", "dk", "dv")
+    exposed_ms = max_over_ranks(timed_steps(lambda: exchanges(skip=inside), 3, 1, barrier=dist.barrier))
   sent = 2 * (2 * ulysses.exchange_bytes_sent(q.shape, 2, world) + 2 * ulysses.exchange_bytes_sent(k.shape, 2, world))
 
   # end to end: each rank's sequence shard starts and ends in pinned host memory.  Copies run on two
@@ -910,7 +913,7 @@ def run_context_parallel(args, w, wname):
                "single_gpu_ms_per_step": single_ms,
                "scaling_efficiency": None if single_ms is None else single_ms / (world * ms),
                # the exchanges run in line with the kernels, so all of their time is exposed; with
-               # --exchange fused the output's exchange is part of the forward kernel and is left out
+               # --exchange fused the outputs' exchanges are part of the kernels and are left out
                "exposed_a2a_ms_per_step": exposed_ms,
                },
         "roofline": {"bound": "tensor", "achieved": value / world, "peak": peak_sustained, "unit": "TFLOP/s",

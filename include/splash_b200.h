@@ -331,6 +331,11 @@ typedef struct SplashBwdArgs {
   float soft_cap;                   /* as in SplashFwdArgs; dS gains the factor 1 - tanh^2
                                        (base.py:159-163).  0 = off */
   uint32_t flags;                   /* SplashBwdFlags; 0 = split form */
+  /* Second destinations of dq / dk / dv in other ranks' memory (see SplashPeerOutput; dk_peer and
+   * dv_peer are laid out over all kv heads).  dk / dv rows leave from the epilogue of the kernel
+   * that accumulates them, dq rows from the cast pass.  Fused form with head dims up to 128 only
+   * (SPLASH_ERR_UNSUPPORTED otherwise). */
+  SplashPeerOutput dq_peer, dk_peer, dv_peer;
 } SplashBwdArgs;
 
 /* SPLASH_BWD_FUSED_DQ: one kernel per (kv tile, kv head) forms all three gradients, five matmuls

@@ -98,7 +98,7 @@ def test_ctypes_structs_have_the_layout_the_c_header_gives_them(tmp_path):
   root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
   structs = {
       "SplashTensor": "stride", "SplashMaskFn": None, "SplashDeviceSchedule": "row_order", "SplashPeerOutput": "head0",
-      "SplashFwdArgs": "o_peer", "SplashFwdFp8Args": "flags", "SplashBwdArgs": "flags", "SplashExchangeArgs": "dst_base_bytes",
+      "SplashFwdArgs": "o_peer", "SplashFwdFp8Args": "flags", "SplashBwdArgs": "dv_peer", "SplashExchangeArgs": "dst_base_bytes",
   }
   lines = ['#include <stddef.h>', '#include <stdio.h>', '#include "splash_b200.h"', "int main(void) {"]
   for name, last in structs.items():

@@ -556,3 +556,42 @@ def test_forward_peer_output_rows_land_in_their_owners_buffers():
   po.rows_per_peer = 200
   with pytest.raises(_native.SplashError):
     splash.splash_forward(kernel, q, k, v, None, None, 0.09, None, None, 0, o_peer=po)
+
+
+def test_backward_peer_outputs_rows_land_in_their_owners_buffers():
+  """`SplashBwdArgs.dq_peer / dk_peer / dv_peer` on one GPU, two local buffers per gradient standing
+  in for two ranks: dk / dv rows (bit for bit) and dq rows (the fused backward's dq, to its
+  run-to-run tolerance) arrive at this rank's head block of the rank that owns them."""
+  b, hq, hkv, s, d, world, rank = 1, 4, 2, 512, 128, 2, 0
+  dev = torch.device("cuda:0")
+  g = torch.Generator().manual_seed(92)
+  mk = lambda h: torch.randn(b, h, s, d, generator=g).to(torch.bfloat16).to(dev)
+  q, k, v, do = mk(hq), mk(hkv), mk(hkv), mk(hq)
+  kernel = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1)  # fused backward
+  s_loc = s // world
+  _, _, _, o, lse, _, _ = splash.splash_forward(kernel, q, k, v, None, None, 0.09, None, None, 0)
+
+  def receive_buffers(heads):
+    h_all = heads * world
+    bufs = [torch.full((b, h_all, s_loc, d), 7.0, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+    ptrs = torch.tensor([t.data_ptr() for t in bufs], dtype=torch.int64, device=dev)
+    po = _native.SplashPeerOutput()
+    po.ptrs, po.base_bytes, po.rows_per_peer = ptrs.data_ptr(), 0, s_loc
+    po.stride_b, po.stride_h, po.stride_s, po.head0 = h_all * s_loc * d, s_loc * d, d, rank * heads
+    return bufs, ptrs, po
+
+  recv = [receive_buffers(h) for h in (hq, hkv, hkv)]
+  dq, dk, dv, _ = splash.splash_backward(kernel, q, k, v, o, lse, do, None, None, 0.09, 0,
+                                         peers=tuple(po for _, _, po in recv))
+  torch.cuda.synchronize()
+  kernel.check_errors()
+  for (bufs, _, _), local, heads, exact in zip(recv, (dq, dk, dv), (hq, hkv, hkv), (False, True, True)):
+    for peer in range(world):
+      got = bufs[peer][:, rank * heads:(rank + 1) * heads]
+      want = local[:, :, peer * s_loc:(peer + 1) * s_loc]
+      assert torch.equal(got, want) if exact else torch.equal(got, want)  # the cast pass writes both from the same registers
+      assert (bufs[peer][:, (rank + 1) * heads:] == 7.0).all()
+  # the split backward has no second destination
+  split = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1, repeatable_dq=True)
+  with pytest.raises(_native.SplashError):
+    splash.splash_backward(split, q, k, v, o, lse, do, None, None, 0.09, 0, peers=tuple(po for _, _, po in recv))

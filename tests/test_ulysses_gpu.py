@@ -24,7 +24,7 @@ def _free_port():
     return s.getsockname()[1]
 
 
-def _worker(rank, world, port, queue, exchange="nccl"):
+def _worker(rank, world, port, queue, exchange="nccl", repeatable=True):
   os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
   dev = torch.device("cuda", rank)
   torch.cuda.set_device(dev)
@@ -38,8 +38,11 @@ def _worker(rank, world, port, queue, exchange="nccl"):
     g = torch.Generator().manual_seed(7)
     mk = lambda h: torch.randn(b, h, s, D, generator=g).to(torch.bfloat16)
     q, k, v, do = (t.to(dev) for t in (mk(hq), mk(hkv), mk(hkv), mk(hq)))
-    # split backward: every gradient repeats bit for bit, so the comparison can be exact
-    kernel = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1, repeatable_dq=True)
+    # split backward: every gradient repeats bit for bit, so the comparison can be exact; with the
+    # fused backward dq is summed in an order that changes from run to run and gets a tolerance
+    kernel = splash.make_splash_mha(mask_lib.CausalMask((s, s)), q_seq_shards=1, repeatable_dq=repeatable)
+    same_dq = torch.equal if repeatable else (
+        lambda a, b: ((a.float() - b.float()).norm() / b.float().norm()).item() <= 1e-3)
     scale = 1 / math.sqrt(D)
     qf, kf, vf = (t.clone().requires_grad_(True) for t in (q, k, v))
     full = kernel(qf, kf, vf, logits_scale=scale)
@@ -54,7 +57,7 @@ def _worker(rank, world, port, queue, exchange="nccl"):
       out.backward(do[:, :, sl].contiguous())
       torch.cuda.synchronize()
       kernel.check_errors()
-      ok = ok and (torch.equal(out, full[:, :, sl]) and torch.equal(ql.grad, qf.grad[:, :, sl])
+      ok = ok and (torch.equal(out, full[:, :, sl]) and same_dq(ql.grad, qf.grad[:, :, sl])
                    and torch.equal(kl.grad, kf.grad[:, :, sl]) and torch.equal(vl.grad, vf.grad[:, :, sl]))
     with torch.no_grad():
       ok = ok and torch.equal(cp(ql, kl, vl, logits_scale=scale), full[:, :, sl])
@@ -66,13 +69,15 @@ def _worker(rank, world, port, queue, exchange="nccl"):
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
-@pytest.mark.parametrize("exchange", ["nccl", "peer", "fused"])
-def test_ulysses_matches_single_gpu_bitwise(exchange):
+@pytest.mark.parametrize("exchange,repeatable", [("nccl", True), ("peer", True), ("fused", True), ("fused", False)])
+def test_ulysses_matches_single_gpu_bitwise(exchange, repeatable):
+  """("fused", False): the fused backward, whose kernels store dq / dk / dv straight into the ranks
+  that own the rows."""
   world = 2
   ctx = mp.get_context("spawn")
   queue = ctx.Queue()
   port = _free_port()
-  procs = [ctx.Process(target=_worker, args=(r, world, port, queue, exchange)) for r in range(world)]
+  procs = [ctx.Process(target=_worker, args=(r, world, port, queue, exchange, repeatable)) for r in range(world)]
   for p in procs:
     p.start()
   results = [queue.get(timeout=300) for _ in range(world)]

@@ -60,8 +60,9 @@ def test_handler_arguments_cover_the_args_struct_field_for_field(which, struct):
   # derived inside the handler from the sizes of the arrays it is given, or fixed
   derived = {f"{s}.{leaf}" for s in ("sched", "sched_dq", "sched_dkv") for leaf in ("n_rows", "n_entries")}
   derived |= {"workspace_bytes", "launch_mask"}
-  # the second destination of o in other ranks' memory: not reachable from a single-device custom call, left zero
-  derived |= {f"o_peer.{leaf}" for leaf in ("ptrs", "base_bytes", "rows_per_peer", "stride_b", "stride_h", "stride_s", "head0")}
+  # second destinations of outputs in other ranks' memory: not reachable from a single-device custom call, left zero
+  derived |= {f"{out}_peer.{leaf}" for out in ("o", "dq", "dk", "dv")
+              for leaf in ("ptrs", "base_bytes", "rows_per_peer", "stride_b", "stride_h", "stride_s", "head0")}
   assert fields - filled <= derived, sorted(fields - filled - derived)
   names = [n for g in ("operands", "results", "attrs") for n, _ in sig[g]]
   assert len(names) == len(set(names))

@@ -182,6 +182,9 @@ class SplashBwdArgs(C.Structure):
       ("launch_mask", C.c_uint32),
       ("soft_cap", C.c_float),
       ("flags", C.c_uint32),
+      ("dq_peer", SplashPeerOutput),
+      ("dk_peer", SplashPeerOutput),
+      ("dv_peer", SplashPeerOutput),
   ]
 
 

@@ -17,6 +17,7 @@ struct BwdParams {
   int64_t out0_sb, out0_sh, out0_ss;
   __nv_bfloat16* out1;
   int64_t out1_sb, out1_sh, out1_ss;
+  SplashPeerOutput out0_peer, out1_peer;  // second destinations in other ranks' memory (ptrs == nullptr: none)
   const float* nlse2;  // [B, Hq, Sq]  -logsumexp * log2(e)
   const float* delta;  // [B, Hq, Sq]  -sum_d(o * do)
   const int32_t* q_seg;

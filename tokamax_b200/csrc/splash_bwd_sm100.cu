@@ -943,9 +943,12 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
         tmem_ld32(tmem + lane_addr + 2 * kTile + cq * 32, v);
         tmem_ld_wait();
         store_row_half(dk, v, p.scale, cq * 32, p.d_qk);
+        // context parallelism: the row also goes to the rank that owns it in the sequence-sharded layout
+        if (p.out0_peer.ptrs) store_row_half(peer_row(p.out0_peer, batch, kv_head, kv_row) + cq * 32, v, p.scale, cq * 32, p.d_qk);
         tmem_ld32(tmem + lane_addr + 3 * kTile + cq * 32, v);
         tmem_ld_wait();
         store_row_half(dv, v, 1.0f, cq * 32, p.d_v);
+        if (p.out1_peer.ptrs) store_row_half(peer_row(p.out1_peer, batch, kv_head, kv_row) + cq * 32, v, 1.0f, cq * 32, p.d_v);
       }
     } else {
       uint32_t v[32];
@@ -953,6 +956,8 @@ splash_dkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constan
       for (int j = 0; j < 32; ++j) v[j] = 0u;
       store_row_half(dk, v, 0.f, cq * 32, p.d_qk);
       store_row_half(dv, v, 0.f, cq * 32, p.d_v);
+      if (p.out0_peer.ptrs) store_row_half(peer_row(p.out0_peer, batch, kv_head, kv_row) + cq * 32, v, 0.f, cq * 32, p.d_qk);
+      if (p.out1_peer.ptrs) store_row_half(peer_row(p.out1_peer, batch, kv_head, kv_row) + cq * 32, v, 0.f, cq * 32, p.d_v);
     }
   }
 
@@ -977,6 +982,7 @@ struct DqConvertParams {
   int q_heads, n_q_tiles;
   int d_qk;  // columns of dq
   float scale;
+  SplashPeerOutput dq_peer;  // second destination in other ranks' memory (ptrs == nullptr: none)
 };
 
 __global__ void __launch_bounds__(256) splash_dq_convert_kernel(const DqConvertParams p) {
@@ -1003,7 +1009,11 @@ __global__ void __launch_bounds__(256) splash_dq_convert_kernel(const DqConvertP
       uint2 w;
       w.x = pack_bf16(x.x * p.scale, x.y * p.scale);
       w.y = pack_bf16(x.z * p.scale, x.w * p.scale);
-      if ((jg * 8 + jj) * 4 < p.d_qk) *reinterpret_cast<uint2*>(dst + (int64_t)r * p.dq_ss + (jg * 8 + jj) * 4) = w;
+      if ((jg * 8 + jj) * 4 < p.d_qk) {
+        *reinterpret_cast<uint2*>(dst + (int64_t)r * p.dq_ss + (jg * 8 + jj) * 4) = w;
+        if (p.dq_peer.ptrs)
+          *reinterpret_cast<uint2*>(peer_row(p.dq_peer, (int)b, h, qt * kTile + r) + (jg * 8 + jj) * 4) = w;
+      }
     }
   }
 }
@@ -1050,6 +1060,10 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   if (a.logsumexp == nullptr || a.error_record == nullptr || a.workspace == nullptr)
     return SPLASH_ERR_INVALID_ARGUMENT;
   const bool fused = (a.flags & SPLASH_BWD_FUSED_DQ) != 0 && !wide;  // the wide passes are separate by construction
+  if ((st = check_peer_output(a.dq_peer, Sq, D)) || (st = check_peer_output(a.dk_peer, Skv, D)) ||
+      (st = check_peer_output(a.dv_peer, Skv, Dv)))
+    return st;
+  if ((a.dq_peer.ptrs || a.dk_peer.ptrs || a.dv_peer.ptrs) && !fused) return SPLASH_ERR_UNSUPPORTED;
   if (a.workspace_bytes < (fused ? bwd_fused_workspace_bytes(B, Hq, Sq) : bwd_workspace_bytes(B, Hq, Sq)))
     return SPLASH_ERR_INVALID_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(a.workspace) & 255u) != 0) return SPLASH_ERR_INVALID_ARGUMENT;
@@ -1119,6 +1133,8 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   }
 
   BwdParams p;
+  p.out0_peer = SplashPeerOutput{};
+  p.out1_peer = SplashPeerOutput{};
   p.nlse2 = nlse2;
   p.delta = delta;
   p.q_seg = a.q_segment_ids;
@@ -1175,6 +1191,8 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
   p.out1_sb = a.dv.stride[0];
   p.out1_sh = a.dv.stride[1];
   p.out1_ss = a.dv.stride[2];
+  p.out0_peer = a.dk_peer;
+  p.out1_peer = a.dv_peer;
   p.row_ptr = a.sched_dkv.row_ptr;
   p.entries = reinterpret_cast<const int4*>(a.sched_dkv.entries);
   p.row_order = a.sched_dkv.row_order;
@@ -1204,6 +1222,7 @@ int launch_bwd(const SplashBwdArgs& a, cudaStream_t stream) {
     cp.n_q_tiles = (int)(Sq / kTile);
     cp.d_qk = (int)D;
     cp.scale = a.scale;
+    cp.dq_peer = a.dq_peer;
     const int64_t n_tiles = B * Hq * (Sq / kTile);
     if (n_tiles > 0x7fffffffll) return SPLASH_ERR_TOO_LARGE;
     splash_dq_convert_kernel<<<(unsigned)n_tiles, 256, 0, stream>>>(cp);

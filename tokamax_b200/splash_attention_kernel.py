@@ -368,8 +368,11 @@ class _SplashFunction(torch.autograd.Function):
 
 
 def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg=None, kv_seg=None,
-                    scale: float = 1.0, shard: int = 0):
+                    scale: float = 1.0, shard: int = 0, peers=None):
   """One `splash_bwd` call: ``(dq, dk, dv, neg_di)`` for batched ``[B, H, S, 128]`` bf16 tensors.
+
+  ``peers``: optional ``(dq_peer, dk_peer, dv_peer)`` of `_native.SplashPeerOutput`, second
+  destinations of the gradients in other ranks' memory (fused backward only).
 
   ``o`` and ``lse`` are the forward's output and logsumexp for these q rows; they may come from a
   softmax over more keys than ``k`` holds (ring attention passes the merged values, reference
@@ -409,6 +412,8 @@ def splash_backward(kernel: "SplashAttentionKernel", q, k, v, o, lse, d_o, q_seg
   args.workspace_bytes = ws_bytes
   args.soft_cap = float(kernel.config.attn_logits_soft_cap or 0.0)
   args.error_record = tables.error_record.data_ptr()
+  if peers is not None:
+    args.dq_peer, args.dk_peer, args.dv_peer = peers
   stream = torch.cuda.current_stream(q.device).cuda_stream
   with torch.cuda.device(q.device):
     _native.check(lib.splash_bwd(C.byref(args), C.c_void_p(stream)), "splash_bwd")

@@ -205,48 +205,92 @@ def head_to_seq(x: torch.Tensor, group=None, engine: PeerExchange | None = None,
   return _HeadToSeq.apply(x, group, engine, tag)
 
 
-class _AttentionIntoPeers(torch.autograd.Function):
-  """Splash attention on this rank's heads whose forward kernel also stores every output row into
-  the receive buffer of the rank that owns it in the sequence-sharded layout (`SplashFwdArgs.o_peer`:
-  plain 16-byte stores over NVLink from the kernel's epilogue, spread over the whole kernel), so the
-  head -> sequence exchange of the output costs one barrier instead of a transfer.  Returns the
-  sequence shard ``[B, H, S/P, D]``; the backward pass brings dO in by the copy kernel and runs the
-  ordinary backward on the saved head shard.
+def _peer_output(engine: "PeerExchange", tag: str, shape, like: torch.Tensor, head0: int):
+  """(receive buffer of `shape` = [B, all heads, S/P, D], its SplashPeerOutput for this rank's head block)."""
+  from tokamax_b200 import _native  # pylint: disable=g-import-not-at-top
 
-  The receive buffers must be free when this runs: the caller has exchanged q / k / v through the
-  same engine just before, and the barriers of those exchanges lie behind every rank's last read.
+  buf, handle, base = engine._buffer(tag, shape, like.dtype, like.device)  # pylint: disable=protected-access
+  po = _native.SplashPeerOutput()
+  po.ptrs, po.base_bytes, po.rows_per_peer = int(handle.buffer_ptrs_dev), base, shape[2]
+  po.stride_b, po.stride_h, po.stride_s, po.head0 = buf.stride(0), buf.stride(1), buf.stride(2), head0
+  return buf, po
+
+
+class _FusedUlysses(torch.autograd.Function):
+  """Sequence shards of q, k, v in, sequence shard of the output out, as one autograd node whose
+  kernels write their results where they are needed.
+
+  Forward: q, k, v reach the head layout by the copy kernel (three pushes, one pair of barriers); the
+  forward kernel stores every output row into the local head-sharded `o` (the backward's residual)
+  and, from its epilogue, into the receive buffer of the rank that owns the row
+  (`SplashFwdArgs.o_peer`) — plain 16-byte stores over NVLink spread over the whole kernel — so the
+  output's exchange costs one barrier.  Backward: dO comes in by the copy kernel; with the fused
+  backward dK / dV rows leave from the epilogue of the kernel that accumulates them and dQ rows from
+  the cast pass (`SplashBwdArgs.dq_peer / dk_peer / dv_peer`), again followed by one barrier; with
+  the split backward (`repeatable_dq`) the three gradients are pushed (one pair of barriers).
+  There is no device-side wait anywhere: ordering between ranks is the NCCL-ordered barriers.
   """
 
   @staticmethod
-  def forward(ctx, q, k, v, q_seg, kv_seg, kernel, scale, sinks, max_logit, shard, engine, tag):
-    from tokamax_b200 import _native  # pylint: disable=g-import-not-at-top
+  def forward(ctx, q, k, v, owner, segment_ids, logits_scale):
     from tokamax_b200 import splash_attention_kernel as splash  # pylint: disable=g-import-not-at-top
 
-    if sinks is not None or max_logit is not None or shard:
-      raise NotImplementedError("sinks, a fixed maximum and q shards are not taken by the fused exchange")
+    engine, kernel = owner.engine, owner.attention
     rank, world = _world(engine.group)
-    b, h_loc, s_all = q.shape[:3]
+    needs_grad = any(ctx.needs_input_grad[:3])
+    slot = engine.acquire(needs_grad)
+    q_h = engine.exchange(q, True, f"q{slot}", (True, False))
+    k_h = engine.exchange(k, True, f"k{slot}", (False, False))
+    v_h = engine.exchange(v, True, f"v{slot}", (False, True))
+    b, h_loc, s_all = q_h.shape[:3]
     s_loc = s_all // world
-    out, handle, base = engine._buffer(tag, (b, h_loc * world, s_loc, v.shape[3]), q.dtype, q.device)  # pylint: disable=protected-access
-    po = _native.SplashPeerOutput()
-    po.ptrs, po.base_bytes, po.rows_per_peer = int(handle.buffer_ptrs_dev), base, s_loc
-    po.stride_b, po.stride_h, po.stride_s, po.head0 = out.stride(0), out.stride(1), out.stride(2), rank * h_loc
-    q, k, v, o, lse, max_logits, _ = splash.splash_forward(kernel, q, k, v, q_seg, kv_seg, scale, None, None, 0, o_peer=po)
+    out, po = _peer_output(engine, f"o{slot}", (b, h_loc * world, s_loc, v_h.shape[3]), q_h, rank * h_loc)
+    stash = {}
+
+    def into_peers(qh, kh, vh, q_seg, kv_seg, kern, scale, sinks, max_logit, shard):
+      if sinks is not None or max_logit is not None or shard:
+        raise NotImplementedError("sinks, a fixed maximum and q shards are not taken by the fused exchange")
+      res = splash.splash_forward(kern, qh, kh, vh, q_seg, kv_seg, scale, None, None, 0, o_peer=po)
+      stash.update(res=res[:5], seg=(q_seg, kv_seg), scale=scale)
+      return out, res[4], res[5]
+
+    # (the q / k / v pushes' barriers lie behind every rank's last read of its receive buffers)
+    kernel(q_h, k_h, v_h, segment_ids, logits_scale=logits_scale, _function=into_peers)
     with torch.cuda.device(q.device):
-      engine._barrier(q.device)  # every rank's kernel has finished: all rows have landed  # pylint: disable=protected-access
-    ctx.save_for_backward(q, k, v, o, lse, q_seg, kv_seg)
-    ctx.kernel, ctx.scale, ctx.engine, ctx.tag = kernel, scale, engine, tag
-    ctx.mark_non_differentiable(lse, max_logits)
-    return out.clone(), lse, max_logits  # the caller's tensor must outlive the buffer's next use
+      engine._barrier(q.device)  # every rank's forward has finished: all rows have landed  # pylint: disable=protected-access
+    if needs_grad:
+      qh, kh, vh, o_h, lse = stash["res"]
+      q_seg, kv_seg = stash["seg"]
+      ctx.save_for_backward(qh, kh, vh, o_h, lse, q_seg, kv_seg)
+      ctx.kernel, ctx.scale, ctx.engine, ctx.slot = kernel, stash["scale"], engine, slot
+      ctx.shapes = (tuple(q.shape), tuple(k.shape), tuple(v.shape))
+    return out.clone()  # the caller's tensor must outlive the buffer's next use
 
   @staticmethod
-  def backward(ctx, g, _dlse, _dmax):
+  def backward(ctx, g):
     from tokamax_b200 import splash_attention_kernel as splash  # pylint: disable=g-import-not-at-top
 
     q, k, v, o, lse, q_seg, kv_seg = ctx.saved_tensors
-    d_o = ctx.engine.exchange(g, True, ctx.tag + ".grad")
-    dq, dk, dv, _ = splash.splash_backward(ctx.kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale, 0)
-    return (dq, dk, dv) + (None,) * 9
+    engine, slot, kernel = ctx.engine, ctx.slot, ctx.kernel
+    rank, _ = _world(engine.group)
+    d_o = engine.exchange(g, True, f"o{slot}.grad")
+    if kernel.repeatable_dq:  # split backward: its kernels have no second destination
+      dq_h, dk_h, dv_h, _ = splash.splash_backward(kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale, 0)
+      grads = [engine.exchange(dq_h, False, f"q{slot}.grad", (True, False)),
+               engine.exchange(dk_h, False, f"k{slot}.grad", (False, False)),
+               engine.exchange(dv_h, False, f"v{slot}.grad", (False, True))]
+    else:
+      outs = [_peer_output(engine, f"{name}{slot}.grad", shape, q, rank * heads)
+              for name, shape, heads in zip("qkv", ctx.shapes, (q.shape[1], k.shape[1], v.shape[1]))]
+      # (the dO push's barriers lie behind every rank's last read of these buffers)
+      splash.splash_backward(kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale, 0,
+                             peers=tuple(po for _, po in outs))
+      with torch.cuda.device(q.device):
+        engine._barrier(q.device)  # every rank's backward has finished: all rows have landed  # pylint: disable=protected-access
+      grads = [buf for buf, _ in outs]
+    grads = [t.clone() for t in grads]  # handed to the caller as .grad: must outlive the buffers' next use
+    engine.release(slot)
+    return grads[0], grads[1], grads[2], None, None, None
 
 
 class _ReleaseOnBackward(torch.autograd.Function):
@@ -281,9 +325,9 @@ class UlyssesSplashAttention:
     group: process group spanning the context-parallel ranks (default: the world).
     exchange: "nccl" (default: one ``all_to_all_single`` per tensor), "peer" (:class:`PeerExchange`:
       own copy kernel over symmetric memory; CUDA + NVLink peers only) or "fused" ("peer", and the
-      forward kernel itself stores the output into the ranks that own its rows, so the output's
-      exchange is hidden under the kernel; needs a ``SplashAttentionKernel`` with head dims up to 128,
-      falls back to "peer" otherwise).
+      kernels themselves store the output, and with the fused backward the gradients, into the ranks
+      that own the rows (:class:`_FusedUlysses`); needs a ``SplashAttentionKernel`` with head dims up
+      to 128, falls back to "peer" otherwise).
 
   Call with the local sequence shards ``q [B, Hq, S/P, D]``, ``k, v [B, Hkv, S/P, D]``; rank ``r``
   holds tokens ``[r*S/P, (r+1)*S/P)``.  ``P`` must divide the q-head count, and either divide the
@@ -322,6 +366,11 @@ class UlyssesSplashAttention:
       index = torch.tensor(replicate, device=k.device)
       k, v = k.index_select(1, index), v.index_select(1, index)  # [B, P, S/P, D]: one head per destination
     engine = self.engine if world > 1 else None
+    if engine is not None and self.fused and replicate is None and self._can_fuse(q, v):
+      seg_full = None
+      if segment_ids is not None:
+        seg_full = base.SegmentIds(self._gather_seq(segment_ids.q), self._gather_seq(segment_ids.kv))
+      return _FusedUlysses.apply(q, k, v, self, seg_full, logits_scale)
     tags = (None, None, None, None)
     if engine is not None:
       needs_grad = torch.is_grad_enabled() and any(t.requires_grad for t in (q, k, v))
@@ -336,9 +385,6 @@ class UlyssesSplashAttention:
     seg_full = None
     if segment_ids is not None:
       seg_full = base.SegmentIds(self._gather_seq(segment_ids.q), self._gather_seq(segment_ids.kv))
-    if engine is not None and self.fused and self._can_fuse(q_h, v_h):
-      into_peers = lambda *args: _AttentionIntoPeers.apply(*args, engine, tags[3])
-      return self.attention(q_h, k_h, v_h, seg_full, logits_scale=logits_scale, _function=into_peers)
     o_h = self.attention(q_h, k_h, v_h, seg_full, logits_scale=logits_scale)
     out = head_to_seq(o_h, self.group, engine, tags[3])
     return out.clone() if engine is not None else out  # the caller's tensor must outlive the buffer's next use
