@@ -761,6 +761,8 @@ def run_context_parallel(args, w, wname):
       else:
         exchange_used = "nccl (peer exchange unavailable" + (f": {why})" if ok_here == 0.0 else " on another rank)")
         cp = ulysses.UlyssesSplashAttention(kernel, exchange="nccl")
+    elif args.exchange == "fused-o":  # the output from the forward kernel, the gradients by the copy kernel
+      cp = ulysses.UlyssesSplashAttention(kernel, exchange="fused", fuse_gradients=False)
     else:
       cp = ulysses.UlyssesSplashAttention(kernel, exchange=args.exchange)
   n_live = live_pairs(w, None)
@@ -806,7 +808,7 @@ def run_context_parallel(args, w, wname):
   # so only the input exchanges (q, k, v, do) stay in line with the kernels
   exposed_ms = a2a_ms
   if not ring_mode and getattr(cp, "fused", False):
-    inside = ("o",) if kernel.repeatable_dq else ("o", "dq", "dk", "dv")
+    inside = ("o", "dq", "dk", "dv") if cp.fuse_gradients and not kernel.repeatable_dq else ("o",)
     exposed_ms = max_over_ranks(timed_steps(lambda: exchanges(skip=inside), 3, 1, barrier=dist.barrier))
   sent = 2 * (2 * ulysses.exchange_bytes_sent(q.shape, 2, world) + 2 * ulysses.exchange_bytes_sent(k.shape, 2, world))
 
@@ -932,7 +934,7 @@ def main():
   ap.add_argument("--warmup", type=int, default=3)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--workload", default="auto", choices=["auto", "c1", "c2", "c3", "c4", "c5", "wide"])
-  ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer", "fused"],
+  ap.add_argument("--exchange", default="auto", choices=["auto", "nccl", "peer", "fused", "fused-o"],
                   help="Ulysses exchange: the library's own peer-store kernel over symmetric memory (peer), NCCL "
                        "all_to_all_single (nccl), or peer with nccl as the fallback if symmetric memory cannot be set up (auto)")
   ap.add_argument("--cp", default="ulysses", choices=["ulysses", "ring", "ring_zigzag"],

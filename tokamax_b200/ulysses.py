@@ -263,6 +263,7 @@ class _FusedUlysses(torch.autograd.Function):
       q_seg, kv_seg = stash["seg"]
       ctx.save_for_backward(qh, kh, vh, o_h, lse, q_seg, kv_seg)
       ctx.kernel, ctx.scale, ctx.engine, ctx.slot = kernel, stash["scale"], engine, slot
+      ctx.fuse_gradients = owner.fuse_gradients and not kernel.repeatable_dq
       ctx.shapes = (tuple(q.shape), tuple(k.shape), tuple(v.shape))
     return out.clone()  # the caller's tensor must outlive the buffer's next use
 
@@ -274,7 +275,7 @@ class _FusedUlysses(torch.autograd.Function):
     engine, slot, kernel = ctx.engine, ctx.slot, ctx.kernel
     rank, _ = _world(engine.group)
     d_o = engine.exchange(g, True, f"o{slot}.grad")
-    if kernel.repeatable_dq:  # split backward: its kernels have no second destination
+    if not ctx.fuse_gradients:  # (the split backward's kernels have no second destination)
       dq_h, dk_h, dv_h, _ = splash.splash_backward(kernel, q, k, v, o, lse, d_o, q_seg, kv_seg, ctx.scale, 0)
       grads = [engine.exchange(dq_h, False, f"q{slot}.grad", (True, False)),
                engine.exchange(dk_h, False, f"k{slot}.grad", (False, False)),
@@ -336,13 +337,15 @@ class UlyssesSplashAttention:
   rank-local.  Returns the local sequence shard of the output ``[B, Hq, S/P, D]``.
   """
 
-  def __init__(self, attention: Callable, group=None, exchange: str = "nccl"):
+  def __init__(self, attention: Callable, group=None, exchange: str = "nccl", fuse_gradients: bool = True):
     if exchange not in ("nccl", "peer", "fused"):
       raise ValueError(f"exchange must be 'nccl', 'peer' or 'fused', got {exchange!r}")
     self.attention = attention
     self.group = group
     self.engine = PeerExchange(group) if exchange in ("peer", "fused") else None
     self.fused = exchange == "fused"
+    # "fused" only: whether dq / dk / dv also leave from the backward's kernels (else they are pushed)
+    self.fuse_gradients = fuse_gradients
 
   @staticmethod
   def kv_heads_for_ranks(q_heads: int, kv_heads: int, world: int) -> list[int] | None:
