@@ -82,6 +82,14 @@ CASES = [
     _case("causal_2x2_shards_static", ["dense", ["causal", 128, 128, 0]], (16, 16), q_shards=2, kv_shards=2),
     _case("causal_lazy_4qshards", ["causal", 256, 256, 0], (16, 32), q_shards=4, dkv_dynamic=True),
     _case("no_downcast", ["dense", ["causal", 64, 64, 0]], (16, 16), downcast=False, dkv_dynamic=True),
+    # full blocks after the last partial one: the reference's walk over the partial blocks runs out
+    # and stays on the first of them (mask_info.py:208-223)
+    _case("full_blocks_after_last_partial", ["or", ["chunked", 512, 512, 512], ["local", 512, 512, 128, 200, 9]],
+          (128, 256)),
+    _case("full_blocks_after_last_partial_dyn", ["or", ["chunked", 512, 512, 512], ["local", 512, 512, 128, 200, 9]],
+          (128, 128), dkv_dynamic=True),
+    _case("full_blocks_after_last_partial_kvshards", ["or", ["causal", 512, 512, 0], ["random", 512, 512, 0.5, 7]],
+          (128, 128), kv_shards=2, downcast=False),
     # int16 indices: more than 128 blocks per side
     _case("causal_int16_index", ["causal", 4096, 4096, 0], (16, 16), dkv_dynamic=True, digest=True),
     # the benchmark configurations at the kernels' 128x128 blocks; stored as digests

@@ -210,11 +210,20 @@ void shard_metadata(const std::vector<int32_t>& state, const std::vector<int32_t
     m->mask_next.assign(m->block_mask.size(), -1);
     return;
   }
+  // The reference walks the partial blocks with a Python iterator: one advance per step that lies
+  // beyond the current one; once the iterator has run out it stays run out, so every later step
+  // falls back to the FIRST partial block (it does not go round again).
   size_t cur = 0;
+  bool exhausted = false;
   m->mask_next.reserve(walk.size());
   for (int64_t idx : walk) {
     if (idx > partial[cur]) {  // lexicographic (r, c) order == linear order
-      cur = cur + 1 < partial.size() ? cur + 1 : 0;
+      if (!exhausted && cur + 1 < partial.size()) {
+        ++cur;
+      } else {
+        exhausted = true;
+        cur = 0;
+      }
     }
     m->mask_next.push_back(pid[(size_t)partial[cur]]);
   }
