@@ -54,6 +54,14 @@ class QKVLayout(enum.IntEnum):
   SEQ_MINOR = enum.auto()  # [..., head_dim, seq_len]
 
 
+def from_head_minor(vals: tuple, layout: QKVLayout):
+  """A shape (or any tuple) written head-dim-minor, as seen in ``layout``: the last two entries
+  swap for SEQ_MINOR (reference kernel.py:108-111)."""
+  if layout == QKVLayout.HEAD_DIM_MINOR:
+    return vals
+  return (*vals[:-2], vals[-1], vals[-2])
+
+
 @dataclasses.dataclass(frozen=True, slots=True)
 class SplashConfig:
   """Tile sizes and feature switches of the splash kernels (field-compatible with the reference).
