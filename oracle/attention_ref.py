@@ -16,11 +16,18 @@ tokamax/_src/ops/attention/pallas_mosaic_tpu.py:112); here ``scale`` multiplies 
 logits, which is the same function of the inputs up to the rounding of ``q * scale``.
 
 Pinning: the reference holds no stored golden tensors for this path (its kernel tests compare
-against this very function at run time, splash_attention_kernel_test.py:422,508-524), and JAX is
-not installed here, so the numeric oracle cannot be executed against the reference itself.  It is
-pinned instead by (1) an independent float64 numpy evaluation in tests/test_oracle.py and
+against this very function at run time, splash_attention_kernel_test.py:422,508-524).  The
+restatement is pinned against the reference's own functions: ``base.py`` is loaded unmodified
+(oracle/ref_loader.py: load_reference_base) with numpy standing in for ``jax.numpy`` — JAX is not
+installed where this was built, so the arithmetic is numpy's fp32 rather than XLA's, which changes
+the order of summation and nothing else — and the outputs of its ``attention_reference`` (with
+residuals) and ``attention_reference_vjp`` (both ``backward_impl`` values; MHA, GQA, MQA, segment
+ids, sinks, soft cap, head_dim_v != head_dim) are committed as tests/golden/attention_golden.npz
+(generator: tests/golden/gen_attention_golden.py); tests/test_oracle.py compares this module with
+them to fp32 noise, and repeats the comparison live on random cases where a checkout of the
+reference is at hand.  It is also checked against (1) an independent float64 numpy evaluation and
 (2) torch autograd of the forward for the backward formulas.  The MaskInfo half of the path is
-pinned against the reference's own code (see oracle/ref_loader.py).
+pinned against the reference's own code as well (see oracle/ref_loader.py).
 """
 
 from __future__ import annotations

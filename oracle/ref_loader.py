@@ -82,6 +82,55 @@ def load_reference():
   return _load("splash_attention_mask"), _load("splash_attention_mask_info")
 
 
+def _install_numpy_jnp() -> None:
+  """Gives the stub ``jax`` what the reference's dense attention oracle (base.py:74-285) calls, with
+  numpy doing the arithmetic: the ``jnp`` functions it uses (same names and semantics in numpy;
+  ``einsum`` drops ``preferred_element_type``, whose fp32 the fp32 operands already give), ``jax.jit``
+  as the identity and ``jax.vmap`` as a Python loop over axis 0 that stacks the results leaf by leaf.
+  The reference's code then runs unmodified; what differs from a run under XLA is the order of fp32
+  summation inside einsum / sum, nothing else."""
+  import numpy as np
+
+  jax = sys.modules["jax"]
+  if not getattr(jax, "_splash_stub", False) or getattr(jax, "_splash_numpy_jnp", False):
+    return
+  jnp = sys.modules["jax.numpy"]
+  for name in ("logical_and", "tanh", "maximum", "exp", "log", "sum", "repeat", "float32", "where"):
+    setattr(jnp, name, getattr(np, name))
+  jnp.einsum = lambda spec, *ops, preferred_element_type=None, **kw: np.einsum(spec, *ops, **kw)
+
+  def stack(items):
+    first = items[0]
+    if first is None:
+      return None
+    if isinstance(first, dict):
+      return {k: stack([it[k] for it in items]) for k in first}
+    if isinstance(first, tuple):
+      return tuple(stack([it[i] for it in items]) for i in range(len(first)))
+    return np.stack([np.asarray(it) for it in items])
+
+  def vmap(fn, in_axes=0):
+    def mapped(*args):
+      axes = in_axes if isinstance(in_axes, (tuple, list)) else (in_axes,) * len(args)
+      n = next(np.shape(a)[0] for a, ax in zip(args, axes) if ax == 0 and a is not None)
+      return stack([fn(*[(a[i] if ax == 0 and a is not None else a) for a, ax in zip(args, axes)]) for i in range(n)])
+    return mapped
+
+  jax.vmap = vmap
+  jax._splash_numpy_jnp = True
+
+
+def load_reference_base():
+  """The reference's ``base.py`` (its dense attention oracle ``attention_reference`` /
+  ``attention_reference_vjp``), loaded unmodified and runnable on numpy arrays; see
+  :func:`_install_numpy_jnp` for what stands in for JAX."""
+  if not available():
+    raise FileNotFoundError(f"reference tree not found under {REFERENCE_ROOT}")
+  load_reference()       # (installs the stub jax)
+  _install_numpy_jnp()   # before base.py binds `jnp`
+  return _load("base")
+
+
 def run_reference_mask_tests(mask_module=None, mask_info_module=None, verbosity: int = 0):
   """Runs the reference's ``splash_attention_mask_test.py`` and returns the unittest result.
 

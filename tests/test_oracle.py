@@ -1,18 +1,93 @@
 """Pins the numeric oracle (oracle/attention_ref.py).
 
-The reference keeps no stored tensors for this path (its kernel tests call its fp32 oracle at run
-time), and JAX is absent, so the restatement is checked against two independent evaluations:
-a float64 numpy softmax attention written from the definition, and torch autograd of the
-oracle's own forward for the backward formulas (both the "flash" and the "vanilla" di).
+(1) Against the reference's own dense oracle: tests/golden/attention_golden.npz holds the outputs
+of the reference's ``attention_reference`` / ``attention_reference_vjp`` (base.py:185-285), run
+unmodified with numpy standing in for ``jax.numpy`` (tests/golden/gen_attention_golden.py; JAX is
+not installed where the vectors were made, so what differs from a run under XLA is the order of
+fp32 summation).  Where a checkout of the reference is at hand (SPLASH_REFERENCE_ROOT) the same
+comparison also runs live on further random cases.  (2) Against two independent evaluations: a
+float64 numpy softmax attention written from the definition, and torch autograd of the oracle's own
+forward for the backward formulas (both the "flash" and the "vanilla" di).
 """
 import math
+import os
+import sys
 
 import numpy as np
 import pytest
 import torch
 
 from oracle import attention_ref
+from oracle import ref_loader
 from tokamax_b200 import splash_attention_mask as mask_lib
+
+sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden"))
+import attention_cases  # noqa: E402  pylint: disable=wrong-import-position
+
+ATTENTION_GOLDEN = np.load(os.path.join(os.path.dirname(__file__), "golden", "attention_golden.npz"))
+
+
+def _restated(case, q, k, v, do, mask, seg, sinks, impl):
+  """The restatement's outputs for one case, as float32 numpy arrays keyed like the golden file."""
+  t = lambda x: None if x is None else torch.from_numpy(np.ascontiguousarray(x))
+  o, lse, mx = attention_ref.attention_reference(t(q), t(k), t(v), mask, seg, scale=1.0,
+                                                 attn_logits_soft_cap=case["soft_cap"], sinks=t(sinks))
+  o_stored = torch.from_numpy(attention_cases.to_bf16(o.numpy()))
+  dq, dk, dv = attention_ref.attention_reference_vjp(t(do), t(q), t(k), t(v), mask, seg, o_stored, lse, scale=1.0,
+                                                     attn_logits_soft_cap=case["soft_cap"], backward_impl=impl)
+  out = {"o": o, "logsumexp": lse, "max_logits": mx, f"{impl}/dq": dq, f"{impl}/dk": dk, f"{impl}/dv": dv}
+  if sinks is not None:
+    out[f"{impl}/dsinks"] = attention_ref.sinks_vjp(t(do), o_stored, lse, t(sinks))
+  return {key: val.numpy() for key, val in out.items()}
+
+
+def _close(got, want, what):
+  assert got.shape == want.shape, (what, got.shape, want.shape)
+  # fp32 on both sides; the sums (over up to 128 terms with cancellation) are taken in different orders
+  scale = max(1.0, float(np.abs(want).max()))
+  assert np.abs(got - want).max() <= 1e-4 * scale, (what, float(np.abs(got - want).max()), scale)
+
+
+@pytest.mark.parametrize("case", attention_cases.CASES, ids=lambda c: c["name"])
+def test_restatement_matches_the_references_own_oracle(case):
+  q, k, v, do, mask, seg, sinks = attention_cases.build(case)
+  for impl in ("flash", "vanilla") if case["name"] in attention_cases.VANILLA_TOO else ("flash",):
+    got = _restated(case, q, k, v, do, mask, seg, sinks, impl)
+    for key, value in got.items():
+      _close(value, ATTENTION_GOLDEN[f"{case['name']}/{key}"], (case["name"], key))
+  stored = [key for key in ATTENTION_GOLDEN.files if key.startswith(case["name"] + "/")]
+  assert len(stored) >= 6  # o, logsumexp, max_logits, dq, dk, dv (+ dsinks, + the vanilla set)
+
+
+@pytest.mark.skipif(not ref_loader.available(), reason="needs a checkout of the reference (SPLASH_REFERENCE_ROOT)")
+def test_restatement_matches_the_reference_live_on_random_cases():
+  import random
+
+  base = ref_loader.load_reference_base()
+  for n in range(25):
+    rng = random.Random(n)
+    mqa = rng.random() < 0.3
+    hkv = 1 if mqa else rng.choice([1, 2, 3])
+    case = dict(name=f"live{n}", hq=hkv * rng.choice([1, 2, 4]), hkv=hkv, s=8 * rng.randint(2, 12), t=0,
+                d=rng.choice([16, 32, 64]), dv=rng.choice([16, 32, 64]), mask=rng.choice(["causal", "local", "random"]),
+                mqa=mqa, segments=rng.random() < 0.4, sinks=rng.random() < 0.4,
+                soft_cap=rng.choice([None, None, 3.0, 30.0]), seed=100 + n)
+    case["t"] = case["s"] if rng.random() < 0.7 else 8 * rng.randint(2, 12)
+    q, k, v, do, mask, seg, sinks = attention_cases.build(case)
+    seg_ids = None if seg is None else base.SegmentIds(q=seg[0], kv=seg[1])
+    kw = dict(is_mqa=mqa, attn_logits_soft_cap=case["soft_cap"])
+    o, res = base.attention_reference(q, k, v, mask, seg_ids, sinks, save_residuals=True, **kw)
+    impl = rng.choice(["flash", "vanilla"])
+    dq, dk, dv, dsinks = base.attention_reference_vjp(do, q, k, v, mask, seg_ids, sinks, attention_cases.to_bf16(o),
+                                                      res["logsumexp"], backward_impl=impl, **kw)
+    want = {"o": o, "logsumexp": res["logsumexp"], "max_logits": res["max_logits"], f"{impl}/dq": dq,
+            f"{impl}/dk": dk, f"{impl}/dv": dv}
+    if dsinks is not None:
+      want[f"{impl}/dsinks"] = dsinks
+    got = _restated(case, q, k, v, do, mask, seg, sinks, impl)
+    assert set(got) == set(want), (case, sorted(got), sorted(want))
+    for key in want:
+      _close(got[key], np.asarray(want[key], dtype=np.float32), (case, key))
 
 
 def _numpy_attention(q, k, v, mask, scale):
