@@ -435,7 +435,9 @@ def run_reference(args, w, wname):
   line = {
       "impl": "reference", "metric": "splash fwd+bwd TFLOP/s (masked FLOPs)", "value": value, "unit": "TFLOP/s",
       "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3,
-      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+      # (as in the product arm: one GPU runs c2 with fixed work per GPU, N > 1 split c4's fixed work)
+      "higher_is_better": True, "scaling": "weak" if args.gpus == 1 else "strong", "vs_baseline": None,
+      "dtype": "f32", "data": "synthetic",
       "config": {"workload": wname, **{k: w[k] for k in ("batch", "q_heads", "kv_heads", "seq", "mask")},
                  "head_dim": D, "sample_seq": base["sample_seq"],
                  "note": "each step is a bounded sample of the workload (one batch row x one kv-head group at "
