@@ -133,3 +133,27 @@ def test_autotuning_cache_entries_are_in_the_reference_format():
       assert set(json.loads(cfg)) == {"block_q", "block_kv"}
       assert {"compile_time_ms", "lower_time_ms", "evaluation_times_ms", "metadata"} <= set(timing)
       assert all(t > 0 for t in timing["evaluation_times_ms"])
+
+
+def test_jax_backend_overrides_have_the_reference_signatures():
+  """`_fwd` of the backend and of its vjp, parameter by parameter, against the methods they
+  override (tokamax/_src/ops/attention/base.py:564-584 and :813-843; the lists were read off the
+  reference's source).  The module is parsed, not imported: it needs JAX."""
+  import ast
+
+  fwd = ["self", "q", "k", "v", "precision", "logits_dtype", "logits_scale", "bias", "logits_soft_cap", "mask",
+         "dropout_mask", "dropout_rate", "paging_info", "q_indices", "k_indices", "normalize_output",
+         "return_residuals", "config"]
+  vjp = ["self", "residuals", "out", "dout"] + fwd[1:]
+  path = os.path.join(os.path.dirname(HERE), "tokamax_b200", "jax_backend.py")
+  tree = ast.parse(open(path).read())
+  found = {}
+  for node in tree.body:
+    if isinstance(node, ast.ClassDef):
+      for item in node.body:
+        if isinstance(item, ast.FunctionDef) and item.name == "_fwd":
+          a = item.args
+          found[node.name] = [x.arg for x in a.posonlyargs + a.args] + [x.arg for x in a.kwonlyargs]
+  assert found == {"CudaSm100SplashAttention": fwd, "CudaSm100SplashAttentionVjp": vjp}
+  names = {n.name for n in tree.body if isinstance(n, (ast.FunctionDef, ast.ClassDef))}
+  assert {"Config", "register"} <= names
