@@ -14,16 +14,19 @@
 //  dq    Q panels, dO panels        K panels / V panels                   dq += dS k
 //  dk    K panels, V panels         Q panels / dO panels                  dk += dS^T q   (over the q-head group)
 //  dv    K panels                   dO panels / Q panels                  dv += P^T do   (over the q-head group)
-// "held" panels (two slots) feed the output MMA, after the element-wise phase, so they stay for the
-// whole step; "passing" panels go through one slot, one after the other, into an MMA that
+// "held" panels feed the output MMA, after the element-wise phase, so they stay for the whole step;
+// "passing" panels go one after the other (through one slot; two in the dv pass) into an MMA that
 // accumulates over them (dP over the V / dO panels; in the dv pass S over the Q panels).  S of the
 // dq / dk passes multiplies the stationary panels with the held ones.  In the dk / dv passes the
 // tile is transposed (threads own kv rows, columns are query rows), so logsumexp and di come per
 // column and the mask function is evaluated per element, as in the 128-wide dkv kernel.
-// Shared memory: 4 stationary + 2 held + 1 passing panel of 32 KiB (dv pass: 2 + 2 + 2).  A step's
-// first passing panel is loaded while the previous step is still in its element-wise phase (dq / dk:
-// dP of a step is issued ahead of its S, whose held panels arrive later; dv: both Q panels of the
-// next step), the held panels only once the previous output MMAs have released them.  Built for
+// Shared memory: seven panels of 32 KiB — dq / dk: 4 stationary + 2 held + 1 passing; dv (no second
+// stationary operand): 2 stationary + a ring of 3 held + 2 passing.  A step's first passing panel is
+// loaded while the previous step is still in its element-wise phase (dq / dk with two passing
+// panels: the first half of dP is issued ahead of S, whose held panels arrive later; dv: both Q
+// panels and one dO panel of the next step, and S^T alternates between two TMEM buffers — the dP
+// columns are free there — so S^T(n+1) runs under the element-wise phase of step n).  The held
+// panels of dq / dk are loaded only once the previous output MMAs have released them.  Built for
 // coverage of the reference's head dims rather than tuned: S is computed in all three passes.
 #include <mutex>
 
